@@ -1,0 +1,277 @@
+/*
+ * reflex_b200.h -- C ABI of libreflex_b200.so: the paged-KV attention path of
+ * reflex-infer's Python kernel library, as hand-written sm_100a CUDA kernels.
+ *
+ * Conventions (they follow the reference's own C++ API, include/reflex/infer.h:16-23,
+ * 92,189-220, and its API principles, docs/library-architecture.md:57-64,100-105):
+ *   - every entry point takes one pointer to a plain args struct and returns an int
+ *     status; the first six codes are the reference's `Status` values in its order;
+ *   - all pointers are raw DEVICE pointers unless a field says "host";
+ *   - the library never allocates, frees or synchronises: outputs and workspaces are
+ *     caller-owned, every kernel is enqueued on `stream` (a cudaStream_t, 0 = default);
+ *   - strides are in ELEMENTS; index tensors are int64 (slots, block tables) and int32
+ *     (context lengths, positions) exactly as in the reference
+ *     (kernels/kv_cache/triton_kv_paged.py:9-15);
+ *   - nothing throws, aborts or traps; invalid arguments come back as
+ *     RFX_INVALID_ARGUMENT with a message in rfx_last_error().
+ *
+ * Paged cache layout (kernels/kv_cache/triton_kv_paged.py:9-15):
+ *   k_cache, v_cache : [num_blocks, num_kv_heads, block_size, head_dim]
+ *   slot             = page * block_size + position_in_page
+ *   block_table[b,j] = physical page of logical block j of request b
+ */
+#ifndef REFLEX_B200_H_
+#define REFLEX_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RFX_ABI_VERSION 1
+
+/* include/reflex/infer.h:16-23 (first six, same order) + three additions. */
+typedef enum {
+    RFX_SUCCESS = 0,
+    RFX_UNSUPPORTED_DEVICE = 1,
+    RFX_UNSUPPORTED_MODEL = 2,
+    RFX_UNSUPPORTED_QUANT_FORMAT = 3,
+    RFX_INVALID_ARGUMENT = 4,
+    RFX_NOT_IMPLEMENTED = 5,
+    RFX_CUDA_ERROR = 6,          /* a CUDA runtime/driver call failed; see rfx_last_error() */
+    RFX_TIMEOUT = 7,             /* a bounded device-side wait expired (status word) */
+    RFX_WORKSPACE_TOO_SMALL = 8
+} rfx_status;
+
+typedef enum { RFX_F32 = 0, RFX_BF16 = 1, RFX_F16 = 2 } rfx_dtype;
+
+typedef void* rfx_stream; /* cudaStream_t; mirrors StreamHandle, include/reflex/infer.h:92 */
+
+int rfx_abi_version(void);
+/* sizeof() of the args struct with the given index (0 RfxKvAppendArgs, 1 RfxKvLookupArgs,
+ * 2 RfxRopeArgs, 3 RfxRopeTableArgs, 4 RfxRopeAppendArgs, 5 RfxSoftmaxArgs,
+ * 6 RfxAttentionArgs, 7 RfxPagedAttentionArgs, 8 RfxCombineArgs; 0 for anything else), so
+ * a foreign-function binding can verify its struct mirrors before the first call. */
+size_t rfx_args_size(int which);
+const char* rfx_status_string(int status);
+/* Thread-local text of the last non-success status returned on this host thread. */
+const char* rfx_last_error(void);
+
+/* ------------------------------------------------------------------ kv_cache ---- */
+
+/* kv_paged_append / kv_paged_scatter: kernels/kv_cache/__init__.py:31-51,74-90;
+ * semantics of torch_reference_kv_paged_append, triton_kv_paged.py:279-292:
+ *   cache[slot / bs, :, slot % bs, :] = in[n]   for K and V.
+ * Slots must be distinct. A slot outside [0, num_blocks*block_size) is skipped
+ * (the reference's torch path wraps negatives Python-style and raises on overflow;
+ * its .cu would write out of bounds, cuda_kv_paged.cu:33-38). */
+typedef struct {
+    const void* k_in;            /* [N, H_kv, D], strides below */
+    const void* v_in;
+    void* k_cache;               /* [num_blocks, H_kv, block_size, D] */
+    void* v_cache;
+    const int64_t* slot_mapping; /* [N] */
+    int64_t n_tokens, num_kv_heads, head_dim, num_blocks, block_size;
+    int64_t in_stride_n, in_stride_h;        /* shared by k_in and v_in; last dim contiguous */
+    int64_t cache_stride_blk, cache_stride_h, cache_stride_pos; /* last dim contiguous */
+    int dtype;                   /* rfx_dtype; a pure byte copy, any of the three */
+    rfx_stream stream;
+} RfxKvAppendArgs;
+int rfx_kv_paged_append(const RfxKvAppendArgs* a);
+int rfx_kv_paged_scatter(const RfxKvAppendArgs* a); /* same op, kv_cache/__init__.py:74-90 */
+
+/* kv_paged_lookup: kernels/kv_cache/__init__.py:54-71; semantics of
+ * torch_reference_kv_paged_lookup, triton_kv_paged.py:295-317:
+ *   out[b, h, t, :] = cache[block_table[b, t / bs], h, t % bs, :]  for t < ctx_len[b],
+ *   zero for t >= ctx_len[b] (K and V both; tests/test_kv_cache.py:117-122). */
+typedef struct {
+    const void* k_cache;
+    const void* v_cache;
+    void* k_out;                 /* [B, H_kv, max_ctx, D] contiguous, fully written */
+    void* v_out;
+    const int64_t* block_table;  /* [B, max_blocks] */
+    const int32_t* context_lens; /* [B] */
+    int64_t batch, num_kv_heads, head_dim, num_blocks, block_size, max_ctx, max_blocks;
+    int64_t cache_stride_blk, cache_stride_h, cache_stride_pos;
+    int64_t bt_stride_b;         /* block_table row stride, entries contiguous in a row */
+    int dtype;
+    rfx_stream stream;
+} RfxKvLookupArgs;
+int rfx_kv_paged_lookup(const RfxKvLookupArgs* a);
+
+/* --------------------------------------------------------------------- rope ---- */
+
+/* apply_rope / apply_rope_: kernels/rope/__init__.py:19-65; arithmetic of
+ * torch_reference_rope, triton_rope.py:199-244: every multiply, subtract and add is
+ * rounded to the activation dtype (the torch eager sequence), so 16-bit results are
+ * bit-identical to the reference's torch path when the tables have the activation
+ * dtype. Row s of cos/sin belongs to sequence index s. y may alias x (in place). */
+typedef struct {
+    const void* x;               /* logical [B, S, H, D]; strides below */
+    void* y;
+    const void* cos;             /* [S, D] in the activation dtype */
+    const void* sin;
+    int64_t batch, seq, heads, head_dim;
+    int64_t x_stride_b, x_stride_s, x_stride_h;   /* last dim contiguous */
+    int64_t y_stride_b, y_stride_s, y_stride_h;
+    int64_t table_stride_s;
+    int interleaved;             /* 0: pairs (i, i+D/2); 1: pairs (2i, 2i+1) */
+    int dtype;
+    rfx_stream stream;
+} RfxRopeArgs;
+int rfx_rope_apply(const RfxRopeArgs* a);
+
+/* build_rope_tables: kernels/rope/triton_rope.py:247-285, computed on the device:
+ * angle = pos*theta_i as one fp32 multiply (:269), cos/sin evaluated in fp64 of that
+ * fp32 angle and rounded to fp32 (:270-271), duplicated to width D (:273-280), cast to
+ * `dtype` (:285). theta_i = 1/base^(i/half) (:267) is read from inv_freq when given (so
+ * a caller can pass the exact fp32 vector its own framework computes), else computed
+ * here as 1.0f / (float)pow(base, (float)i/half). */
+typedef struct {
+    void* cos;                   /* [seq_len, D] contiguous */
+    void* sin;
+    const float* inv_freq;       /* [D/2] or NULL */
+    int64_t seq_len, head_dim;
+    double base;
+    int interleaved;
+    int dtype;
+    rfx_stream stream;
+} RfxRopeTableArgs;
+int rfx_rope_build_tables(const RfxRopeTableArgs* a);
+
+/* Fused RoPE + append (no single reference function; it is the composition
+ * apply_rope(k_new) -> kv_paged_append of kernels/rope/__init__.py:19-39 and
+ * kernels/kv_cache/__init__.py:31-51). Token n is rotated with table row positions[n];
+ * K is rotated and written to the pool, V is copied; if q/q_out are given, Q is
+ * rotated too (q_out may alias q). Cache contents equal the reference composition
+ * bit for bit. */
+typedef struct {
+    const void* k_in;            /* [N, H_kv, D] contiguous */
+    const void* v_in;
+    const void* q_in;            /* [N, H_q, D] contiguous, or NULL */
+    void* q_out;                 /* or NULL */
+    void* k_cache;
+    void* v_cache;
+    const int64_t* slot_mapping; /* [N] */
+    const int32_t* positions;    /* [N] row of the tables for token n */
+    const void* cos;             /* [table_rows, D] activation dtype */
+    const void* sin;
+    int64_t n_tokens, num_q_heads, num_kv_heads, head_dim, num_blocks, block_size, table_rows;
+    int64_t cache_stride_blk, cache_stride_h, cache_stride_pos;
+    int interleaved;
+    int dtype;
+    rfx_stream stream;
+} RfxRopeAppendArgs;
+int rfx_rope_append(const RfxRopeAppendArgs* a);
+
+/* ------------------------------------------------------------------ softmax ---- */
+
+/* online_softmax: kernels/softmax/__init__.py:15-35; torch_reference_softmax,
+ * triton_softmax.py:178-202. Rows of a [rows, n] contiguous matrix; causal masks
+ * col > row % n (square contract, triton_softmax.py:66-69,146-164). */
+typedef struct {
+    const void* x;
+    void* y;
+    int64_t rows, n;
+    int is_causal;
+    int log;
+    int dtype;
+    rfx_stream stream;
+} RfxSoftmaxArgs;
+int rfx_online_softmax(const RfxSoftmaxArgs* a);
+
+/* ---------------------------------------------------------------- attention ---- */
+
+/* fused_attention (dense): kernels/attention/__init__.py:86-123; semantics of
+ * torch_reference_attention, triton_fused_attention.py:350-371, with in-kernel GQA
+ * h_kv = h / (H/H_kv) (triton_fused_attention.py:130-132), top-left causal
+ * (:185-187), optional additive mask [B,H,S_q,S_k] (:190-202,303-308). */
+typedef struct {
+    const void* q;               /* [B, H, S_q, D] contiguous */
+    const void* k;               /* [B, H_kv, S_k, D] contiguous */
+    const void* v;
+    void* out;                   /* [B, H, S_q, D] */
+    const void* attn_mask;       /* same dtype as q, contiguous, or NULL */
+    int64_t batch, num_q_heads, num_kv_heads, seq_q, seq_k, head_dim;
+    float sm_scale;
+    int is_causal;
+    int dtype;
+    void* workspace;             /* may be NULL when rfx_fused_attention_workspace_bytes() is 0 */
+    size_t workspace_bytes;
+    rfx_stream stream;
+} RfxAttentionArgs;
+size_t rfx_fused_attention_workspace_bytes(const RfxAttentionArgs* a);
+int rfx_fused_attention(const RfxAttentionArgs* a);
+
+/* Paged attention over ragged query chunks: the fused form of the composition
+ * kv_paged_lookup -> repeat_interleave -> fused_attention evaluated per request with
+ * max_ctx = context_lens[b] (kernels/kv_cache/__init__.py:54-71,
+ * kernels/attention/__init__.py:86-123). Request b owns query rows
+ * [q_start[b], q_start[b+1]) (one row per request when q_start is NULL: decode) and
+ * keys 0..context_lens[b]-1, the new tokens included. Causal is bottom-right aligned:
+ * query row i of n_b sees keys 0..context_lens[b]-n_b+i, the rule of
+ * src/kernels/attention.cu:187. A request with no keys gives zeros
+ * (src/kernels/attention.cu:163).
+ *
+ * Split-K: the work is cut into (request, kv_head, key-range) items by
+ * rfx_paged_attention_plan, each item leaves an un-normalised (m, l, acc) partial in
+ * the workspace, and rfx_splitk_combine merges them with the recurrence of
+ * kernels/softmax/triton_softmax.py:84-89 / triton_fused_attention.py:205-227.
+ * rfx_paged_attention runs plan (unless reuse_plan), partial kernel and combine. */
+typedef struct {
+    const void* q;               /* [N_q, H_q, D] contiguous */
+    void* out;                   /* [N_q, H_q, D] */
+    const void* k_cache;         /* [num_blocks, H_kv, block_size, D] contiguous */
+    const void* v_cache;
+    const int64_t* block_table;  /* [B, max_blocks] */
+    const int32_t* context_lens; /* [B] keys per request, new tokens included */
+    const int32_t* q_start;      /* [B+1] or NULL (decode: row b belongs to request b) */
+    /* optional RoPE fused into the Q load (rows rope_positions[n] of the tables) */
+    const void* rope_cos;        /* [table_rows, D] activation dtype, or NULL */
+    const void* rope_sin;
+    const int32_t* rope_positions; /* [N_q] */
+    int64_t n_q, batch, num_q_heads, num_kv_heads, head_dim;
+    int64_t num_blocks, block_size, max_blocks, bt_stride_b, table_rows;
+    int64_t max_q_len;           /* host upper bound of any request's query rows (1 for decode) */
+    float sm_scale;
+    int is_causal;               /* bottom-right; irrelevant when every request has one row */
+    int rope_interleaved;
+    int dtype;
+    int reuse_plan;              /* 1: workspace already holds a plan for these lengths */
+    int force_generic;           /* 1: use the scalar kernel (debug / parity cross-check) */
+    int64_t target_chunk;        /* 0 = choose; else keys per split (rounded to 64) */
+    void* workspace;
+    size_t workspace_bytes;
+    rfx_stream stream;
+} RfxPagedAttentionArgs;
+size_t rfx_paged_attention_workspace_bytes(const RfxPagedAttentionArgs* a);
+int rfx_paged_attention_plan(const RfxPagedAttentionArgs* a);
+int rfx_paged_attention(const RfxPagedAttentionArgs* a);
+
+/* Split-K combine on caller-provided partials (the recurrence of
+ * kernels/softmax/triton_softmax.py:84-89 with an accumulator,
+ * triton_fused_attention.py:205-227): rows r = 0..rows-1 each own splits
+ * [split_begin[r], split_begin[r+1]); out[r,:] = sum_s acc[s,:]*exp(m[s]-M) / sum_s l[s]*exp(m[s]-M). */
+typedef struct {
+    const float* acc;            /* [n_partials, D] */
+    const float* m;              /* [n_partials] row maxima (natural-log domain) */
+    const float* l;              /* [n_partials] */
+    const int32_t* split_begin;  /* [rows+1] */
+    void* out;                   /* [rows, D] in dtype */
+    int64_t rows, head_dim;
+    int dtype;
+    rfx_stream stream;
+} RfxCombineArgs;
+int rfx_splitk_combine(const RfxCombineArgs* a);
+
+/* Reads the device status word a paged-attention launch leaves in its workspace
+ * (0 = ok; bit 0 = a bounded wait expired; bit 1 = a page index outside the pool was
+ * skipped). Synchronises the stream; meant for tests and debugging. */
+int rfx_paged_attention_status(const void* workspace, rfx_stream stream, int* status_word_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* REFLEX_B200_H_ */

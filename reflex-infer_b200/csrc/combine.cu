@@ -1,0 +1,145 @@
+// Split-K combine: merges the un-normalised (m, l, acc) partials of one attention row
+// with the running-max recurrence of kernels/softmax/triton_softmax.py:84-89 (with an
+// accumulator: triton_fused_attention.py:205-227), written as max-then-weighted-sum so
+// the result does not depend on the order of the splits:
+//   M = max_s m_s ; out = sum_s acc_s*exp(m_s - M) / sum_s l_s*exp(m_s - M).
+// One warp per output row, lanes across head_dim. Traffic: (D+2)*4 bytes per partial
+// row read, D*e bytes per output row written.
+#include "paged_plan.cuh"
+
+namespace rfx {
+
+constexpr int kCombineWarps = 4;
+
+template <typename T, typename PartialRow>
+__device__ inline void combine_row(int ns, PartialRow prow_of, const float* __restrict__ pm,
+                                   const float* __restrict__ pl, const float* __restrict__ pacc, int D,
+                                   T* __restrict__ orow) {
+    const int lane = threadIdx.x & 31;
+    float M = -INFINITY;
+    for (int s = lane; s < ns; s += 32) M = fmaxf(M, pm[prow_of(s)]);
+    M = warp_max(M);
+    float L = 0.f;
+    if (M > -INFINITY)
+        for (int s = lane; s < ns; s += 32) {
+            const long long pr = prow_of(s);
+            L += pl[pr] * expf(pm[pr] - M);
+        }
+    L = warp_sum(L);
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    for (int d0 = 0; d0 < D; d0 += 128) {
+        const int d = d0 + lane * 4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (d < D && M > -INFINITY) {
+            for (int s = 0; s < ns; ++s) {
+                const long long pr = prow_of(s);
+                const float w = expf(pm[pr] - M);
+                const float* ar = pacc + pr * D + d;
+                if (d + 3 < D && (D & 3) == 0) {
+                    const float4 v = *reinterpret_cast<const float4*>(ar);
+                    acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y);
+                    acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+                } else {
+                    acc.x = fmaf(w, ar[0], acc.x);
+                    if (d + 1 < D) acc.y = fmaf(w, ar[1], acc.y);
+                    if (d + 2 < D) acc.z = fmaf(w, ar[2], acc.z);
+                    if (d + 3 < D) acc.w = fmaf(w, ar[3], acc.w);
+                }
+            }
+        }
+        if (d < D) {
+            orow[d] = Num<T>::from_f(acc.x * inv);
+            if (d + 1 < D) orow[d + 1] = Num<T>::from_f(acc.y * inv);
+            if (d + 2 < D) orow[d + 2] = Num<T>::from_f(acc.z * inv);
+            if (d + 3 < D) orow[d + 3] = Num<T>::from_f(acc.w * inv);
+        }
+    }
+}
+
+// Output rows = n_q * Hq, row = (query row r, head h).
+template <typename T>
+__global__ void __launch_bounds__(kCombineWarps * 32)
+paged_combine_kernel(T* __restrict__ out, const int32_t* __restrict__ q_start, int B, int64_t n_q, int Hq,
+                     int Hkv, int D, int32_t* hdr, const int32_t* __restrict__ split_base,
+                     const int32_t* __restrict__ item_prow, const float* __restrict__ pm,
+                     const float* __restrict__ pl, const float* __restrict__ pacc) {
+    const int warp = threadIdx.x >> 5;
+    const int G = Hq / Hkv;
+    const int64_t rows = n_q * Hq;
+    for (int64_t orow = (int64_t)blockIdx.x * kCombineWarps + warp; orow < rows;
+         orow += (int64_t)gridDim.x * kCombineWarps) {
+        const int h = (int)(orow % Hq);
+        const int64_t r = orow / Hq;
+        int b, qi;
+        if (q_start) {
+            int lo = 0, hi = B;  // last b with q_start[b] <= r
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (q_start[mid] <= r) lo = mid; else hi = mid;
+            }
+            b = lo;
+            qi = (int)(r - q_start[b]);
+        } else {
+            b = (int)r;
+            qi = 0;
+        }
+        const int hkv = h / G, g = h % G;
+        const int ns = split_base[b + 1] - split_base[b];
+        const long long item0 = (long long)Hkv * split_base[b] + (long long)hkv * ns;
+        const int within = qi * G + g;
+        combine_row<T>(ns, [&](int s) { return (long long)item_prow[item0 + s] + within; }, pm, pl, pacc, D,
+                       out + orow * D);
+    }
+    // Re-arm the work counter so the same plan can drive the next layer's launch.
+    if (blockIdx.x == 0 && threadIdx.x == 0) hdr[HdrWorkCounter] = 0;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kCombineWarps * 32)
+splitk_combine_kernel(T* __restrict__ out, const int32_t* __restrict__ split_begin, int64_t rows, int D,
+                      const float* __restrict__ pm, const float* __restrict__ pl,
+                      const float* __restrict__ pacc) {
+    const int warp = threadIdx.x >> 5;
+    for (int64_t r = (int64_t)blockIdx.x * kCombineWarps + warp; r < rows;
+         r += (int64_t)gridDim.x * kCombineWarps) {
+        const int s0 = split_begin[r], ns = split_begin[r + 1] - s0;
+        combine_row<T>(ns, [&](int s) { return (long long)(s0 + s); }, pm, pl, pacc, D, out + r * D);
+    }
+}
+
+int launch_paged_combine(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P) {
+    const int64_t rows = a->n_q * a->num_q_heads;
+    int64_t blocks = ceil_div<int64_t>(rows, kCombineWarps);
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    RFX_DISPATCH_DTYPE(a->dtype, T, {
+        paged_combine_kernel<T><<<(int)blocks, kCombineWarps * 32, 0, as_stream(a->stream)>>>(
+            (T*)a->out, a->q_start, (int)a->batch, a->n_q, (int)a->num_q_heads, (int)a->num_kv_heads,
+            (int)a->head_dim, P.hdr, P.split_base, P.item_prow, P.m, P.l, P.acc);
+    });
+    return check_launch("rfx_paged_attention (combine)");
+}
+
+}  // namespace rfx
+
+extern "C" int rfx_splitk_combine(const RfxCombineArgs* a) {
+    using namespace rfx;
+    const char* name = "rfx_splitk_combine";
+    if (!a) return fail(RFX_INVALID_ARGUMENT, "%s: null args", name);
+    RFX_REQUIRE(dtype_ok(a->dtype), "%s: unknown dtype %d", name, a->dtype);
+    RFX_REQUIRE(a->rows >= 0 && a->head_dim > 0, "%s: bad sizes", name);
+    if (a->rows == 0) return RFX_SUCCESS;
+    RFX_REQUIRE(a->acc && a->m && a->l && a->split_begin && a->out, "%s: null pointer", name);
+    RFX_REQUIRE(((uintptr_t)a->acc % 16) == 0, "%s: acc must be 16-byte aligned", name);
+    int st = check_device();
+    if (st != RFX_SUCCESS) return st;
+    int64_t blocks = ceil_div<int64_t>(a->rows, kCombineWarps);
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    RFX_DISPATCH_DTYPE(a->dtype, T, {
+        splitk_combine_kernel<T><<<(int)blocks, kCombineWarps * 32, 0, as_stream(a->stream)>>>(
+            (T*)a->out, a->split_begin, a->rows, (int)a->head_dim, a->m, a->l, a->acc);
+    });
+    return check_launch(name);
+}

@@ -1,0 +1,94 @@
+// Entry points of paged attention: argument checks, workspace layout, and the three
+// launches of a step (plan, split-K partials, combine).
+#include "paged_plan.cuh"
+
+namespace rfx {
+
+static int validate(const RfxPagedAttentionArgs* a, const char* name) {
+    if (!a) return fail(RFX_INVALID_ARGUMENT, "%s: null args", name);
+    RFX_REQUIRE(dtype_ok(a->dtype), "%s: unknown dtype %d", name, a->dtype);
+    RFX_REQUIRE(a->batch >= 0 && a->n_q >= 0 && a->num_q_heads > 0 && a->num_kv_heads > 0 && a->head_dim > 0 &&
+                    a->num_blocks > 0 && a->block_size > 0 && a->max_blocks >= 0,
+                "%s: bad sizes", name);
+    RFX_REQUIRE(a->num_q_heads % a->num_kv_heads == 0,
+                "GQA requires num_heads_q (%lld) divisible by num_heads_kv (%lld)", (long long)a->num_q_heads,
+                (long long)a->num_kv_heads);
+    RFX_REQUIRE(a->head_dim <= 256, "%s: head_dim %lld > 256", name, (long long)a->head_dim);
+    RFX_REQUIRE(a->q_start != nullptr || a->n_q == a->batch,
+                "%s: without q_start there is one query row per request (n_q=%lld, batch=%lld)", name,
+                (long long)a->n_q, (long long)a->batch);
+    RFX_REQUIRE(a->batch < (1ll << 24) && a->n_q < (1ll << 31), "%s: batch too large", name);
+    RFX_REQUIRE((a->rope_cos == nullptr) == (a->rope_sin == nullptr), "%s: rope_cos and rope_sin go together", name);
+    RFX_REQUIRE(a->rope_cos == nullptr || (a->rope_positions != nullptr && a->head_dim % 2 == 0),
+                "%s: fused RoPE needs rope_positions and an even head_dim", name);
+    return RFX_SUCCESS;
+}
+
+static PlanLayout layout_of(const RfxPagedAttentionArgs* a) {
+    const int64_t G = a->num_q_heads / a->num_kv_heads;
+    return plan_layout(a->batch, a->num_kv_heads, G, a->n_q, a->max_q_len, a->head_dim, sm_count());
+}
+
+}  // namespace rfx
+
+extern "C" size_t rfx_paged_attention_workspace_bytes(const RfxPagedAttentionArgs* a) {
+    using namespace rfx;
+    if (validate(a, "rfx_paged_attention_workspace_bytes") != RFX_SUCCESS) return 0;
+    return layout_of(a).total;
+}
+
+extern "C" int rfx_paged_attention_plan(const RfxPagedAttentionArgs* a) {
+    using namespace rfx;
+    const char* name = "rfx_paged_attention_plan";
+    int st = validate(a, name);
+    if (st != RFX_SUCCESS) return st;
+    if (a->batch == 0) return RFX_SUCCESS;
+    RFX_REQUIRE(a->context_lens && a->workspace, "%s: null pointer", name);
+    st = check_device();
+    if (st != RFX_SUCCESS) return st;
+    const PlanLayout L = layout_of(a);
+    if (a->workspace_bytes < L.total)
+        return fail(RFX_WORKSPACE_TOO_SMALL, "%s: workspace %zu B < %zu B", name, a->workspace_bytes, L.total);
+    RFX_REQUIRE(((uintptr_t)a->workspace % 256) == 0, "%s: workspace must be 256-byte aligned", name);
+    const PlanPtrs P = plan_ptrs(a->workspace, L);
+    const int ctas = decode_mma_supported(a) ? decode_mma_ctas(a) : sm_count() * 4;
+    return launch_plan(a, L, P, ctas);
+}
+
+extern "C" int rfx_paged_attention(const RfxPagedAttentionArgs* a) {
+    using namespace rfx;
+    const char* name = "rfx_paged_attention";
+    int st = validate(a, name);
+    if (st != RFX_SUCCESS) return st;
+    if (a->batch == 0 || a->n_q == 0) return RFX_SUCCESS;
+    RFX_REQUIRE(a->q && a->out && a->k_cache && a->v_cache && a->block_table && a->context_lens && a->workspace,
+                "%s: null pointer", name);
+    st = check_device();
+    if (st != RFX_SUCCESS) return st;
+    const PlanLayout L = layout_of(a);
+    if (a->workspace_bytes < L.total)
+        return fail(RFX_WORKSPACE_TOO_SMALL, "%s: workspace %zu B < %zu B", name, a->workspace_bytes, L.total);
+    RFX_REQUIRE(((uintptr_t)a->workspace % 256) == 0, "%s: workspace must be 256-byte aligned", name);
+    const PlanPtrs P = plan_ptrs(a->workspace, L);
+    const bool mma = decode_mma_supported(a);
+    if (!a->reuse_plan) {
+        st = launch_plan(a, L, P, mma ? decode_mma_ctas(a) : sm_count() * 4);
+        if (st != RFX_SUCCESS) return st;
+    }
+    st = mma ? launch_decode_mma(a, L, P) : launch_paged_generic(a, L, P);
+    if (st != RFX_SUCCESS) return st;
+    return launch_paged_combine(a, L, P);
+}
+
+extern "C" int rfx_paged_attention_status(const void* workspace, rfx_stream stream, int* status_word_host) {
+    using namespace rfx;
+    if (!workspace || !status_word_host) return fail(RFX_INVALID_ARGUMENT, "rfx_paged_attention_status: null pointer");
+    int32_t w = 0;
+    cudaError_t e = cudaMemcpyAsync(&w, (const int32_t*)workspace + HdrStatus, sizeof(w), cudaMemcpyDeviceToHost,
+                                    as_stream(stream));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(as_stream(stream));
+    if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "rfx_paged_attention_status: %s", cudaGetErrorString(e));
+    *status_word_host = w;
+    if (w & kStatusWaitExpired) return fail(RFX_TIMEOUT, "a bounded device-side wait expired (status word %d)", w);
+    return RFX_SUCCESS;
+}

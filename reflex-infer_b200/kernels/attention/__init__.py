@@ -1,0 +1,370 @@
+"""Attention; ``fused_attention`` keeps the reference's surface
+(``kernels/attention/__init__.py:86-123``) and the paged entry points fuse the
+composition the reference spells as lookup -> attention.
+
+Dense:
+    ``fused_attention(q, k, v, *, is_causal, attn_mask, sm_scale, backend)``
+
+Paged (additive; none of them changes the functions above):
+    ``rope_append``        RoPE on new K (and optionally Q) + write K, V into the pool
+    ``paged_attention``    split-K attention straight from the pool, ragged query chunks,
+                           bottom-right causal, optional RoPE fused into the Q load
+    ``paged_decode``       the one-row-per-request case of ``paged_attention``
+    ``paged_decode_step``  ``rope_append`` + ``paged_decode`` for one decode step
+    ``PagedWorkspace``     caller-owned scratch for the split-K plan and partials
+    ``splitk_combine``     merge caller-provided (m, l, acc) partials
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .. import _native as N
+
+
+def _resolve_head_repeat(num_heads_q: int, num_heads_kv: int) -> int:
+    if num_heads_q % num_heads_kv != 0:
+        raise ValueError(
+            f"GQA requires num_heads_q ({num_heads_q}) divisible by "
+            f"num_heads_kv ({num_heads_kv})"
+        )
+    return num_heads_q // num_heads_kv
+
+
+def fused_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    *,
+    is_causal: bool = False,
+    attn_mask: Optional[torch.Tensor] = None,
+    sm_scale: Optional[float] = None,
+    backend: Optional[str] = None,
+) -> torch.Tensor:
+    """``softmax(q k^T * sm_scale + attn_mask) v`` with in-kernel GQA.
+
+    ``q``: ``[B, H, S_q, D]``; ``k``, ``v``: ``[B, H_kv, S_k, D]`` with ``H % H_kv == 0`` (query
+    head ``h`` reads kv head ``h // (H/H_kv)``, ``triton_fused_attention.py:130-132``);
+    ``is_causal`` masks ``key > query`` (top-left aligned, ``:185-187``); ``attn_mask`` is an
+    additive ``[B, H, S_q, S_k]`` bias (bool masks and broadcastable shapes are expanded);
+    ``sm_scale`` defaults to ``1/sqrt(D)``. Output ``[B, H, S_q, D]`` in ``q``'s dtype.
+    """
+    N.check_backend(backend)
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError(f"shape mismatch q={tuple(q.shape)} k={tuple(k.shape)} v={tuple(v.shape)}")
+    if not q.is_cuda:
+        raise RuntimeError("fused_attention requires a CUDA tensor")
+    dev = N.require_cuda("fused_attention", q, k, v, attn_mask)
+    B, H, S_q, D = q.shape
+    Bk, Hk, S_k, Dk = k.shape
+    Bv, Hv, S_v, Dv = v.shape
+    if (B, S_k, D) != (Bk, S_k, Dk) or (B, S_k, D) != (Bv, S_v, Dv):
+        raise ValueError(f"shape mismatch q={q.shape} k={k.shape} v={v.shape}")
+    if Hk != Hv:
+        raise ValueError(f"K/V head count mismatch: {Hk} vs {Hv}")
+    _resolve_head_repeat(H, Hk)
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise RuntimeError(f"q, k, v dtypes differ: {q.dtype}, {k.dtype}, {v.dtype}")
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    if attn_mask is not None:
+        if attn_mask.dtype == torch.bool:
+            attn_mask = torch.zeros(attn_mask.shape, dtype=q.dtype, device=dev).masked_fill_(~attn_mask, float("-inf"))
+        try:
+            attn_mask = attn_mask.expand(B, H, S_q, S_k)
+        except RuntimeError:
+            raise ValueError(
+                f"attn_mask must be [{B},{H},{S_q},{S_k}], got {tuple(attn_mask.shape)}"
+            ) from None
+        attn_mask = attn_mask.to(q.dtype).contiguous()
+    out = torch.empty_like(q)
+    a = N.AttentionArgs(
+        q=N.ptr(q), k=N.ptr(k), v=N.ptr(v), out=N.ptr(out), attn_mask=N.ptr(attn_mask),
+        batch=B, num_q_heads=H, num_kv_heads=Hk, seq_q=S_q, seq_k=S_k, head_dim=D,
+        sm_scale=float(sm_scale), is_causal=int(bool(is_causal)), dtype=N.dtype_code(q),
+        workspace=None, workspace_bytes=0, stream=N.stream_handle(dev),
+    )
+    N.call("rfx_fused_attention", a, dev)
+    return out
+
+
+# ---------------------------------------------------------------------------- paged ----
+
+class PagedWorkspace:
+    """Caller-owned scratch of one paged-attention problem size (plan + split-K partials).
+
+    The native library never allocates; this object asks it for the size and keeps a
+    ``torch.uint8`` buffer. Reuse it across steps and layers of the same shape.
+    """
+
+    def __init__(self, device: torch.device):
+        self.device = torch.device(device)
+        self.buffer: Optional[torch.Tensor] = None
+
+    def ensure(self, nbytes: int) -> torch.Tensor:
+        if self.buffer is None or self.buffer.numel() < nbytes:
+            self.buffer = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        return self.buffer
+
+    def status(self) -> int:
+        """Device status word of the last launch (0 = clean). Synchronises the stream."""
+        import ctypes as C
+        if self.buffer is None:
+            return 0
+        word = C.c_int(0)
+        with torch.cuda.device(self.device):
+            st = N.lib().rfx_paged_attention_status(self.buffer.data_ptr(), N.stream_handle(self.device), C.byref(word))
+        if st not in (N.RFX_SUCCESS, N.RFX_TIMEOUT):
+            N.check(st)
+        return int(word.value)
+
+
+def _paged_args(q, out, k_cache, v_cache, block_table, context_lens, q_start, max_q_len, is_causal, sm_scale,
+                rope_cos, rope_sin, rope_positions, rope_interleaved, reuse_plan, force_generic, target_chunk, dev):
+    n_q, Hq, D = q.shape
+    nb, Hkv, bs, Dc = k_cache.shape
+    return N.PagedAttentionArgs(
+        q=N.ptr(q), out=N.ptr(out), k_cache=N.ptr(k_cache), v_cache=N.ptr(v_cache),
+        block_table=N.ptr(block_table), context_lens=N.ptr(context_lens), q_start=N.ptr(q_start),
+        rope_cos=N.ptr(rope_cos), rope_sin=N.ptr(rope_sin), rope_positions=N.ptr(rope_positions),
+        n_q=n_q, batch=context_lens.shape[0], num_q_heads=Hq, num_kv_heads=Hkv, head_dim=D,
+        num_blocks=nb, block_size=bs, max_blocks=block_table.shape[1], bt_stride_b=block_table.stride(0),
+        table_rows=0 if rope_cos is None else rope_cos.shape[0],
+        max_q_len=max_q_len,
+        sm_scale=float(sm_scale), is_causal=int(bool(is_causal)), rope_interleaved=int(bool(rope_interleaved)),
+        dtype=N.dtype_code(q), reuse_plan=int(bool(reuse_plan)), force_generic=int(bool(force_generic)),
+        target_chunk=int(target_chunk),
+        workspace=None, workspace_bytes=0, stream=N.stream_handle(dev),
+    )
+
+
+def paged_attention(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    context_lens: torch.Tensor,
+    *,
+    q_start: Optional[torch.Tensor] = None,
+    max_q_len: int = 1,
+    is_causal: bool = True,
+    sm_scale: Optional[float] = None,
+    rope_cos: Optional[torch.Tensor] = None,
+    rope_sin: Optional[torch.Tensor] = None,
+    rope_positions: Optional[torch.Tensor] = None,
+    rope_interleaved: bool = False,
+    workspace: Optional[PagedWorkspace] = None,
+    out: Optional[torch.Tensor] = None,
+    reuse_plan: bool = False,
+    force_generic: bool = False,
+    target_chunk: int = 0,
+) -> torch.Tensor:
+    """Attention of ragged query chunks over the paged pool.
+
+    ``q``: ``[N_q, H_q, D]``; request ``b`` owns rows ``q_start[b]:q_start[b+1]`` (one row per
+    request when ``q_start`` is None) and keys ``0..context_lens[b]-1``, which include the
+    request's new tokens (append first). With ``is_causal`` row ``i`` of ``n_b`` sees keys
+    ``0..context_lens[b]-n_b+i`` (bottom-right aligned). Equals, per request,
+    ``fused_attention(q_b, *kv_paged_lookup(..., max_ctx=context_lens[b]))`` with GQA
+    expansion. ``max_q_len`` is a host-side upper bound of any request's row count (sizes
+    the workspace). Pass ``rope_cos/rope_sin/rope_positions`` to rotate Q on load.
+    """
+    name = "paged_attention"
+    dev = N.require_cuda(name, q, k_cache, v_cache, block_table, context_lens, q_start, rope_cos, rope_sin,
+                         rope_positions, out)
+    if q.dim() != 3:
+        raise ValueError(f"{name}: q must be [N_q, H_q, D], got {tuple(q.shape)}")
+    if k_cache.dim() != 4 or v_cache.shape != k_cache.shape:
+        raise ValueError(f"{name}: caches must both be [num_blocks, H_kv, block_size, D]")
+    n_q, Hq, D = q.shape
+    nb, Hkv, bs, Dc = k_cache.shape
+    if Dc != D:
+        raise ValueError(f"{name}: head_dim of q ({D}) and cache ({Dc}) differ")
+    _resolve_head_repeat(Hq, Hkv)
+    if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise RuntimeError(f"{name}: q dtype {q.dtype} differs from the cache dtype {k_cache.dtype}")
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError(f"{name}: the caches must be contiguous")
+    q = q.contiguous()
+    if block_table.dtype != torch.int64:
+        block_table = block_table.to(torch.int64)
+    if block_table.dim() != 2 or block_table.stride(1) != 1:
+        block_table = block_table.contiguous()
+    if context_lens.dtype != torch.int32:
+        context_lens = context_lens.to(torch.int32)
+    context_lens = context_lens.contiguous()
+    B = context_lens.shape[0]
+    if block_table.shape[0] != B:
+        raise ValueError(f"{name}: block_table has {block_table.shape[0]} rows, context_lens {B}")
+    if q_start is not None:
+        if q_start.shape != (B + 1,):
+            raise ValueError(f"{name}: q_start must be [B+1]={B + 1}, got {tuple(q_start.shape)}")
+        q_start = q_start.to(torch.int32).contiguous()
+    elif n_q != B:
+        raise ValueError(f"{name}: without q_start q needs one row per request ({B}), got {n_q}")
+    if (rope_cos is None) != (rope_sin is None):
+        raise ValueError(f"{name}: rope_cos and rope_sin go together")
+    if rope_cos is not None:
+        if rope_positions is None or rope_positions.shape != (n_q,):
+            raise ValueError(f"{name}: rope_positions must be [N_q]={n_q}")
+        rope_positions = rope_positions.to(torch.int32).contiguous()
+        rope_cos = rope_cos.to(q.dtype).contiguous()
+        rope_sin = rope_sin.to(q.dtype).contiguous()
+        if rope_cos.dim() != 2 or rope_cos.shape[1] != D or rope_sin.shape != rope_cos.shape:
+            raise ValueError(f"{name}: rope tables must be [rows, {D}]")
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    if out is None:
+        out = torch.empty_like(q)
+    elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous():
+        raise ValueError(f"{name}: out must be a contiguous tensor shaped like q")
+    if workspace is None:
+        workspace = PagedWorkspace(dev)
+    a = _paged_args(q, out, k_cache, v_cache, block_table, context_lens, q_start, int(max_q_len), is_causal, sm_scale,
+                    rope_cos, rope_sin, rope_positions, rope_interleaved, reuse_plan, force_generic, target_chunk, dev)
+    import ctypes as C
+    need = N.lib().rfx_paged_attention_workspace_bytes(C.byref(a))
+    if need == 0 and n_q > 0:
+        N.check(N.RFX_INVALID_ARGUMENT)
+    buf = workspace.ensure(max(int(need), 256))
+    a.workspace = buf.data_ptr()
+    a.workspace_bytes = buf.numel()
+    N.call("rfx_paged_attention", a, dev)
+    return out
+
+
+def paged_decode(q, k_cache, v_cache, block_table, context_lens, **kw) -> torch.Tensor:
+    """One query row per request (``q``: ``[B, H_q, D]``): the decode case of ``paged_attention``."""
+    kw.pop("q_start", None)
+    kw.setdefault("max_q_len", 1)
+    return paged_attention(q, k_cache, v_cache, block_table, context_lens, q_start=None, **kw)
+
+
+def rope_append(
+    k_new: torch.Tensor,
+    v_new: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    slot_mapping: torch.Tensor,
+    positions: torch.Tensor,
+    cos: torch.Tensor,
+    sin: torch.Tensor,
+    *,
+    q: Optional[torch.Tensor] = None,
+    q_out: Optional[torch.Tensor] = None,
+    interleaved: bool = False,
+) -> Optional[torch.Tensor]:
+    """Rotate ``k_new`` with table rows ``positions`` and write it and ``v_new`` into the
+    pool at ``slot_mapping`` in one launch; with ``q`` also returns the rotated queries.
+
+    Pool contents equal ``kv_paged_append(apply_rope(k_new...), v_new, ...)`` of the
+    reference bit for bit (tables in the activation dtype).
+    """
+    name = "rope_append"
+    dev = N.require_cuda(name, k_new, v_new, k_cache, v_cache, slot_mapping, positions, cos, sin, q, q_out)
+    if k_new.dim() != 3 or v_new.shape != k_new.shape:
+        raise ValueError(f"{name}: k_new and v_new must both be [N, H_kv, D]")
+    n, Hkv, D = k_new.shape
+    if k_cache.dim() != 4 or v_cache.shape != k_cache.shape or k_cache.stride() != v_cache.stride():
+        raise ValueError(f"{name}: caches must both be [num_blocks, H_kv, block_size, D] with one stride pattern")
+    nb, ch, bs, cd = k_cache.shape
+    if (Hkv, D) != (ch, cd):
+        raise ValueError(f"{name}: input heads/head_dim {(Hkv, D)} do not match the cache {(ch, cd)}")
+    if k_cache.stride(3) != 1:
+        raise ValueError(f"{name}: the head_dim axis of the caches must be contiguous")
+    if D % 2 != 0:
+        raise ValueError("head_dim must be even for RoPE")
+    if k_new.dtype != k_cache.dtype or v_new.dtype != k_cache.dtype:
+        raise RuntimeError(f"{name}: input dtype {k_new.dtype} does not match cache dtype {k_cache.dtype}")
+    k_new, v_new = k_new.contiguous(), v_new.contiguous()
+    slot_mapping = slot_mapping.to(torch.int64).contiguous()
+    positions = positions.to(torch.int32).contiguous()
+    if slot_mapping.shape != (n,) or positions.shape != (n,):
+        raise ValueError(f"{name}: slot_mapping and positions must be [N]={n}")
+    cos = cos.to(k_new.dtype).contiguous()
+    sin = sin.to(k_new.dtype).contiguous()
+    if cos.dim() != 2 or cos.shape[1] != D or sin.shape != cos.shape:
+        raise ValueError(f"{name}: rope tables must be [rows, {D}]")
+    Hq = 0
+    if q is not None:
+        if q.dim() != 3 or q.shape[0] != n or q.shape[2] != D or q.dtype != k_new.dtype:
+            raise ValueError(f"{name}: q must be [N, H_q, D] in the activation dtype")
+        q = q.contiguous()
+        Hq = q.shape[1]
+        if q_out is None:
+            q_out = torch.empty_like(q)
+        elif q_out.shape != q.shape or q_out.dtype != q.dtype or not q_out.is_contiguous():
+            raise ValueError(f"{name}: q_out must be a contiguous tensor shaped like q")
+    a = N.RopeAppendArgs(
+        k_in=N.ptr(k_new), v_in=N.ptr(v_new), q_in=N.ptr(q), q_out=N.ptr(q_out if q is not None else None),
+        k_cache=N.ptr(k_cache), v_cache=N.ptr(v_cache), slot_mapping=N.ptr(slot_mapping), positions=N.ptr(positions),
+        cos=N.ptr(cos), sin=N.ptr(sin),
+        n_tokens=n, num_q_heads=Hq, num_kv_heads=Hkv, head_dim=D, num_blocks=nb, block_size=bs,
+        table_rows=cos.shape[0],
+        cache_stride_blk=k_cache.stride(0), cache_stride_h=k_cache.stride(1), cache_stride_pos=k_cache.stride(2),
+        interleaved=int(bool(interleaved)), dtype=N.dtype_code(k_new), stream=N.stream_handle(dev),
+    )
+    N.call("rfx_rope_append", a, dev)
+    return q_out if q is not None else None
+
+
+def paged_decode_step(
+    q_new: torch.Tensor,
+    k_new: torch.Tensor,
+    v_new: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    context_lens: torch.Tensor,
+    slot_mapping: torch.Tensor,
+    positions: torch.Tensor,
+    cos: torch.Tensor,
+    sin: torch.Tensor,
+    *,
+    sm_scale: Optional[float] = None,
+    interleaved: bool = False,
+    workspace: Optional[PagedWorkspace] = None,
+    out: Optional[torch.Tensor] = None,
+    **kw,
+) -> torch.Tensor:
+    """One decode step of one layer: append the new token's rotated K and its V to the
+    pool, then attend the rotated query over ``context_lens`` keys (which count the new
+    token). Three launches on top of the plan: RoPE+append, split-K partials with RoPE
+    fused into the Q load, combine."""
+    rope_append(k_new, v_new, k_cache, v_cache, slot_mapping, positions, cos, sin, interleaved=interleaved)
+    return paged_decode(q_new, k_cache, v_cache, block_table, context_lens, sm_scale=sm_scale,
+                        rope_cos=cos, rope_sin=sin, rope_positions=positions, rope_interleaved=interleaved,
+                        workspace=workspace, out=out, **kw)
+
+
+def splitk_combine(acc: torch.Tensor, m: torch.Tensor, l: torch.Tensor, split_begin: torch.Tensor,
+                   *, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Merge split-K partials: rows ``r`` own partials ``split_begin[r]:split_begin[r+1]``;
+    ``acc`` ``[P, D]`` fp32 un-normalised, ``m`` ``[P]`` maxima (natural-log domain), ``l`` ``[P]``
+    sums. Returns ``[rows, D]`` in ``dtype``. The running-max recurrence of the reference
+    (``kernels/softmax/triton_softmax.py:84-89``) applied across splits."""
+    dev = N.require_cuda("splitk_combine", acc, m, l, split_begin)
+    if acc.dim() != 2 or acc.dtype != torch.float32 or m.dtype != torch.float32 or l.dtype != torch.float32:
+        raise ValueError("splitk_combine: acc [P, D], m [P], l [P] must be float32")
+    acc, m, l = acc.contiguous(), m.contiguous(), l.contiguous()
+    split_begin = split_begin.to(torch.int32).contiguous()
+    rows = split_begin.shape[0] - 1
+    out = torch.empty((rows, acc.shape[1]), dtype=dtype, device=dev)
+    a = N.CombineArgs(acc=N.ptr(acc), m=N.ptr(m), l=N.ptr(l), split_begin=N.ptr(split_begin), out=N.ptr(out),
+                      rows=rows, head_dim=acc.shape[1], dtype=N.dtype_code(out), stream=N.stream_handle(dev))
+    N.call("rfx_splitk_combine", a, dev)
+    return out
+
+
+__all__ = [
+    "fused_attention",
+    "paged_attention",
+    "paged_decode",
+    "paged_decode_step",
+    "rope_append",
+    "splitk_combine",
+    "PagedWorkspace",
+]
