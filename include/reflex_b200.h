@@ -249,6 +249,11 @@ typedef struct {
 size_t rfx_paged_attention_workspace_bytes(const RfxPagedAttentionArgs* a);
 int rfx_paged_attention_plan(const RfxPagedAttentionArgs* a);
 int rfx_paged_attention(const RfxPagedAttentionArgs* a);
+/* The last two stages on their own, for callers that build their own launch sequence (a
+ * CUDA graph, per-kernel timing): the split-K partial kernel over an existing plan, and
+ * the combine that turns the partials into `out` and re-arms the plan for the next use. */
+int rfx_paged_attention_partials(const RfxPagedAttentionArgs* a);
+int rfx_paged_attention_combine(const RfxPagedAttentionArgs* a);
 
 /* Split-K combine on caller-provided partials (the recurrence of
  * kernels/softmax/triton_softmax.py:84-89 with an accumulator,

@@ -15,6 +15,8 @@
 //
 // Algorithmic bytes per item: 2 * keys * D * e (K and V). Arithmetic is G FLOP/byte, far
 // below what the warp MMA path sustains, so the kernel's roofline is HBM bandwidth.
+#include <stdlib.h>
+
 #include <type_traits>
 
 #include "paged_plan.cuh"
@@ -50,6 +52,7 @@ struct DecodeParams {
     float* pacc;
     int64_t num_blocks, max_blocks, bt_sb, table_rows;
     int Hq, Hkv, G, block_size, box_rows, rope_inter;
+    int map2d;         // 1: the maps are 2-D [rows, D] with {64, box_rows} boxes, one copy per 128-byte half
     float scale_log2;  // sm_scale * log2(e)
 };
 
@@ -184,7 +187,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int R = P.box_rows;                 // rows per TMA box = min(block_size, 64)
-    const int boxes = kTile / R;              // boxes per stage and per K/V
     const uint32_t box_bytes = (uint32_t)R * S::kRowBytes;
 
     if (threadIdx.x == 0) {
@@ -278,10 +280,18 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 __syncwarp();
                 if (lane < n_boxes && page_ok) {
                     const int row = (int)((my_page * P.Hkv + hkv) * P.block_size + my_row0);
-                    ptx::tma_load_3d(sK + (size_t)stage * S::kTileBytes + (size_t)lane * box_bytes, &kmap,
-                                     &full[stage], 0, row, 0);
-                    ptx::tma_load_3d(sV + (size_t)stage * S::kTileBytes + (size_t)lane * box_bytes, &vmap,
-                                     &full[stage], 0, row, 0);
+                    unsigned char* kd = sK + (size_t)stage * S::kTileBytes + (size_t)lane * box_bytes;
+                    unsigned char* vd = sV + (size_t)stage * S::kTileBytes + (size_t)lane * box_bytes;
+                    if (!P.map2d) {
+                        ptx::tma_load_3d(kd, &kmap, &full[stage], 0, row, 0);
+                        ptx::tma_load_3d(vd, &vmap, &full[stage], 0, row, 0);
+                    } else {
+#pragma unroll
+                        for (int hf = 0; hf < HD / 64; ++hf) {
+                            ptx::tma_load_2d(kd + (size_t)hf * R * 128, &kmap, &full[stage], hf * 64, row);
+                            ptx::tma_load_2d(vd + (size_t)hf * R * 128, &vmap, &full[stage], hf * 64, row);
+                        }
+                    }
                 }
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 // advance the block window once the next stage starts beyond it
@@ -525,6 +535,22 @@ int encode_rows_map_3d(CUtensorMap* map, const void* base, uint64_t rows, uint32
     return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+// Plain 2-D view [rows, row_elems] with a {64, box_rows} box (one 128-byte half per copy),
+// used when the driver refuses the 3-D view above.
+static int encode_rows_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint32_t row_elems,
+                              uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return -1;
+    const cuuint64_t dims[2] = {row_elems, rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)row_elems * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
 static bool box_rows_ok(int64_t bs) {
     if (bs >= 64) return bs % 64 == 0;
     return bs >= 8 && 64 % bs == 0;
@@ -569,9 +595,23 @@ int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const P
     const int R = (int)(a->block_size < 64 ? a->block_size : 64);
     CUtensorMap km, vm;
     const uint64_t rows = (uint64_t)(a->num_blocks * a->num_kv_heads * a->block_size);
-    int r1 = encode_rows_map_3d(&km, a->k_cache, rows, (uint32_t)HD, (uint32_t)R);
-    int r2 = encode_rows_map_3d(&vm, a->v_cache, rows, (uint32_t)HD, (uint32_t)R);
-    if (r1 || r2) return fail(RFX_CUDA_ERROR, "cuTensorMapEncodeTiled failed (%d, %d)", r1, r2);
+    static int force_2d = -1;  // REFLEX_B200_TMA2D=1 selects the 2-D maps (debugging aid)
+    if (force_2d < 0) {
+        const char* e = getenv("REFLEX_B200_TMA2D");
+        force_2d = (e && e[0] == '1') ? 1 : 0;
+    }
+    int map2d = force_2d;
+    int r1 = 0, r2 = 0;
+    if (!map2d) {
+        r1 = encode_rows_map_3d(&km, a->k_cache, rows, (uint32_t)HD, (uint32_t)R);
+        r2 = encode_rows_map_3d(&vm, a->v_cache, rows, (uint32_t)HD, (uint32_t)R);
+        if (r1 || r2) map2d = 1;
+    }
+    if (map2d) {
+        r1 = encode_rows_map_2d(&km, a->k_cache, rows, (uint32_t)HD, (uint32_t)R);
+        r2 = encode_rows_map_2d(&vm, a->v_cache, rows, (uint32_t)HD, (uint32_t)R);
+        if (r1 || r2) return fail(RFX_CUDA_ERROR, "cuTensorMapEncodeTiled failed (%d, %d)", r1, r2);
+    }
 
     DecodeParams P;
     P.q = a->q; P.block_table = a->block_table;
@@ -583,6 +623,7 @@ int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const P
     P.Hq = (int)a->num_q_heads; P.Hkv = (int)a->num_kv_heads; P.G = G;
     P.block_size = (int)a->block_size; P.box_rows = R; P.rope_inter = a->rope_interleaved;
     P.scale_log2 = a->sm_scale * 1.4426950408889634f;
+    P.map2d = map2d;
 
 #define RFX_DECODE_CASE(T)                                                                   \
     if (HD == 128) {                                                                         \

@@ -55,9 +55,10 @@ extern "C" int rfx_paged_attention_plan(const RfxPagedAttentionArgs* a) {
     return launch_plan(a, L, P, ctas);
 }
 
-extern "C" int rfx_paged_attention(const RfxPagedAttentionArgs* a) {
-    using namespace rfx;
-    const char* name = "rfx_paged_attention";
+namespace rfx {
+enum : int { kStagePlan = 1, kStagePartials = 2, kStageCombine = 4 };
+
+static int run_stages(const RfxPagedAttentionArgs* a, const char* name, int stages) {
     int st = validate(a, name);
     if (st != RFX_SUCCESS) return st;
     if (a->batch == 0 || a->n_q == 0) return RFX_SUCCESS;
@@ -71,13 +72,31 @@ extern "C" int rfx_paged_attention(const RfxPagedAttentionArgs* a) {
     RFX_REQUIRE(((uintptr_t)a->workspace % 256) == 0, "%s: workspace must be 256-byte aligned", name);
     const PlanPtrs P = plan_ptrs(a->workspace, L);
     const bool mma = decode_mma_supported(a);
-    if (!a->reuse_plan) {
+    if (stages & kStagePlan) {
         st = launch_plan(a, L, P, mma ? decode_mma_ctas(a) : sm_count() * 4);
         if (st != RFX_SUCCESS) return st;
     }
-    st = mma ? launch_decode_mma(a, L, P) : launch_paged_generic(a, L, P);
-    if (st != RFX_SUCCESS) return st;
-    return launch_paged_combine(a, L, P);
+    if (stages & kStagePartials) {
+        st = mma ? launch_decode_mma(a, L, P) : launch_paged_generic(a, L, P);
+        if (st != RFX_SUCCESS) return st;
+    }
+    if (stages & kStageCombine) return launch_paged_combine(a, L, P);
+    return RFX_SUCCESS;
+}
+}  // namespace rfx
+
+extern "C" int rfx_paged_attention(const RfxPagedAttentionArgs* a) {
+    using namespace rfx;
+    const int plan = (a && a->reuse_plan) ? 0 : kStagePlan;
+    return run_stages(a, "rfx_paged_attention", plan | kStagePartials | kStageCombine);
+}
+
+extern "C" int rfx_paged_attention_partials(const RfxPagedAttentionArgs* a) {
+    return rfx::run_stages(a, "rfx_paged_attention_partials", rfx::kStagePartials);
+}
+
+extern "C" int rfx_paged_attention_combine(const RfxPagedAttentionArgs* a) {
+    return rfx::run_stages(a, "rfx_paged_attention_combine", rfx::kStageCombine);
 }
 
 extern "C" int rfx_paged_attention_status(const void* workspace, rfx_stream stream, int* status_word_host) {

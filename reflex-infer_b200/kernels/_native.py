@@ -144,6 +144,8 @@ EXPORTS = {
     "rfx_paged_attention_workspace_bytes": (C.c_size_t, [C.POINTER(PagedAttentionArgs)]),
     "rfx_paged_attention_plan": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_paged_attention": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
+    "rfx_paged_attention_partials": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
+    "rfx_paged_attention_combine": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_splitk_combine": (C.c_int, [C.POINTER(CombineArgs)]),
     "rfx_paged_attention_status": (C.c_int, [vp, vp, C.POINTER(C.c_int)]),
 }
