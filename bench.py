@@ -1,0 +1,499 @@
+#!/usr/bin/env python
+"""Benchmark of the paged-KV decode step on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg4|cfg2]
+                    [--impl ours|reference] [--shard request|replica|head]
+
+One "step" is one decode step of one layer over one synthetic batch of the named
+configuration: fused RoPE + append of the new token's K/V, split-K plan, paged GQA
+attention partials (the HBM-bound kernel), combine. Rank 0 prints ONE JSON line.
+
+  value      decode tokens/s of the whole job, inputs already in HBM, timed with CUDA
+             events per step, max over ranks;
+  e2e        the same step driven from pinned HOST buffers: H2D of q/k/v/slots/positions,
+             the kernels, D2H of the output, all inside the timed region;
+  roofline   algorithmic K+V bytes of the batch / mean duration of the partial kernel
+             (events around that launch inside the timed steps) vs the measured HBM peak;
+  cpu_baseline  the CPU oracle (a port of the reference's torch path) timed on this box's
+             host cores on a bounded sample of the same workload (rank 0, N=1 only).
+
+``--impl reference`` times that CPU port alone, on the same configuration, and prints the
+same line with ``"impl": "reference"``.
+
+Multi-GPU: one process per GPU (torchrun). ``--shard replica`` (default, weak scaling):
+every rank decodes its own batch of the configuration, no collective. ``--shard request``
+(strong): the one batch is split by request across ranks with a greedy balance on context
+length, no collective. ``--shard head`` (strong): ranks own kv-head slices of the pool and
+one NCCL all-gather assembles the output heads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for p in (ROOT / "reflex-infer_b200", ROOT):
+    if str(p) not in sys.path:
+        sys.path.insert(0, str(p))
+
+import torch  # noqa: E402
+
+METRIC = "paged_decode_attn_tokens_per_s"
+UNIT = "tokens/s"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg4", choices=["cfg4", "cfg2"])
+    ap.add_argument("--shard", default="replica", choices=["replica", "request", "head"])
+    ap.add_argument("--cpu-sample", type=int, default=0, help="requests in the CPU-baseline sample (0 = auto)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary configuration block")
+    ap.add_argument("--chunk", type=int, default=0, help="keys per split (0 = planner's choice)")
+    ap.add_argument("--requests", type=int, default=0,
+                    help="profiling aid: shrink the batch to this many requests (0 = the configuration's own)")
+    return ap.parse_args()
+
+
+def workload_desc(name: str) -> dict:
+    if name == "cfg4":
+        return {"workload": "cfg4: bf16 paged GQA decode, 256 requests, ctx U[8192,32768], 64q/8kv heads, D=128, "
+                            "page 32, permuted pages, theta 1e6, 1 new token per request",
+                "batch": 256, "q_heads": 64, "kv_heads": 8, "head_dim": 128, "page_size": 32}
+    return {"workload": "cfg2: bf16 paged GQA decode, 32 requests, ctx U[512,8192], 16q/2kv heads, D=128, "
+                        "page 16, permuted 32768-page pool, theta 1e6, 1 new token per request",
+            "batch": 32, "q_heads": 16, "kv_heads": 2, "head_dim": 128, "page_size": 16}
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+# ---- clocks -----------------------------------------------------------------------------
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.lines = []
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---- CPU legs (oracle: the only place besides tests that may import it) -------------------
+
+def cpu_decode_time(batch, as_written: bool = False) -> float:
+    """One decode step of `batch` (CPU tensors) through the oracle; seconds."""
+    import oracle
+    t0 = time.perf_counter()
+    pos = batch.positions.long()
+    q_rot = oracle.apply_rope(batch.q_new.unsqueeze(0), batch.cos[pos], batch.sin[pos])[0]
+    k_rot = oracle.apply_rope(batch.k_new.unsqueeze(0), batch.cos[pos], batch.sin[pos])[0]
+    oracle.kv_paged_append(k_rot, batch.v_new, batch.k_cache, batch.v_cache, batch.slot_mapping)
+    out = oracle.paged_attention_composed(q_rot, batch.k_cache, batch.v_cache, batch.block_table, batch.context_lens,
+                                          as_written=as_written)
+    dt = time.perf_counter() - t0
+    cpu_decode_time.last_out = out
+    return dt
+
+
+def make_cpu_batch(workload: str, n_req: int, seed: int):
+    import oracle
+    import workloads
+    if workload == "cfg4":
+        cos, sin = oracle.build_rope_tables(32770, 128, base=1e6, dtype=torch.bfloat16)
+        return workloads.cfg4(device="cpu", seed=seed, B=n_req, tables=(cos, sin))
+    cos, sin = oracle.build_rope_tables(8194, 128, base=1e6, dtype=torch.bfloat16)
+    b = workloads.make_paged_batch("cfg2", B=n_req, Hq=16, Hkv=2, D=128, block_size=16, ctx_range=(512, 8192),
+                                   theta=1e6, device="cpu", seed=seed, tables=(cos, sin))
+    return b
+
+
+def cpu_baseline(workload: str, sample: int, budget_s: float = 20.0) -> dict:
+    torch.set_num_threads(os.cpu_count() or 1)
+    cores = torch.get_num_threads()
+    n = sample or 2
+    batch = make_cpu_batch(workload, n, seed=100)
+    t = cpu_decode_time(batch)  # warm-up, also sizes the sample
+    if not sample:
+        n = max(2, min(64, int(budget_s / max(t / n, 1e-3) / 3)))
+        batch = make_cpu_batch(workload, n, seed=101)
+        cpu_decode_time(batch)
+    times = [cpu_decode_time(batch) for _ in range(2)]
+    best = min(times)
+    small = make_cpu_batch(workload, 2, seed=102)
+    t_written = cpu_decode_time(small, as_written=True)
+    return {"value": n / best, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{n} requests of {workload} drawn from the same generator, one decode step, best of 2 after "
+                      f"warm-up; oracle composition (vectorised page gather + torch CPU SDPA)",
+            "as_written_value": 2 / t_written,
+            "as_written_note": "same composition with the reference's per-token Python lookup loop, 2 requests",
+            "torch": torch.__version__}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    cores = torch.get_num_threads()
+    n = args.cpu_sample or 2
+    batch = make_cpu_batch(args.workload, n, seed=100)
+    t = cpu_decode_time(batch)
+    if not args.cpu_sample:
+        # size the per-step sample so that steps+warmup end within about two minutes
+        per_req = t / n
+        n = max(1, min(64, int(120.0 / max(args.steps + args.warmup, 1) / max(per_req, 1e-3))))
+        batch = make_cpu_batch(args.workload, n, seed=101)
+    for _ in range(args.warmup):
+        cpu_decode_time(batch)
+    times = [cpu_decode_time(batch) for _ in range(args.steps)]
+    total = sum(times)
+    value = n * args.steps / total
+    sample = (f"{n} requests of {args.workload} per step (same generator and distributions), CPU oracle port of the "
+              f"reference torch path: rope -> append -> per-request gather -> GQA expansion -> SDPA")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_desc(args.workload),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                         "torch": torch.__version__},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---- GPU legs -----------------------------------------------------------------------------
+
+class DecodeStep:
+    """Prepared launches of one decode step over fixed device buffers."""
+
+    def __init__(self, batch, chunk: int = 0):
+        from kernels.attention import PagedAttentionCall, PagedWorkspace, RopeAppendCall
+        self.b = batch
+        dev = batch.q_new.device
+        self.ws = PagedWorkspace(dev)
+        self.append = RopeAppendCall(batch.k_new, batch.v_new, batch.k_cache, batch.v_cache, batch.slot_mapping,
+                                     batch.positions, batch.cos, batch.sin)
+        self.attn = PagedAttentionCall(batch.q_new, batch.k_cache, batch.v_cache, batch.block_table,
+                                       batch.context_lens, rope_cos=batch.cos, rope_sin=batch.sin,
+                                       rope_positions=batch.positions, workspace=self.ws, target_chunk=chunk)
+        self.out = self.attn.out
+        self.kernel_launches = 4
+
+    def run(self, ev0=None, ev1=None):
+        self.append.run()
+        self.attn.plan()
+        if ev0 is not None:
+            ev0.record()
+        self.attn.partials()
+        if ev1 is not None:
+            ev1.record()
+        self.attn.combine()
+        return self.out
+
+
+class HostDrivenStep:
+    """The same step fed from pinned host buffers, result read back to pinned host memory."""
+
+    def __init__(self, step: DecodeStep):
+        b = step.b
+        self.step = step
+        self.dev = [b.q_new, b.k_new, b.v_new, b.slot_mapping, b.positions]
+        self.host = [t.cpu().pin_memory() for t in self.dev]
+        self.out_host = torch.empty(step.out.shape, dtype=step.out.dtype).pin_memory()
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host)
+        self.d2h = self.out_host.numel() * self.out_host.element_size()
+
+    def run(self):
+        for d, h in zip(self.dev, self.host):
+            d.copy_(h, non_blocking=True)
+        out = self.step.run()
+        self.out_host.copy_(out, non_blocking=True)
+
+
+def timed_steps(fn, steps, warmup, flush=None, dist=None, with_kernel_events=False):
+    """W warm-up steps, then K steps each bracketed by its own CUDA event pair (an untimed L2
+    flush in between when `flush` is given); barrier + synchronize on both sides. Returns
+    (total_ms, [per-kernel ms] or None)."""
+    for _ in range(warmup):
+        if flush is not None:
+            flush()
+        fn(None, None) if with_kernel_events else fn()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    se = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ee = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    k0 = [torch.cuda.Event(enable_timing=True) for _ in range(steps)] if with_kernel_events else None
+    k1 = [torch.cuda.Event(enable_timing=True) for _ in range(steps)] if with_kernel_events else None
+    for i in range(steps):
+        if flush is not None:
+            flush()
+        se[i].record()
+        if with_kernel_events:
+            fn(k0[i], k1[i])
+        else:
+            fn()
+        ee[i].record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    total = sum(s.elapsed_time(e) for s, e in zip(se, ee))
+    kern = [a.elapsed_time(b) for a, b in zip(k0, k1)] if with_kernel_events else None
+    return total, kern
+
+
+def build_batch(workload, device, seed, shard, rank, world, requests=0):
+    import workloads
+    if workload == "cfg4":
+        b = workloads.cfg4(device=device, seed=seed, B=requests or None)
+    elif requests:
+        b = workloads.make_paged_batch("cfg2", B=requests, Hq=16, Hkv=2, D=128, block_size=16, ctx_range=(512, 8192),
+                                       num_blocks=32768, theta=1e6, device=device, seed=seed)
+    else:
+        b = workloads.cfg2(device=device, seed=seed)
+    if world > 1 and shard == "request":
+        from sharding import shard_batch_by_request
+        b = shard_batch_by_request(b, rank, world)
+    elif world > 1 and shard == "head":
+        from sharding import shard_batch_by_kv_head
+        b = shard_batch_by_kv_head(b, rank, world)
+    return b
+
+
+def measure(workload, args, device, rank, world, dist, want_e2e=True):
+    seed_base = {"cfg4": 3, "cfg2": 1}[workload]
+    # replica: every rank draws its own batch; request/head: all ranks draw the same one, then cut it
+    seed = seed_base + (1000 * rank if args.shard == "replica" else 0)
+    batch = build_batch(workload, device, seed, args.shard, rank, world, args.requests if workload == args.workload else 0)
+    step = DecodeStep(batch, chunk=args.chunk)
+    kv_bytes = batch.kv_bytes()
+    tokens = batch.n_tokens
+    flush = None
+    flush_note = "K+V read per step exceeds L2 (126 MB) many times over; no flush"
+    if kv_bytes < 4 * 126e6:
+        scratch = torch.empty(512 << 20, dtype=torch.uint8, device=device)
+        flush = lambda: scratch.zero_()  # noqa: E731
+        flush_note = "512 MiB memset between timed steps flushes L2 (outside the timed events)"
+
+    gather = None
+    if world > 1 and args.shard == "head":
+        from sharding import HeadGather
+        gather = HeadGather(step.out, dist)
+
+    def run(ev0=None, ev1=None):
+        out = step.run(ev0, ev1)
+        if gather is not None:
+            gather.run(out)
+
+    total_ms, kern_ms = timed_steps(run, args.steps, args.warmup, flush, dist, with_kernel_events=True)
+    status = step.ws.status()
+    res = {"tokens": tokens, "kv_bytes": kv_bytes, "total_ms": total_ms, "kernel_ms": statistics.mean(kern_ms),
+           "kernel_ms_min": min(kern_ms), "status": status, "flush": flush_note, "kernel_kind": step.attn.kernel_kind,
+           "launches": step.kernel_launches * args.steps}
+    if want_e2e:
+        host = HostDrivenStep(step)
+        e2e_ms, _ = timed_steps(host.run, args.steps, args.warmup, flush, dist)
+        res.update(e2e_ms=e2e_ms, h2d=host.h2d, d2h=host.d2h)
+    res["batch"] = batch
+    res["step"] = step
+    return res
+
+
+def check_against_oracle(res, n_req=2):
+    """Cheap sanity outside every timed region: first requests of the batch vs the CPU oracle."""
+    import oracle
+    b = res["batch"]
+    out = res["step"].run()
+    torch.cuda.synchronize()
+    n = min(n_req, b.B)
+    errs = []
+    for r in range(n):
+        ctx = int(b.context_lens[r])
+        npg = (ctx + b.block_size - 1) // b.block_size
+        pages = b.block_table[r, :npg]
+        kc, vc = b.k_cache[pages].cpu(), b.v_cache[pages].cpu()
+        bt = torch.arange(npg).view(1, -1)
+        pos = b.positions[r:r + 1].cpu().long()
+        cos, sin = b.cos.cpu(), b.sin.cpu()
+        q_rot = oracle.apply_rope(b.q_new[r:r + 1].cpu().unsqueeze(0), cos[pos], sin[pos])[0]
+        ref = oracle.paged_attention_composed(q_rot, kc, vc, bt, torch.tensor([ctx], dtype=torch.int32))
+        errs.append((out[r].cpu().float() - ref[0].float()).abs().max().item())
+    return max(errs) if errs else 0.0
+
+
+def run_ours(args):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus > 1 and world == 1:
+        # convenience: relaunch under torchrun
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29531", __file__] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
+    from kernels import _native
+    _native.lib()  # no fallback: fail here if the CUDA library is missing
+    assert torch.cuda.is_available(), "bench.py needs a GPU for --impl ours"
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=device)
+        dist = dist_mod
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    res = measure(args.workload, args, device, rank, world, dist)
+    clocks = sampler.stop() if sampler else None
+
+    # whole-job numbers: tokens of all ranks over the slowest rank's time
+    t = torch.tensor([res["total_ms"], res["e2e_ms"], res["kernel_ms"]], dtype=torch.float64, device=device)
+    toks = torch.tensor([float(res["tokens"]), float(res["kv_bytes"])], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(toks, op=dist.ReduceOp.SUM)
+    total_ms, e2e_ms, kernel_ms = t.tolist()
+    all_tokens, all_bytes = toks.tolist()
+    if args.shard == "head" and world > 1:
+        all_tokens = float(res["tokens"])  # every rank works on all requests; count them once
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peak()
+    achieved = res["kv_bytes"] / (res["kernel_ms"] * 1e-3) / 1e9  # this rank's kernel, GB/s
+    line = {
+        "metric": METRIC,
+        "value": all_tokens * args.steps / (total_ms * 1e-3),
+        "unit": UNIT,
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": total_ms / args.steps,
+        "higher_is_better": True,
+        "scaling": "weak" if args.shard == "replica" else "strong",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": {**workload_desc(args.workload), "shard": args.shard, "l2": res["flush"],
+                   **({"requests_override": args.requests} if args.requests else {}),
+                   "timing": "CUDA events per step on the launch stream, max over ranks"},
+        "e2e": {"value": all_tokens * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"],
+                "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": res["launches"],
+        "roofline": {"bound": "hbm", "kernel": "decode_mma_kernel" if res["kernel_kind"] == 1 else "paged_partial_generic_kernel",
+                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
+                     "algorithmic_bytes_per_launch": res["kv_bytes"], "kernel_ms": res["kernel_ms"],
+                     "kernel_ms_min": res["kernel_ms_min"], "traffic": None},
+        "clocks": clocks,
+        "device_status_word": res["status"],
+    }
+    traffic = ROOT / "profiles" / "traffic.json"
+    if traffic.exists():
+        try:
+            tr = json.loads(traffic.read_text()).get(args.workload)
+            if tr:
+                line["roofline"]["traffic"] = tr["dram_bytes_per_algorithmic_byte"] * res["kv_bytes"]
+                line["roofline"]["traffic_note"] = tr.get("note")
+        except Exception:
+            pass
+    line["max_abs_err_vs_oracle"] = check_against_oracle(res)
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(args.workload, args.cpu_sample)
+    if world == 1 and not args.no_extra:
+        other = "cfg2" if args.workload == "cfg4" else "cfg4"
+        del res
+        torch.cuda.empty_cache()
+        r2 = measure(other, args, device, rank, world, dist)
+        ach2 = r2["kv_bytes"] / (r2["kernel_ms"] * 1e-3) / 1e9
+        line["other_workloads"] = {other: {
+            "config": workload_desc(other)["workload"], "value": r2["tokens"] * args.steps / (r2["total_ms"] * 1e-3),
+            "unit": UNIT, "ms_per_step": r2["total_ms"] / args.steps, "e2e_ms_per_step": r2["e2e_ms"] / args.steps,
+            "roofline_achieved_gbs": ach2, "roofline_frac": ach2 / peak, "kernel_ms": r2["kernel_ms"],
+            "l2": r2["flush"]}}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

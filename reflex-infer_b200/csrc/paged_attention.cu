@@ -95,6 +95,11 @@ extern "C" int rfx_paged_attention_partials(const RfxPagedAttentionArgs* a) {
     return rfx::run_stages(a, "rfx_paged_attention_partials", rfx::kStagePartials);
 }
 
+extern "C" int rfx_paged_attention_kernel_kind(const RfxPagedAttentionArgs* a) {
+    if (rfx::validate(a, "rfx_paged_attention_kernel_kind") != RFX_SUCCESS) return -1;
+    return rfx::decode_mma_supported(a) ? 1 : 0;
+}
+
 extern "C" int rfx_paged_attention_combine(const RfxPagedAttentionArgs* a) {
     return rfx::run_stages(a, "rfx_paged_attention_combine", rfx::kStageCombine);
 }

@@ -146,6 +146,7 @@ EXPORTS = {
     "rfx_paged_attention": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_paged_attention_partials": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_paged_attention_combine": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
+    "rfx_paged_attention_kernel_kind": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_splitk_combine": (C.c_int, [C.POINTER(CombineArgs)]),
     "rfx_paged_attention_status": (C.c_int, [vp, vp, C.POINTER(C.c_int)]),
 }

@@ -122,23 +122,118 @@ class PagedWorkspace:
         return int(word.value)
 
 
-def _paged_args(q, out, k_cache, v_cache, block_table, context_lens, q_start, max_q_len, is_causal, sm_scale,
-                rope_cos, rope_sin, rope_positions, rope_interleaved, reuse_plan, force_generic, target_chunk, dev):
-    n_q, Hq, D = q.shape
-    nb, Hkv, bs, Dc = k_cache.shape
-    return N.PagedAttentionArgs(
-        q=N.ptr(q), out=N.ptr(out), k_cache=N.ptr(k_cache), v_cache=N.ptr(v_cache),
-        block_table=N.ptr(block_table), context_lens=N.ptr(context_lens), q_start=N.ptr(q_start),
-        rope_cos=N.ptr(rope_cos), rope_sin=N.ptr(rope_sin), rope_positions=N.ptr(rope_positions),
-        n_q=n_q, batch=context_lens.shape[0], num_q_heads=Hq, num_kv_heads=Hkv, head_dim=D,
-        num_blocks=nb, block_size=bs, max_blocks=block_table.shape[1], bt_stride_b=block_table.stride(0),
-        table_rows=0 if rope_cos is None else rope_cos.shape[0],
-        max_q_len=max_q_len,
-        sm_scale=float(sm_scale), is_causal=int(bool(is_causal)), rope_interleaved=int(bool(rope_interleaved)),
-        dtype=N.dtype_code(q), reuse_plan=int(bool(reuse_plan)), force_generic=int(bool(force_generic)),
-        target_chunk=int(target_chunk),
-        workspace=None, workspace_bytes=0, stream=N.stream_handle(dev),
-    )
+class PagedAttentionCall:
+    """A validated, ready-to-launch paged attention over fixed buffers.
+
+    Construction does all argument checking, dtype/stride normalisation and workspace
+    sizing once; ``run()`` (plan + partials + combine) and the single stages then cost one
+    foreign call each, which is what a serving loop that reuses its buffers every step
+    wants. The tensors are referenced, not copied: refill them in place between calls.
+    """
+
+    def __init__(self, q, k_cache, v_cache, block_table, context_lens, *, q_start=None, max_q_len=1,
+                 is_causal=True, sm_scale=None, rope_cos=None, rope_sin=None, rope_positions=None,
+                 rope_interleaved=False, workspace=None, out=None, force_generic=False, target_chunk=0):
+        import ctypes as C
+        name = "paged_attention"
+        dev = N.require_cuda(name, q, k_cache, v_cache, block_table, context_lens, q_start, rope_cos, rope_sin,
+                             rope_positions, out)
+        if q.dim() != 3:
+            raise ValueError(f"{name}: q must be [N_q, H_q, D], got {tuple(q.shape)}")
+        if k_cache.dim() != 4 or v_cache.shape != k_cache.shape:
+            raise ValueError(f"{name}: caches must both be [num_blocks, H_kv, block_size, D]")
+        n_q, Hq, D = q.shape
+        nb, Hkv, bs, Dc = k_cache.shape
+        if Dc != D:
+            raise ValueError(f"{name}: head_dim of q ({D}) and cache ({Dc}) differ")
+        _resolve_head_repeat(Hq, Hkv)
+        if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+            raise RuntimeError(f"{name}: q dtype {q.dtype} differs from the cache dtype {k_cache.dtype}")
+        if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+            raise ValueError(f"{name}: the caches must be contiguous")
+        q = q.contiguous()
+        if block_table.dtype != torch.int64:
+            block_table = block_table.to(torch.int64)
+        if block_table.dim() != 2 or block_table.stride(1) != 1:
+            block_table = block_table.contiguous()
+        if context_lens.dtype != torch.int32:
+            context_lens = context_lens.to(torch.int32)
+        context_lens = context_lens.contiguous()
+        B = context_lens.shape[0]
+        if block_table.shape[0] != B:
+            raise ValueError(f"{name}: block_table has {block_table.shape[0]} rows, context_lens {B}")
+        if q_start is not None:
+            if q_start.shape != (B + 1,):
+                raise ValueError(f"{name}: q_start must be [B+1]={B + 1}, got {tuple(q_start.shape)}")
+            q_start = q_start.to(torch.int32).contiguous()
+        elif n_q != B:
+            raise ValueError(f"{name}: without q_start q needs one row per request ({B}), got {n_q}")
+        if (rope_cos is None) != (rope_sin is None):
+            raise ValueError(f"{name}: rope_cos and rope_sin go together")
+        if rope_cos is not None:
+            if rope_positions is None or rope_positions.shape != (n_q,):
+                raise ValueError(f"{name}: rope_positions must be [N_q]={n_q}")
+            rope_positions = rope_positions.to(torch.int32).contiguous()
+            rope_cos = rope_cos.to(q.dtype).contiguous()
+            rope_sin = rope_sin.to(q.dtype).contiguous()
+            if rope_cos.dim() != 2 or rope_cos.shape[1] != D or rope_sin.shape != rope_cos.shape:
+                raise ValueError(f"{name}: rope tables must be [rows, {D}]")
+        if sm_scale is None:
+            sm_scale = 1.0 / math.sqrt(D)
+        if out is None:
+            out = torch.empty_like(q)
+        elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous():
+            raise ValueError(f"{name}: out must be a contiguous tensor shaped like q")
+        if workspace is None:
+            workspace = PagedWorkspace(dev)
+        a = N.PagedAttentionArgs(
+            q=N.ptr(q), out=N.ptr(out), k_cache=N.ptr(k_cache), v_cache=N.ptr(v_cache),
+            block_table=N.ptr(block_table), context_lens=N.ptr(context_lens), q_start=N.ptr(q_start),
+            rope_cos=N.ptr(rope_cos), rope_sin=N.ptr(rope_sin), rope_positions=N.ptr(rope_positions),
+            n_q=n_q, batch=B, num_q_heads=Hq, num_kv_heads=Hkv, head_dim=D,
+            num_blocks=nb, block_size=bs, max_blocks=block_table.shape[1], bt_stride_b=block_table.stride(0),
+            table_rows=0 if rope_cos is None else rope_cos.shape[0],
+            max_q_len=int(max_q_len),
+            sm_scale=float(sm_scale), is_causal=int(bool(is_causal)), rope_interleaved=int(bool(rope_interleaved)),
+            dtype=N.dtype_code(q), reuse_plan=0, force_generic=int(bool(force_generic)),
+            target_chunk=int(target_chunk), workspace=None, workspace_bytes=0, stream=None,
+        )
+        lib = N.lib()
+        need = lib.rfx_paged_attention_workspace_bytes(C.byref(a))
+        if need == 0 and n_q > 0:
+            N.check(N.RFX_INVALID_ARGUMENT)
+        buf = workspace.ensure(max(int(need), 256))
+        a.workspace = buf.data_ptr()
+        a.workspace_bytes = buf.numel()
+        self.kernel_kind = int(lib.rfx_paged_attention_kernel_kind(C.byref(a)))  # 1 TMA/MMA, 0 scalar
+        self.out = out
+        self.workspace = workspace
+        self.device = dev
+        self._args = a
+        self._ref = C.byref(a)
+        self._lib = lib
+        self._keep = (q, k_cache, v_cache, block_table, context_lens, q_start, rope_cos, rope_sin, rope_positions, buf)
+
+    def _call(self, fn):
+        self._args.stream = N.stream_handle(self.device)
+        with torch.cuda.device(self.device):
+            N.check(fn(self._ref))
+
+    def run(self, reuse_plan: bool = False) -> torch.Tensor:
+        """plan (unless ``reuse_plan``) + split-K partials + combine."""
+        self._args.reuse_plan = int(bool(reuse_plan))
+        self._call(self._lib.rfx_paged_attention)
+        return self.out
+
+    def plan(self) -> None:
+        self._call(self._lib.rfx_paged_attention_plan)
+
+    def partials(self) -> None:
+        self._call(self._lib.rfx_paged_attention_partials)
+
+    def combine(self) -> torch.Tensor:
+        self._call(self._lib.rfx_paged_attention_combine)
+        return self.out
 
 
 def paged_attention(
@@ -172,68 +267,11 @@ def paged_attention(
     expansion. ``max_q_len`` is a host-side upper bound of any request's row count (sizes
     the workspace). Pass ``rope_cos/rope_sin/rope_positions`` to rotate Q on load.
     """
-    name = "paged_attention"
-    dev = N.require_cuda(name, q, k_cache, v_cache, block_table, context_lens, q_start, rope_cos, rope_sin,
-                         rope_positions, out)
-    if q.dim() != 3:
-        raise ValueError(f"{name}: q must be [N_q, H_q, D], got {tuple(q.shape)}")
-    if k_cache.dim() != 4 or v_cache.shape != k_cache.shape:
-        raise ValueError(f"{name}: caches must both be [num_blocks, H_kv, block_size, D]")
-    n_q, Hq, D = q.shape
-    nb, Hkv, bs, Dc = k_cache.shape
-    if Dc != D:
-        raise ValueError(f"{name}: head_dim of q ({D}) and cache ({Dc}) differ")
-    _resolve_head_repeat(Hq, Hkv)
-    if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
-        raise RuntimeError(f"{name}: q dtype {q.dtype} differs from the cache dtype {k_cache.dtype}")
-    if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
-        raise ValueError(f"{name}: the caches must be contiguous")
-    q = q.contiguous()
-    if block_table.dtype != torch.int64:
-        block_table = block_table.to(torch.int64)
-    if block_table.dim() != 2 or block_table.stride(1) != 1:
-        block_table = block_table.contiguous()
-    if context_lens.dtype != torch.int32:
-        context_lens = context_lens.to(torch.int32)
-    context_lens = context_lens.contiguous()
-    B = context_lens.shape[0]
-    if block_table.shape[0] != B:
-        raise ValueError(f"{name}: block_table has {block_table.shape[0]} rows, context_lens {B}")
-    if q_start is not None:
-        if q_start.shape != (B + 1,):
-            raise ValueError(f"{name}: q_start must be [B+1]={B + 1}, got {tuple(q_start.shape)}")
-        q_start = q_start.to(torch.int32).contiguous()
-    elif n_q != B:
-        raise ValueError(f"{name}: without q_start q needs one row per request ({B}), got {n_q}")
-    if (rope_cos is None) != (rope_sin is None):
-        raise ValueError(f"{name}: rope_cos and rope_sin go together")
-    if rope_cos is not None:
-        if rope_positions is None or rope_positions.shape != (n_q,):
-            raise ValueError(f"{name}: rope_positions must be [N_q]={n_q}")
-        rope_positions = rope_positions.to(torch.int32).contiguous()
-        rope_cos = rope_cos.to(q.dtype).contiguous()
-        rope_sin = rope_sin.to(q.dtype).contiguous()
-        if rope_cos.dim() != 2 or rope_cos.shape[1] != D or rope_sin.shape != rope_cos.shape:
-            raise ValueError(f"{name}: rope tables must be [rows, {D}]")
-    if sm_scale is None:
-        sm_scale = 1.0 / math.sqrt(D)
-    if out is None:
-        out = torch.empty_like(q)
-    elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous():
-        raise ValueError(f"{name}: out must be a contiguous tensor shaped like q")
-    if workspace is None:
-        workspace = PagedWorkspace(dev)
-    a = _paged_args(q, out, k_cache, v_cache, block_table, context_lens, q_start, int(max_q_len), is_causal, sm_scale,
-                    rope_cos, rope_sin, rope_positions, rope_interleaved, reuse_plan, force_generic, target_chunk, dev)
-    import ctypes as C
-    need = N.lib().rfx_paged_attention_workspace_bytes(C.byref(a))
-    if need == 0 and n_q > 0:
-        N.check(N.RFX_INVALID_ARGUMENT)
-    buf = workspace.ensure(max(int(need), 256))
-    a.workspace = buf.data_ptr()
-    a.workspace_bytes = buf.numel()
-    N.call("rfx_paged_attention", a, dev)
-    return out
+    call = PagedAttentionCall(q, k_cache, v_cache, block_table, context_lens, q_start=q_start, max_q_len=max_q_len,
+                              is_causal=is_causal, sm_scale=sm_scale, rope_cos=rope_cos, rope_sin=rope_sin,
+                              rope_positions=rope_positions, rope_interleaved=rope_interleaved, workspace=workspace,
+                              out=out, force_generic=force_generic, target_chunk=target_chunk)
+    return call.run(reuse_plan=reuse_plan)
 
 
 def paged_decode(q, k_cache, v_cache, block_table, context_lens, **kw) -> torch.Tensor:
@@ -241,6 +279,71 @@ def paged_decode(q, k_cache, v_cache, block_table, context_lens, **kw) -> torch.
     kw.pop("q_start", None)
     kw.setdefault("max_q_len", 1)
     return paged_attention(q, k_cache, v_cache, block_table, context_lens, q_start=None, **kw)
+
+
+class RopeAppendCall:
+    """A validated, ready-to-launch fused RoPE + append over fixed buffers (see ``rope_append``)."""
+
+    def __init__(self, k_new, v_new, k_cache, v_cache, slot_mapping, positions, cos, sin, *, q=None, q_out=None,
+                 interleaved=False):
+        import ctypes as C
+        name = "rope_append"
+        dev = N.require_cuda(name, k_new, v_new, k_cache, v_cache, slot_mapping, positions, cos, sin, q, q_out)
+        if k_new.dim() != 3 or v_new.shape != k_new.shape:
+            raise ValueError(f"{name}: k_new and v_new must both be [N, H_kv, D]")
+        n, Hkv, D = k_new.shape
+        if k_cache.dim() != 4 or v_cache.shape != k_cache.shape or k_cache.stride() != v_cache.stride():
+            raise ValueError(f"{name}: caches must both be [num_blocks, H_kv, block_size, D] with one stride pattern")
+        nb, ch, bs, cd = k_cache.shape
+        if (Hkv, D) != (ch, cd):
+            raise ValueError(f"{name}: input heads/head_dim {(Hkv, D)} do not match the cache {(ch, cd)}")
+        if k_cache.stride(3) != 1:
+            raise ValueError(f"{name}: the head_dim axis of the caches must be contiguous")
+        if D % 2 != 0:
+            raise ValueError("head_dim must be even for RoPE")
+        if k_new.dtype != k_cache.dtype or v_new.dtype != k_cache.dtype:
+            raise RuntimeError(f"{name}: input dtype {k_new.dtype} does not match cache dtype {k_cache.dtype}")
+        k_new, v_new = k_new.contiguous(), v_new.contiguous()
+        slot_mapping = slot_mapping.to(torch.int64).contiguous()
+        positions = positions.to(torch.int32).contiguous()
+        if slot_mapping.shape != (n,) or positions.shape != (n,):
+            raise ValueError(f"{name}: slot_mapping and positions must be [N]={n}")
+        cos = cos.to(k_new.dtype).contiguous()
+        sin = sin.to(k_new.dtype).contiguous()
+        if cos.dim() != 2 or cos.shape[1] != D or sin.shape != cos.shape:
+            raise ValueError(f"{name}: rope tables must be [rows, {D}]")
+        Hq = 0
+        if q is not None:
+            if q.dim() != 3 or q.shape[0] != n or q.shape[2] != D or q.dtype != k_new.dtype:
+                raise ValueError(f"{name}: q must be [N, H_q, D] in the activation dtype")
+            q = q.contiguous()
+            Hq = q.shape[1]
+            if q_out is None:
+                q_out = torch.empty_like(q)
+            elif q_out.shape != q.shape or q_out.dtype != q.dtype or not q_out.is_contiguous():
+                raise ValueError(f"{name}: q_out must be a contiguous tensor shaped like q")
+        else:
+            q_out = None
+        self._args = N.RopeAppendArgs(
+            k_in=N.ptr(k_new), v_in=N.ptr(v_new), q_in=N.ptr(q), q_out=N.ptr(q_out),
+            k_cache=N.ptr(k_cache), v_cache=N.ptr(v_cache), slot_mapping=N.ptr(slot_mapping),
+            positions=N.ptr(positions), cos=N.ptr(cos), sin=N.ptr(sin),
+            n_tokens=n, num_q_heads=Hq, num_kv_heads=Hkv, head_dim=D, num_blocks=nb, block_size=bs,
+            table_rows=cos.shape[0],
+            cache_stride_blk=k_cache.stride(0), cache_stride_h=k_cache.stride(1), cache_stride_pos=k_cache.stride(2),
+            interleaved=int(bool(interleaved)), dtype=N.dtype_code(k_new), stream=None,
+        )
+        self._ref = C.byref(self._args)
+        self._fn = N.lib().rfx_rope_append
+        self.device = dev
+        self.q_out = q_out
+        self._keep = (k_new, v_new, q, k_cache, v_cache, slot_mapping, positions, cos, sin)
+
+    def run(self) -> Optional[torch.Tensor]:
+        self._args.stream = N.stream_handle(self.device)
+        with torch.cuda.device(self.device):
+            N.check(self._fn(self._ref))
+        return self.q_out
 
 
 def rope_append(
@@ -263,52 +366,8 @@ def rope_append(
     Pool contents equal ``kv_paged_append(apply_rope(k_new...), v_new, ...)`` of the
     reference bit for bit (tables in the activation dtype).
     """
-    name = "rope_append"
-    dev = N.require_cuda(name, k_new, v_new, k_cache, v_cache, slot_mapping, positions, cos, sin, q, q_out)
-    if k_new.dim() != 3 or v_new.shape != k_new.shape:
-        raise ValueError(f"{name}: k_new and v_new must both be [N, H_kv, D]")
-    n, Hkv, D = k_new.shape
-    if k_cache.dim() != 4 or v_cache.shape != k_cache.shape or k_cache.stride() != v_cache.stride():
-        raise ValueError(f"{name}: caches must both be [num_blocks, H_kv, block_size, D] with one stride pattern")
-    nb, ch, bs, cd = k_cache.shape
-    if (Hkv, D) != (ch, cd):
-        raise ValueError(f"{name}: input heads/head_dim {(Hkv, D)} do not match the cache {(ch, cd)}")
-    if k_cache.stride(3) != 1:
-        raise ValueError(f"{name}: the head_dim axis of the caches must be contiguous")
-    if D % 2 != 0:
-        raise ValueError("head_dim must be even for RoPE")
-    if k_new.dtype != k_cache.dtype or v_new.dtype != k_cache.dtype:
-        raise RuntimeError(f"{name}: input dtype {k_new.dtype} does not match cache dtype {k_cache.dtype}")
-    k_new, v_new = k_new.contiguous(), v_new.contiguous()
-    slot_mapping = slot_mapping.to(torch.int64).contiguous()
-    positions = positions.to(torch.int32).contiguous()
-    if slot_mapping.shape != (n,) or positions.shape != (n,):
-        raise ValueError(f"{name}: slot_mapping and positions must be [N]={n}")
-    cos = cos.to(k_new.dtype).contiguous()
-    sin = sin.to(k_new.dtype).contiguous()
-    if cos.dim() != 2 or cos.shape[1] != D or sin.shape != cos.shape:
-        raise ValueError(f"{name}: rope tables must be [rows, {D}]")
-    Hq = 0
-    if q is not None:
-        if q.dim() != 3 or q.shape[0] != n or q.shape[2] != D or q.dtype != k_new.dtype:
-            raise ValueError(f"{name}: q must be [N, H_q, D] in the activation dtype")
-        q = q.contiguous()
-        Hq = q.shape[1]
-        if q_out is None:
-            q_out = torch.empty_like(q)
-        elif q_out.shape != q.shape or q_out.dtype != q.dtype or not q_out.is_contiguous():
-            raise ValueError(f"{name}: q_out must be a contiguous tensor shaped like q")
-    a = N.RopeAppendArgs(
-        k_in=N.ptr(k_new), v_in=N.ptr(v_new), q_in=N.ptr(q), q_out=N.ptr(q_out if q is not None else None),
-        k_cache=N.ptr(k_cache), v_cache=N.ptr(v_cache), slot_mapping=N.ptr(slot_mapping), positions=N.ptr(positions),
-        cos=N.ptr(cos), sin=N.ptr(sin),
-        n_tokens=n, num_q_heads=Hq, num_kv_heads=Hkv, head_dim=D, num_blocks=nb, block_size=bs,
-        table_rows=cos.shape[0],
-        cache_stride_blk=k_cache.stride(0), cache_stride_h=k_cache.stride(1), cache_stride_pos=k_cache.stride(2),
-        interleaved=int(bool(interleaved)), dtype=N.dtype_code(k_new), stream=N.stream_handle(dev),
-    )
-    N.call("rfx_rope_append", a, dev)
-    return q_out if q is not None else None
+    return RopeAppendCall(k_new, v_new, k_cache, v_cache, slot_mapping, positions, cos, sin, q=q, q_out=q_out,
+                          interleaved=interleaved).run()
 
 
 def paged_decode_step(
@@ -367,4 +426,6 @@ __all__ = [
     "rope_append",
     "splitk_combine",
     "PagedWorkspace",
+    "PagedAttentionCall",
+    "RopeAppendCall",
 ]
