@@ -11,48 +11,68 @@ namespace rfx {
 
 constexpr int kCombineWarps = 4;
 
+// `prow_of(s)` gives the partial row of split s. Lanes first fetch the splits' rows and
+// statistics side by side (one round trip for up to 32 splits), then walk the splits with
+// every lane owning four consecutive dims, the loads of successive splits independent.
 template <typename T, typename PartialRow>
 __device__ inline void combine_row(int ns, PartialRow prow_of, const float* __restrict__ pm,
                                    const float* __restrict__ pl, const float* __restrict__ pacc, int D,
                                    T* __restrict__ orow) {
     const int lane = threadIdx.x & 31;
     float M = -INFINITY;
-    for (int s = lane; s < ns; s += 32) M = fmaxf(M, pm[prow_of(s)]);
+    for (int s0 = 0; s0 < ns; s0 += 32) {
+        const int s = s0 + lane;
+        if (s < ns) M = fmaxf(M, pm[prow_of(s)]);
+    }
     M = warp_max(M);
     float L = 0.f;
-    if (M > -INFINITY)
-        for (int s = lane; s < ns; s += 32) {
-            const long long pr = prow_of(s);
-            L += pl[pr] * expf(pm[pr] - M);
-        }
-    L = warp_sum(L);
-    const float inv = L > 0.f ? 1.f / L : 0.f;
-    for (int d0 = 0; d0 < D; d0 += 128) {
-        const int d = d0 + lane * 4;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (d < D && M > -INFINITY) {
-            for (int s = 0; s < ns; ++s) {
-                const long long pr = prow_of(s);
-                const float w = expf(pm[pr] - M);
-                const float* ar = pacc + pr * D + d;
-                if (d + 3 < D && (D & 3) == 0) {
-                    const float4 v = *reinterpret_cast<const float4*>(ar);
-                    acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y);
-                    acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
-                } else {
-                    acc.x = fmaf(w, ar[0], acc.x);
-                    if (d + 1 < D) acc.y = fmaf(w, ar[1], acc.y);
-                    if (d + 2 < D) acc.z = fmaf(w, ar[2], acc.z);
-                    if (d + 3 < D) acc.w = fmaf(w, ar[3], acc.w);
+    float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+    const bool vec = (D & 3) == 0;
+    if (M > -INFINITY) {
+        for (int s0 = 0; s0 < ns; s0 += 32) {
+            const int s = s0 + lane;
+            long long pr = 0;
+            float w = 0.f;
+            if (s < ns) {
+                pr = prow_of(s);
+                const float m = pm[pr];
+                w = (m == -INFINITY) ? 0.f : expf(m - M);
+                L += pl[pr] * w;
+            }
+            const int cnt = min(32, ns - s0);
+#pragma unroll 4
+            for (int j = 0; j < cnt; ++j) {
+                const float wj = __shfl_sync(0xffffffffu, w, j);
+                const long long pj = __shfl_sync(0xffffffffu, pr, j);
+                const float* ar = pacc + pj * D;
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const int d = r * 128 + lane * 4;
+                    if (d >= D) continue;
+                    if (vec) {
+                        const float4 v = *reinterpret_cast<const float4*>(ar + d);
+                        acc[r].x = fmaf(wj, v.x, acc[r].x); acc[r].y = fmaf(wj, v.y, acc[r].y);
+                        acc[r].z = fmaf(wj, v.z, acc[r].z); acc[r].w = fmaf(wj, v.w, acc[r].w);
+                    } else {
+                        acc[r].x = fmaf(wj, ar[d], acc[r].x);
+                        if (d + 1 < D) acc[r].y = fmaf(wj, ar[d + 1], acc[r].y);
+                        if (d + 2 < D) acc[r].z = fmaf(wj, ar[d + 2], acc[r].z);
+                        if (d + 3 < D) acc[r].w = fmaf(wj, ar[d + 3], acc[r].w);
+                    }
                 }
             }
         }
-        if (d < D) {
-            orow[d] = Num<T>::from_f(acc.x * inv);
-            if (d + 1 < D) orow[d + 1] = Num<T>::from_f(acc.y * inv);
-            if (d + 2 < D) orow[d + 2] = Num<T>::from_f(acc.z * inv);
-            if (d + 3 < D) orow[d + 3] = Num<T>::from_f(acc.w * inv);
-        }
+    }
+    L = warp_sum(L);
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int d = r * 128 + lane * 4;
+        if (d >= D) continue;
+        orow[d] = Num<T>::from_f(acc[r].x * inv);
+        if (d + 1 < D) orow[d + 1] = Num<T>::from_f(acc[r].y * inv);
+        if (d + 2 < D) orow[d + 2] = Num<T>::from_f(acc[r].z * inv);
+        if (d + 3 < D) orow[d + 3] = Num<T>::from_f(acc[r].w * inv);
     }
 }
 
@@ -60,7 +80,7 @@ __device__ inline void combine_row(int ns, PartialRow prow_of, const float* __re
 template <typename T>
 __global__ void __launch_bounds__(kCombineWarps * 32)
 paged_combine_kernel(T* __restrict__ out, const int32_t* __restrict__ q_start, int B, int64_t n_q, int Hq,
-                     int Hkv, int D, int32_t* hdr, const int32_t* __restrict__ split_base,
+                     int Hkv, int D, const int32_t* __restrict__ pair_item_begin,
                      const int32_t* __restrict__ item_prow, const float* __restrict__ pm,
                      const float* __restrict__ pl, const float* __restrict__ pacc) {
     const int warp = threadIdx.x >> 5;
@@ -84,14 +104,13 @@ paged_combine_kernel(T* __restrict__ out, const int32_t* __restrict__ q_start, i
             qi = 0;
         }
         const int hkv = h / G, g = h % G;
-        const int ns = split_base[b + 1] - split_base[b];
-        const long long item0 = (long long)Hkv * split_base[b] + (long long)hkv * ns;
+        const long long pair = (long long)b * Hkv + hkv;
+        const int item0 = pair_item_begin[pair];
+        const int ns = pair_item_begin[pair + 1] - item0;
         const int within = qi * G + g;
         combine_row<T>(ns, [&](int s) { return (long long)item_prow[item0 + s] + within; }, pm, pl, pacc, D,
                        out + orow * D);
     }
-    // Re-arm the work counter so the same plan can drive the next layer's launch.
-    if (blockIdx.x == 0 && threadIdx.x == 0) hdr[HdrWorkCounter] = 0;
 }
 
 template <typename T>
@@ -116,7 +135,7 @@ int launch_paged_combine(const RfxPagedAttentionArgs* a, const PlanLayout& L, co
     RFX_DISPATCH_DTYPE(a->dtype, T, {
         paged_combine_kernel<T><<<(int)blocks, kCombineWarps * 32, 0, as_stream(a->stream)>>>(
             (T*)a->out, a->q_start, (int)a->batch, a->n_q, (int)a->num_q_heads, (int)a->num_kv_heads,
-            (int)a->head_dim, P.hdr, P.split_base, P.item_prow, P.m, P.l, P.acc);
+            (int)a->head_dim, P.pair_item_begin, P.item_prow, P.m, P.l, P.acc);
     });
     return check_launch("rfx_paged_attention (combine)");
 }
@@ -128,7 +147,7 @@ extern "C" int rfx_splitk_combine(const RfxCombineArgs* a) {
     const char* name = "rfx_splitk_combine";
     if (!a) return fail(RFX_INVALID_ARGUMENT, "%s: null args", name);
     RFX_REQUIRE(dtype_ok(a->dtype), "%s: unknown dtype %d", name, a->dtype);
-    RFX_REQUIRE(a->rows >= 0 && a->head_dim > 0, "%s: bad sizes", name);
+    RFX_REQUIRE(a->rows >= 0 && a->head_dim > 0 && a->head_dim <= 256, "%s: bad sizes", name);
     if (a->rows == 0) return RFX_SUCCESS;
     RFX_REQUIRE(a->acc && a->m && a->l && a->split_begin && a->out, "%s: null pointer", name);
     RFX_REQUIRE(((uintptr_t)a->acc % 16) == 0, "%s: acc must be 16-byte aligned", name);

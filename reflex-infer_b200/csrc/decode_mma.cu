@@ -1,17 +1,21 @@
 // Paged GQA decode, split-K partial kernel for 16-bit KV with head_dim 128 or 64.
 //
-// HBM-bound: every (request, kv_head, key-range) item streams its K and V pages exactly
-// once. A persistent CTA per SM runs one producer warp and four consumer warps:
-//   producer : pulls items from an atomic work counter, reads block-table entries 32 at a
-//              time, and issues one TMA tile copy per page for K and for V into a ring of
-//              64-key stages; each copy lands the page as [half][row][128 B] with the
-//              128-byte swizzle, completion counted on the stage's mbarrier;
-//   consumers: each takes 16 of the stage's 64 keys: S = Q.K^T with the G query heads of
-//              the group as the (padded) 16 MMA rows, online softmax with quad shuffles,
-//              O += P.V, all through m16n8k16 warp MMAs fed by conflict-free ldmatrix;
-//              at the item's last stage the four warps merge (m, l, acc) through shared
-//              memory and write one partial.
-// RoPE can be fused into the Q load with torch's per-op rounding.
+// HBM-bound: every item (a run of 64-key tiles of one (request, kv_head) pair) streams its
+// K and V pages exactly once. One persistent CTA per SM owns one equal run of the tile
+// stream and has one producer warp and eight consumer warps in two groups:
+//   producer : loads its run's item descriptors in one round trip, keeps the block-table
+//              entries of the current and the next item in registers (32 per lane-window),
+//              and issues one TMA tile copy per page for K and for V into a ring of 64-key
+//              stages; each copy lands the page as [half][row][128 B] with the 128-byte
+//              swizzle, completion counted on the stage's mbarrier. With an item's first
+//              stage it also bulk-copies the G query rows and the RoPE table row;
+//   consumers: stages alternate between the two groups, so two stages are in work at any
+//              time and the MMA/softmax latency of one hides behind the other. In a group
+//              each warp takes 16 of the 64 keys: S = Q.K^T with the G query heads as the
+//              (padded) 16 MMA rows, online softmax with quad shuffles, O += P.V, all through
+//              m16n8k16 warp MMAs fed by conflict-free ldmatrix. At the item's last stage the
+//              eight warps merge (m, l, acc) through shared memory and write one partial.
+// RoPE is fused into the Q load with torch's per-op rounding.
 //
 // Algorithmic bytes per item: 2 * keys * D * e (K and V). Arithmetic is G FLOP/byte, far
 // below what the warp MMA path sustains, so the kernel's roofline is HBM bandwidth.
@@ -24,18 +28,16 @@
 
 namespace rfx {
 
-constexpr int kTile = 64;           // keys per stage
-constexpr int kConsumers = 4;       // consumer warps, 16 keys each
-constexpr int kDecodeThreads = (kConsumers + 1) * 32;
-constexpr int kAccPad = 8;          // floats of padding per merge row (bank spread)
+constexpr int kTile = kPlanTile;    // keys per stage
+constexpr int kGroupWarps = 4;      // warps per consumer group, 16 keys each
+constexpr int kMaxGroups = 2;
+constexpr int kAccPad = 4;          // floats of padding per merge row (bank spread)
 
 struct StageMeta {
     int item;      // -1: no more work
-    int b, hkv;
     int n_valid;   // keys of this stage that exist (0..64)
-    int flags;     // bit0 first stage of item, bit1 last stage of item
+    int flags;     // bit0 first stage of item, bit1 last stage of item, bit2 rotate Q
     int prow;      // first partial row of the item
-    int pad0, pad1;
 };
 
 struct DecodeParams {
@@ -45,6 +47,7 @@ struct DecodeParams {
     const void* rsin;
     const int32_t* rpos;
     int32_t* hdr;
+    const int32_t* part_first;
     const int4* items;
     const int32_t* item_prow;
     float* pm;
@@ -52,6 +55,7 @@ struct DecodeParams {
     float* pacc;
     int64_t num_blocks, max_blocks, bt_sb, table_rows;
     int Hq, Hkv, G, block_size, box_rows, rope_inter;
+    int skip_math;     // debugging aid: consumers release stages without computing
     int map2d;         // 1: the maps are 2-D [rows, D] with {64, box_rows} boxes, one copy per 128-byte half
     float scale_log2;  // sm_scale * log2(e)
 };
@@ -61,12 +65,15 @@ struct DecodeSmem {
     static constexpr int kRowBytes = HD * 2;
     static constexpr int kTileBytes = kTile * kRowBytes;  // K or V of one stage
     static constexpr int kAccStride = HD + kAccPad;
+    static constexpr int kQBytes = GP * kRowBytes;        // raw query rows of the group
+    static constexpr int kQSlot = kQBytes + 2 * kRowBytes;  // + cos row + sin row
     static constexpr size_t off_k = 0;
     static constexpr size_t off_v = (size_t)STAGES * kTileBytes;
-    static constexpr size_t off_merge = 2 * (size_t)STAGES * kTileBytes;
-    static constexpr size_t merge_bytes = (size_t)kConsumers * GP * kAccStride * 4;
-    static constexpr size_t off_ml = off_merge + merge_bytes;             // [warps][GP][2]
-    static constexpr size_t off_meta = off_ml + (size_t)kConsumers * GP * 2 * 4;
+    static constexpr size_t off_q = 2 * (size_t)STAGES * kTileBytes;
+    static constexpr size_t off_merge = off_q + (size_t)STAGES * kQSlot;
+    static constexpr size_t merge_bytes = (size_t)kGroupWarps * GP * kAccStride * 4;
+    static constexpr size_t off_ml = off_merge + merge_bytes;             // [group warps][GP][2]
+    static constexpr size_t off_meta = off_ml + (size_t)kGroupWarps * GP * 2 * 4;
     static constexpr size_t off_bars = off_meta + (size_t)STAGES * sizeof(StageMeta);
     static constexpr size_t total = off_bars + 2 * (size_t)STAGES * 8 + 1024;  // + alignment slack
 };
@@ -86,35 +93,28 @@ template <> struct Pack2<__half> {
 };
 
 template <typename T> __device__ inline uint32_t pack_t(T a, T b) {
-    uint32_t r;
-    uint16_t lo = *reinterpret_cast<uint16_t*>(&a), hi = *reinterpret_cast<uint16_t*>(&b);
-    r = (uint32_t)lo | ((uint32_t)hi << 16);
-    return r;
+    const uint16_t lo = *reinterpret_cast<uint16_t*>(&a), hi = *reinterpret_cast<uint16_t*>(&b);
+    return (uint32_t)lo | ((uint32_t)hi << 16);
 }
 
-// Loads (and optionally rotates) the A fragments of Q for the item's G heads.
+// Builds the A fragments of Q for the item's G heads from the stage's query slot
+// (raw rows, then the cos row, then the sin row), rotating when asked.
 // qa[ks][0] = row g,   dims 16ks + 2c + {0,1};   qa[ks][1] = row g+8, same dims;
 // qa[ks][2] = row g,   dims 16ks + 8 + 2c + ..;  qa[ks][3] = row g+8      (c = lane % 4).
 template <typename T, int HD, int GP>
-__device__ inline void load_q_frags(uint32_t (&qa)[HD / 16][4], const DecodeParams& P, int b, int hkv) {
+__device__ inline void load_q_frags(uint32_t (&qa)[HD / 16][4], const unsigned char* slot, int G, bool rotate,
+                                    bool interleaved) {
     const int lane = threadIdx.x & 31;
     const int g0 = lane >> 2, c = lane & 3;
-    const T* qb = (const T*)P.q + ((int64_t)b * P.Hq + (int64_t)hkv * P.G) * HD;
-    const bool rope = P.rcos != nullptr;
-    int64_t pos = 0;
-    bool pos_ok = false;
-    if (rope) {
-        pos = P.rpos[b];
-        pos_ok = pos >= 0 && pos < P.table_rows;
-    }
-    const T* cr = (const T*)P.rcos + (pos_ok ? pos : 0) * HD;
-    const T* sr = (const T*)P.rsin + (pos_ok ? pos : 0) * HD;
+    const T* qs = reinterpret_cast<const T*>(slot);
+    const T* cr = qs + GP * HD;
+    const T* sr = cr + HD;
 #pragma unroll
     for (int rr = 0; rr < (GP > 8 ? 2 : 1); ++rr) {
         const int g = g0 + 8 * rr;
-        const bool live = g < P.G;
-        const T* qr = qb + (int64_t)g * HD;
-        if (!rope || !pos_ok) {
+        const bool live = g < G;
+        const T* qr = qs + g * HD;
+        if (!rotate) {
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
                 uint32_t lo = 0, hi = 0;
@@ -125,7 +125,7 @@ __device__ inline void load_q_frags(uint32_t (&qa)[HD / 16][4], const DecodePara
                 qa[ks][rr] = lo;
                 qa[ks][2 + rr] = hi;
             }
-        } else if (P.rope_inter) {
+        } else if (interleaved) {
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
 #pragma unroll
@@ -167,18 +167,20 @@ __device__ inline void load_q_frags(uint32_t (&qa)[HD / 16][4], const DecodePara
     }
 }
 
-template <typename T, int HD, int GP, int STAGES>
-__global__ void __launch_bounds__(kDecodeThreads, 1)
+template <typename T, int HD, int GP, int STAGES, int GROUPS>
+__global__ void __launch_bounds__((kGroupWarps * GROUPS + 1) * 32, 1)
 decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                   const DecodeParams P) {
     using S = DecodeSmem<HD, GP, STAGES>;
     constexpr bool BF = std::is_same<T, __nv_bfloat16>::value;
+    constexpr int kConsumers = kGroupWarps * GROUPS;
     extern __shared__ unsigned char smem_raw[];
     // TMA's 128-byte swizzle is a function of the shared-memory address, so tiles must
     // start on 1024-byte boundaries; the launch asks for 1 KiB of slack.
     unsigned char* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char* sK = smem + S::off_k;
     unsigned char* sV = smem + S::off_v;
+    unsigned char* sQ = smem + S::off_q;
     float* sAcc = reinterpret_cast<float*>(smem + S::off_merge);
     float* sML = reinterpret_cast<float*>(smem + S::off_ml);
     StageMeta* sMeta = reinterpret_cast<StageMeta*>(smem + S::off_meta);
@@ -198,142 +200,173 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     }
     __syncthreads();
 
-    if (warp == kConsumers) {
+    if (warp == kConsumers) {  // the last warp
         // ------------------------------------------------------------ producer --
         if (lane == 0) {
             ptx::prefetch_tensormap(&kmap);
             ptx::prefetch_tensormap(&vmap);
         }
-        const int n_items = P.hdr[HdrNumItems];
+        const int n_parts = P.hdr[HdrNumParts];
         int stage = 0;
         uint32_t phase = 0;
         bool alive = true;
-        // Two-deep item pipeline: `cur` is being issued, `nxt_id` is known, the atomic for
-        // the one after is in flight.
-        int cur_id = 0, nxt_id = 0;
-        if (lane == 0) {
-            cur_id = atomicAdd(P.hdr + HdrWorkCounter, 1);
-            nxt_id = atomicAdd(P.hdr + HdrWorkCounter, 1);
-        }
-        cur_id = __shfl_sync(0xffffffffu, cur_id, 0);
-        nxt_id = __shfl_sync(0xffffffffu, nxt_id, 0);
-        int4 cur = make_int4(0, 0, 0, 0);
-        int cur_prow = 0;
-        if (cur_id < n_items) { cur = P.items[cur_id]; cur_prow = P.item_prow[cur_id]; }
-        while (alive && cur_id < n_items) {
-            int4 nxt = make_int4(0, 0, 0, 0);
-            int nxt_prow = 0;
-            if (nxt_id < n_items) { nxt = P.items[nxt_id]; nxt_prow = P.item_prow[nxt_id]; }
-            int nn_id = 0;
-            if (lane == 0) nn_id = atomicAdd(P.hdr + HdrWorkCounter, 1);
-
-            const int b = cur.x, hkv = cur.y, kb = cur.z, ke = cur.w;
-            const int n_tiles = (ke - kb + kTile - 1) / kTile;
-            const int64_t* bt = P.block_table + (int64_t)b * P.bt_sb;
-            // window of 32 consecutive logical blocks held one per lane
-            int win0 = kb / P.block_size;
-            auto load_win = [&](int w0) -> int64_t {
-                const int64_t lb = (int64_t)w0 + lane;
-                const int64_t last = ((int64_t)ke - 1) / P.block_size;
-                return (lb <= last && lb < P.max_blocks) ? bt[lb] : -1;
-            };
-            int64_t pg_cur = (n_tiles > 0) ? load_win(win0) : -1;
-            int64_t pg_nxt = (n_tiles > 0) ? load_win(win0 + 32) : -1;
-            const int it_count = n_tiles > 0 ? n_tiles : 1;  // an empty item still sends one stage
-            for (int t = 0; t < it_count && alive; ++t) {
-                const int tok0 = kb + t * kTile;
-                const int n_valid = max(0, min(kTile, ke - tok0));
-                const int n_boxes = (n_valid + R - 1) / R;
-                bool ok = true;
-                if (lane == 0) ok = ptx::mbar_wait_bounded(&empty[stage], phase ^ 1u);
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (!ok) {
-                    if (lane == 0) atomicOr(P.hdr + HdrStatus, kStatusWaitExpired);
-                    alive = false;
-                    break;
+        for (int part = blockIdx.x; part < n_parts && alive; part += gridDim.x) {
+            const int i_begin = P.part_first[part], i_end = P.part_first[part + 1];
+            for (int ib = i_begin; ib < i_end && alive; ib += 32) {
+                // one round trip: lane j holds the descriptor of item ib + j
+                const int my_id = ib + lane;
+                int4 my_desc = make_int4(0, 0, 0, 0);
+                int my_prow = 0, my_pos = -1;
+                if (my_id < i_end) {
+                    my_desc = P.items[my_id];
+                    my_prow = P.item_prow[my_id];
+                    if (P.rcos) my_pos = P.rpos[my_desc.x];
                 }
-                // page of box i: logical block (tok0 + i*R) / block_size
-                int64_t my_page = -1;
-                int my_row0 = 0;
+                const int n_here = min(32, i_end - ib);
+                auto load_win = [&](const int64_t* bt, int w0, int ke) -> int64_t {
+                    const int64_t lb = (int64_t)w0 + lane;
+                    const int64_t last = ((int64_t)ke - 1) / P.block_size;
+                    return (lb <= last && lb < P.max_blocks) ? bt[lb] : -1;
+                };
+                // block-table window of the first item; later items prefetch during their predecessor
+                int64_t nx_cur, nx_nxt;
                 {
-                    const bool want = lane < n_boxes;
-                    const int tok = tok0 + (want ? lane : 0) * R;
-                    const int lb = tok / P.block_size;
-                    my_row0 = tok - lb * P.block_size;
-                    const int rel = lb - win0;  // 0..63 by construction of the window advance
-                    const int64_t a = __shfl_sync(0xffffffffu, pg_cur, rel & 31);
-                    const int64_t c2 = __shfl_sync(0xffffffffu, pg_nxt, rel & 31);
-                    if (want) my_page = rel < 32 ? a : c2;
+                    const int b0 = __shfl_sync(0xffffffffu, my_desc.x, 0);
+                    const int kb0 = __shfl_sync(0xffffffffu, my_desc.z, 0), ke0 = __shfl_sync(0xffffffffu, my_desc.w, 0);
+                    const int64_t* bt0 = P.block_table + (int64_t)b0 * P.bt_sb;
+                    nx_cur = load_win(bt0, kb0 / P.block_size, ke0);
+                    nx_nxt = load_win(bt0, kb0 / P.block_size + 32, ke0);
                 }
-                const bool page_ok = my_page >= 0 && my_page < P.num_blocks;
-                const unsigned okmask = __ballot_sync(0xffffffffu, lane < n_boxes && page_ok);
-                const unsigned wantmask = __ballot_sync(0xffffffffu, lane < n_boxes);
-                if (lane == 0) {
-                    StageMeta m;
-                    m.item = cur_id; m.b = b; m.hkv = hkv; m.n_valid = n_valid;
-                    m.flags = (t == 0 ? 1 : 0) | (t == it_count - 1 ? 2 : 0);
-                    m.prow = cur_prow; m.pad0 = 0; m.pad1 = 0;
-                    sMeta[stage] = m;
-                    if (okmask != wantmask) atomicOr(P.hdr + HdrStatus, kStatusBadPage);
-                    ptx::mbar_arrive_expect_tx(&full[stage], 2u * box_bytes * (uint32_t)__popc(okmask));
-                }
-                __syncwarp();
-                if (lane < n_boxes && page_ok) {
-                    const int row = (int)((my_page * P.Hkv + hkv) * P.block_size + my_row0);
-                    unsigned char* kd = sK + (size_t)stage * S::kTileBytes + (size_t)lane * box_bytes;
-                    unsigned char* vd = sV + (size_t)stage * S::kTileBytes + (size_t)lane * box_bytes;
-                    if (!P.map2d) {
-                        ptx::tma_load_3d(kd, &kmap, &full[stage], 0, row, 0);
-                        ptx::tma_load_3d(vd, &vmap, &full[stage], 0, row, 0);
-                    } else {
+                for (int j = 0; j < n_here && alive; ++j) {
+                    const int b = __shfl_sync(0xffffffffu, my_desc.x, j), hkv = __shfl_sync(0xffffffffu, my_desc.y, j);
+                    const int kb = __shfl_sync(0xffffffffu, my_desc.z, j), ke = __shfl_sync(0xffffffffu, my_desc.w, j);
+                    const int prow = __shfl_sync(0xffffffffu, my_prow, j);
+                    const int pos = __shfl_sync(0xffffffffu, my_pos, j);
+                    const bool rotate = P.rcos != nullptr && pos >= 0 && (int64_t)pos < P.table_rows;
+                    const int64_t* bt = P.block_table + (int64_t)b * P.bt_sb;
+                    int win0 = kb / P.block_size;
+                    int64_t pg_cur = nx_cur, pg_nxt = nx_nxt;
+                    if (j + 1 < n_here) {
+                        const int b1 = __shfl_sync(0xffffffffu, my_desc.x, j + 1);
+                        const int kb1 = __shfl_sync(0xffffffffu, my_desc.z, j + 1);
+                        const int ke1 = __shfl_sync(0xffffffffu, my_desc.w, j + 1);
+                        const int64_t* bt1 = P.block_table + (int64_t)b1 * P.bt_sb;
+                        nx_cur = load_win(bt1, kb1 / P.block_size, ke1);
+                        nx_nxt = load_win(bt1, kb1 / P.block_size + 32, ke1);
+                    }
+                    const int n_tiles = (ke - kb + kTile - 1) / kTile;
+                    for (int t = 0; t < n_tiles && alive; ++t) {
+                        const int tok0 = kb + t * kTile;
+                        const int n_valid = min(kTile, ke - tok0);
+                        const int n_boxes = (n_valid + R - 1) / R;
+                        int ok = 1;
+                        if (lane == 0) ok = ptx::mbar_wait_bounded(&empty[stage], phase ^ 1u) ? 1 : 0;
+                        ok = __shfl_sync(0xffffffffu, ok, 0);
+                        if (!ok) {
+                            if (lane == 0) atomicOr(P.hdr + HdrStatus, kStatusWaitExpired);
+                            alive = false;
+                            break;
+                        }
+                        // page of box i: logical block (tok0 + i*R) / block_size
+                        int64_t my_page = -1;
+                        int my_row0 = 0;
+                        {
+                            const bool want = lane < n_boxes;
+                            const int tok = tok0 + (want ? lane : 0) * R;
+                            const int lb = tok / P.block_size;
+                            my_row0 = tok - lb * P.block_size;
+                            const int rel = lb - win0;  // 0..63 by construction of the window advance
+                            const int64_t a = __shfl_sync(0xffffffffu, pg_cur, rel & 31);
+                            const int64_t c2 = __shfl_sync(0xffffffffu, pg_nxt, rel & 31);
+                            if (want) my_page = rel < 32 ? a : c2;
+                        }
+                        const bool page_ok = my_page >= 0 && my_page < P.num_blocks;
+                        const unsigned okmask = __ballot_sync(0xffffffffu, lane < n_boxes && page_ok);
+                        const unsigned wantmask = __ballot_sync(0xffffffffu, lane < n_boxes);
+                        const uint32_t q_bytes = (uint32_t)P.G * S::kRowBytes;
+                        if (lane == 0) {
+                            StageMeta m;
+                            m.item = ib + j; m.n_valid = n_valid;
+                            m.flags = (t == 0 ? 1 : 0) | (t == n_tiles - 1 ? 2 : 0) | (rotate ? 4 : 0);
+                            m.prow = prow;
+                            sMeta[stage] = m;
+                            if (okmask != wantmask) atomicOr(P.hdr + HdrStatus, kStatusBadPage);
+                            uint32_t tx = 2u * box_bytes * (uint32_t)__popc(okmask);
+                            if (t == 0) tx += q_bytes + (rotate ? 2u * S::kRowBytes : 0u);
+                            ptx::mbar_arrive_expect_tx(&full[stage], tx);
+                        }
+                        __syncwarp();
+                        if (lane < n_boxes && page_ok) {
+                            const int row = (int)((my_page * P.Hkv + hkv) * P.block_size + my_row0);
+                            unsigned char* kd = sK + (size_t)stage * S::kTileBytes + (size_t)lane * box_bytes;
+                            unsigned char* vd = sV + (size_t)stage * S::kTileBytes + (size_t)lane * box_bytes;
+                            if (!P.map2d) {
+                                ptx::tma_load_3d(kd, &kmap, &full[stage], 0, row, 0);
+                                ptx::tma_load_3d(vd, &vmap, &full[stage], 0, row, 0);
+                            } else {
 #pragma unroll
-                        for (int hf = 0; hf < HD / 64; ++hf) {
-                            ptx::tma_load_2d(kd + (size_t)hf * R * 128, &kmap, &full[stage], hf * 64, row);
-                            ptx::tma_load_2d(vd + (size_t)hf * R * 128, &vmap, &full[stage], hf * 64, row);
+                                for (int hf = 0; hf < HD / 64; ++hf) {
+                                    ptx::tma_load_2d(kd + (size_t)hf * R * 128, &kmap, &full[stage], hf * 64, row);
+                                    ptx::tma_load_2d(vd + (size_t)hf * R * 128, &vmap, &full[stage], hf * 64, row);
+                                }
+                            }
+                        }
+                        if (t == 0 && lane == 31) {
+                            // the item's query rows (contiguous: heads hkv*G .. hkv*G+G-1 of row b) and table rows
+                            unsigned char* qd = sQ + (size_t)stage * S::kQSlot;
+                            const unsigned char* qsrc = (const unsigned char*)P.q +
+                                                        ((int64_t)b * P.Hq + (int64_t)hkv * P.G) * S::kRowBytes;
+                            ptx::bulk_load(qd, qsrc, q_bytes, &full[stage]);
+                            if (rotate) {
+                                ptx::bulk_load(qd + S::kQBytes, (const unsigned char*)P.rcos + (int64_t)pos * S::kRowBytes,
+                                               S::kRowBytes, &full[stage]);
+                                ptx::bulk_load(qd + S::kQBytes + S::kRowBytes,
+                                               (const unsigned char*)P.rsin + (int64_t)pos * S::kRowBytes, S::kRowBytes,
+                                               &full[stage]);
+                            }
+                        }
+                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                        // advance the block window once the next stage starts beyond it
+                        const int next_lb = (tok0 + kTile) / P.block_size;
+                        if (next_lb - win0 >= 32 && t + 1 < n_tiles) {
+                            win0 += 32;
+                            pg_cur = pg_nxt;
+                            pg_nxt = load_win(bt, win0 + 32, ke);
                         }
                     }
                 }
-                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-                // advance the block window once the next stage starts beyond it
-                const int next_lb = (tok0 + kTile) / P.block_size;
-                if (next_lb - win0 >= 32 && t + 1 < it_count) {
-                    win0 += 32;
-                    pg_cur = pg_nxt;
-                    pg_nxt = load_win(win0 + 32);
-                }
             }
-            cur_id = nxt_id; cur = nxt; cur_prow = nxt_prow;
-            nxt_id = __shfl_sync(0xffffffffu, nn_id, 0);
         }
         // Tell the consumers there is nothing left.
-        if (alive) {
-            bool ok = true;
-            if (lane == 0) ok = ptx::mbar_wait_bounded(&empty[stage], phase ^ 1u);
-            if (lane == 0) {
-                if (ok) {
-                    StageMeta m;
-                    m.item = -1; m.b = 0; m.hkv = 0; m.n_valid = 0; m.flags = 0; m.prow = 0; m.pad0 = 0; m.pad1 = 0;
-                    sMeta[stage] = m;
-                    ptx::mbar_arrive(&full[stage]);
-                } else {
-                    atomicOr(P.hdr + HdrStatus, kStatusWaitExpired);
-                }
+        if (alive && lane == 0) {
+            if (ptx::mbar_wait_bounded(&empty[stage], phase ^ 1u)) {
+                StageMeta m;
+                m.item = -1; m.n_valid = 0; m.flags = 0; m.prow = 0;
+                sMeta[stage] = m;
+                ptx::mbar_arrive(&full[stage]);
+            } else {
+                atomicOr(P.hdr + HdrStatus, kStatusWaitExpired);
             }
         }
         return;
     }
 
     // ---------------------------------------------------------------- consumers --
-    const int g0 = lane >> 2, c4 = lane & 3;
+    // Keys are the 16 MMA rows and the group's heads the columns: S^T = K.Q^T (A = K rows
+    // straight from the swizzled tile, B = the Q fragments), softmax down the columns with
+    // lane/4 shuffles, P^T turned into a B operand with movmatrix, O^T += V^T.P^T (A = V
+    // through transposing ldmatrix). No MMA row or column is padding when G is 8 or 16.
+    constexpr int NT = GP / 8;  // head n-tiles
+    const int group = warp / kGroupWarps, wq = warp % kGroupWarps;
+    const int r8 = lane >> 2, c4 = lane & 3;
     uint32_t qa[HD / 16][4];
-    float o[HD / 8][GP > 8 ? 4 : 2];
-    float m_run[GP > 8 ? 2 : 1], l_run[GP > 8 ? 2 : 1];
-    constexpr int NR = GP > 8 ? 2 : 1;
+    float o[HD / 16][NT][4];
+    float m_run[NT][2], l_run[NT][2];
 
     // lane-constant parts of the ldmatrix addresses
     const int mat = lane >> 3, rowi = lane & 7;
-    const int k_tok = warp * 16 + (mat >> 1) * 8 + rowi;  // K: matrices 0,1 keys 0-7; 2,3 keys 8-15
-    const int v_tok = warp * 16 + (mat & 1) * 8 + rowi;   // V: matrices 0,2 keys 0-7; 1,3 keys 8-15
+    const int k_tok = wq * 16 + (mat & 1) * 8 + rowi;   // K (A operand): matrices 0,2 keys 0-7; 1,3 keys 8-15
+    const int v_tok = wq * 16 + (mat >> 1) * 8 + rowi;  // V (A operand, transposed): matrices 0,1 keys 0-7; 2,3 keys 8-15
     const int k_box = k_tok / R, k_r = k_tok - k_box * R;
     const int v_box = v_tok / R, v_r = v_tok - v_box * R;
     const uint32_t k_rowoff = (uint32_t)k_box * box_bytes + (uint32_t)k_r * 128u;
@@ -344,6 +377,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 
     int stage = 0;
     uint32_t phase = 0;
+    int turn = 0;  // which group computes the current stage
     while (true) {
         // every lane acquires the stage itself; the vote keeps an expired wait warp-uniform
         if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&full[stage], phase) ? 1 : 0)) {
@@ -353,16 +387,18 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         const StageMeta meta = sMeta[stage];
         if (meta.item < 0) break;
         if (meta.flags & 1) {
-            load_q_frags<T, HD, GP>(qa, P, meta.b, meta.hkv);
+            load_q_frags<T, HD, GP>(qa, sQ + (size_t)stage * S::kQSlot, P.G, (meta.flags & 4) != 0, P.rope_inter != 0);
 #pragma unroll
-            for (int r = 0; r < NR; ++r) { m_run[r] = -INFINITY; l_run[r] = 0.f; }
+            for (int nt = 0; nt < NT; ++nt) { m_run[nt][0] = m_run[nt][1] = -INFINITY; l_run[nt][0] = l_run[nt][1] = 0.f; }
 #pragma unroll
-            for (int nt = 0; nt < HD / 8; ++nt)
+            for (int j = 0; j < HD / 16; ++j)
 #pragma unroll
-                for (int i = 0; i < 2 * NR; ++i) o[nt][i] = 0.f;
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) o[j][nt][i] = 0.f;
         }
-        const int slice0 = warp * 16;
-        if (slice0 < meta.n_valid) {
+        const int slice0 = wq * 16;
+        if (group == turn && slice0 < meta.n_valid && P.skip_math != 1) {
             const uint32_t kst = sK_u32 + (uint32_t)stage * S::kTileBytes;
             const uint32_t vst = sV_u32 + (uint32_t)stage * S::kTileBytes;
             const bool tail = meta.n_valid < slice0 + 16;
@@ -382,109 +418,162 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
             }
-            // ---- S = Q.K^T : rows = heads of the group, cols = this warp's 16 keys
-            float s[2][4];
+            // ---- S^T = K.Q^T : rows = this warp's 16 keys, cols = heads of the group
+            float s[NT][4];
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
+            for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
+            if (P.skip_math != 3)
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
-                const uint32_t chunk = (uint32_t)(2 * ks + (mat & 1));
+                const uint32_t chunk = (uint32_t)(2 * ks + (mat >> 1));
                 const uint32_t addr = kst + k_rowoff + (chunk >> 3) * half_bytes + (((chunk & 7u) ^ k_sw) << 4);
-                uint32_t b0, b1, b2, b3;
-                ptx::ldmatrix_x4(addr, b0, b1, b2, b3);
-                ptx::mma_16816<BF>(s[0][0], s[0][1], s[0][2], s[0][3], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3],
-                                   b0, b1, s[0][0], s[0][1], s[0][2], s[0][3]);
-                ptx::mma_16816<BF>(s[1][0], s[1][1], s[1][2], s[1][3], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3],
-                                   b2, b3, s[1][0], s[1][1], s[1][2], s[1][3]);
+                uint32_t a0, a1, a2, a3;
+                ptx::ldmatrix_x4(addr, a0, a1, a2, a3);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+                    ptx::mma_16816<BF>(s[nt][0], s[nt][1], s[nt][2], s[nt][3], a0, a1, a2, a3, qa[ks][nt],
+                                       qa[ks][2 + nt], s[nt][0], s[nt][1], s[nt][2], s[nt][3]);
             }
-            // ---- online softmax (base-2 domain), rows g0 (+8)
-            uint32_t pa[4];
+            // ---- online softmax down the columns (base-2 domain). Fast path: nothing exceeds
+            // the running column maxima (the usual case after the first tiles), so the
+            // probabilities come straight from one FMA and one EX2 each; only when some
+            // value does are the exact maxima reduced with shuffles and the state rescaled.
+            uint32_t pb[NT][2];
 #pragma unroll
-            for (int r = 0; r < NR; ++r) {
-                float v[4];
+            for (int nt = 0; nt < NT; ++nt) {
+                float t[4];
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
+                for (int i = 0; i < 4; ++i) {
+                    t[i] = fmaf(s[nt][i], P.scale_log2, -m_run[nt][i & 1]);  // +inf while m_run is -inf
+                    if (tail && slice0 + r8 + 8 * (i >> 1) >= meta.n_valid) t[i] = -INFINITY;
+                }
+                const bool exceeds = fmaxf(fmaxf(t[0], t[1]), fmaxf(t[2], t[3])) > 0.f;
+                if (__any_sync(0xffffffffu, exceeds)) {
+                    float v[4];
 #pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        float x = s[nt][2 * r + i] * P.scale_log2;
-                        if (tail) {
-                            const int tk = slice0 + nt * 8 + 2 * c4 + i;
-                            if (tk >= meta.n_valid) x = -INFINITY;
-                        }
-                        v[nt * 2 + i] = x;
+                    for (int i = 0; i < 4; ++i) {
+                        v[i] = s[nt][i] * P.scale_log2;
+                        if (tail && slice0 + r8 + 8 * (i >> 1) >= meta.n_valid) v[i] = -INFINITY;
                     }
-                float mx = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                const float m_new = fmaxf(m_run[r], mx);  // finite: the slice has a valid key
-                const float alpha = exp2f(m_run[r] - m_new);
-                float p[4];
+                    float mx0 = fmaxf(v[0], v[2]), mx1 = fmaxf(v[1], v[3]);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) p[i] = exp2f(v[i] - m_new);
-                l_run[r] = l_run[r] * alpha + (p[0] + p[1] + p[2] + p[3]);
-                m_run[r] = m_new;
+                    for (int sh = 4; sh < 32; sh <<= 1) {
+                        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
+                        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
+                    }
+                    const float mn0 = fmaxf(m_run[nt][0], mx0), mn1 = fmaxf(m_run[nt][1], mx1);  // finite
+                    const float al0 = ptx::ex2(m_run[nt][0] - mn0), al1 = ptx::ex2(m_run[nt][1] - mn1);
+                    l_run[nt][0] *= al0;
+                    l_run[nt][1] *= al1;
 #pragma unroll
-                for (int nt = 0; nt < HD / 8; ++nt) { o[nt][2 * r] *= alpha; o[nt][2 * r + 1] *= alpha; }
-                pa[r] = Pack2<T>::pack(p[0], p[1]);      // keys 0-7 of the slice
-                pa[2 + r] = Pack2<T>::pack(p[2], p[3]);  // keys 8-15
+                    for (int j = 0; j < HD / 16; ++j) {
+                        o[j][nt][0] *= al0; o[j][nt][2] *= al0;
+                        o[j][nt][1] *= al1; o[j][nt][3] *= al1;
+                    }
+                    m_run[nt][0] = mn0;
+                    m_run[nt][1] = mn1;
+                    t[0] = v[0] - mn0; t[1] = v[1] - mn1; t[2] = v[2] - mn0; t[3] = v[3] - mn1;
+                }
+                const float p0 = ptx::ex2(t[0]), p1 = ptx::ex2(t[1]), p2 = ptx::ex2(t[2]), p3 = ptx::ex2(t[3]);
+                l_run[nt][0] += p0 + p2;
+                l_run[nt][1] += p1 + p3;
+                // C fragment (key rows, head cols) -> B fragment (k = key, n = head)
+                pb[nt][0] = ptx::movmatrix_trans(Pack2<T>::pack(p0, p1));  // keys 0-7 of the slice
+                pb[nt][1] = ptx::movmatrix_trans(Pack2<T>::pack(p2, p3));  // keys 8-15
             }
-            if (NR == 1) { pa[1] = 0; pa[3] = 0; }
-            // ---- O += P.V
+            // ---- O^T += V^T.P^T : rows = 16 dims per tile, cols = heads
+            if (P.skip_math != 2)
 #pragma unroll
             for (int j = 0; j < HD / 16; ++j) {
-                const uint32_t chunk = (uint32_t)(2 * j + (mat >> 1));
+                const uint32_t chunk = (uint32_t)(2 * j + (mat & 1));
                 const uint32_t addr = vst + v_rowoff + (chunk >> 3) * half_bytes + (((chunk & 7u) ^ v_sw) << 4);
-                uint32_t b0, b1, b2, b3;
-                ptx::ldmatrix_x4_trans(addr, b0, b1, b2, b3);
-                if (NR == 2) {
-                    ptx::mma_16816<BF>(o[2 * j][0], o[2 * j][1], o[2 * j][2], o[2 * j][3], pa[0], pa[1], pa[2],
-                                       pa[3], b0, b1, o[2 * j][0], o[2 * j][1], o[2 * j][2], o[2 * j][3]);
-                    ptx::mma_16816<BF>(o[2 * j + 1][0], o[2 * j + 1][1], o[2 * j + 1][2], o[2 * j + 1][3], pa[0],
-                                       pa[1], pa[2], pa[3], b2, b3, o[2 * j + 1][0], o[2 * j + 1][1],
-                                       o[2 * j + 1][2], o[2 * j + 1][3]);
-                } else {
-                    float j2, j3;
-                    ptx::mma_16816<BF>(o[2 * j][0], o[2 * j][1], j2, j3, pa[0], pa[1], pa[2], pa[3], b0, b1,
-                                       o[2 * j][0], o[2 * j][1], 0.f, 0.f);
-                    ptx::mma_16816<BF>(o[2 * j + 1][0], o[2 * j + 1][1], j2, j3, pa[0], pa[1], pa[2], pa[3], b2,
-                                       b3, o[2 * j + 1][0], o[2 * j + 1][1], 0.f, 0.f);
-                }
+                uint32_t a0, a1, a2, a3;
+                ptx::ldmatrix_x4_trans(addr, a0, a1, a2, a3);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+                    ptx::mma_16816<BF>(o[j][nt][0], o[j][nt][1], o[j][nt][2], o[j][nt][3], a0, a1, a2, a3, pb[nt][0],
+                                       pb[nt][1], o[j][nt][0], o[j][nt][1], o[j][nt][2], o[j][nt][3]);
             }
         }
         // release the stage to the producer
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&empty[stage]);
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        if (GROUPS > 1) turn ^= 1;
 
         if (meta.flags & 2) {
-            // ---- merge the four warps' (m, l, acc) and write the item's partial rows
+            // ---- merge the eight warps' (m, l, acc) and write the item's partial rows.
+            // Warp wq of group 1 and warp wq of group 0 hold fragments of identical layout:
+            // group 1 parks its state in slot wq, group 0 folds it into its registers and
+            // parks the sum, then all consumer threads reduce the four slots.
+            float l_tot[NT][2];
 #pragma unroll
-            for (int r = 0; r < NR; ++r) {
-                float l = l_run[r];
-                l += __shfl_xor_sync(0xffffffffu, l, 1);
-                l += __shfl_xor_sync(0xffffffffu, l, 2);
-                const int g = g0 + 8 * r;
-                if (c4 == 0) {
-                    sML[(warp * GP + g) * 2 + 0] = m_run[r];
-                    sML[(warp * GP + g) * 2 + 1] = l;
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    float l = l_run[nt][i];
+#pragma unroll
+                    for (int sh = 4; sh < 32; sh <<= 1) l += __shfl_xor_sync(0xffffffffu, l, sh);
+                    l_tot[nt][i] = l;
                 }
-                float* ar = sAcc + (size_t)(warp * GP + g) * S::kAccStride;
+            auto park = [&]() {
 #pragma unroll
-                for (int nt = 0; nt < HD / 8; ++nt)
-                    *reinterpret_cast<float2*>(ar + nt * 8 + 2 * c4) = make_float2(o[nt][2 * r], o[nt][2 * r + 1]);
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int g = 8 * nt + 2 * c4 + i;
+                        if (r8 == 0) {
+                            sML[(wq * GP + g) * 2 + 0] = m_run[nt][i];
+                            sML[(wq * GP + g) * 2 + 1] = l_tot[nt][i];
+                        }
+                        float* ar = sAcc + (size_t)(wq * GP + g) * S::kAccStride;
+#pragma unroll
+                        for (int j = 0; j < HD / 16; ++j) {
+                            ar[16 * j + r8] = o[j][nt][i];
+                            ar[16 * j + 8 + r8] = o[j][nt][2 + i];
+                        }
+                    }
+            };
+            if (GROUPS > 1) {
+                if (group == 1) park();
+                ptx::named_bar_sync(1, kConsumers * 32);
+            }
+            if (group == 0) {
+                if (GROUPS > 1) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int g = 8 * nt + 2 * c4 + i;
+                        const float mb = sML[(wq * GP + g) * 2 + 0], lb = sML[(wq * GP + g) * 2 + 1];
+                        const float M = fmaxf(m_run[nt][i], mb);
+                        const float wa = (m_run[nt][i] == -INFINITY) ? 0.f : exp2f(m_run[nt][i] - M);
+                        const float wb = (mb == -INFINITY) ? 0.f : exp2f(mb - M);
+                        const float* ar = sAcc + (size_t)(wq * GP + g) * S::kAccStride;
+#pragma unroll
+                        for (int j = 0; j < HD / 16; ++j) {
+                            o[j][nt][i] = o[j][nt][i] * wa + ar[16 * j + r8] * wb;
+                            o[j][nt][2 + i] = o[j][nt][2 + i] * wa + ar[16 * j + 8 + r8] * wb;
+                        }
+                        l_tot[nt][i] = l_tot[nt][i] * wa + lb * wb;
+                        m_run[nt][i] = M;
+                    }
+                __syncwarp();  // every lane has read slot wq before it is overwritten
+                }
+                park();
             }
             ptx::named_bar_sync(1, kConsumers * 32);
-            const int tid = threadIdx.x;  // 0..127
+            const int tid = threadIdx.x;  // consumer threads come first
             for (int idx = tid; idx < P.G * HD; idx += kConsumers * 32) {
                 const int g = idx / HD, d = idx - g * HD;
                 float M = -INFINITY;
 #pragma unroll
-                for (int w = 0; w < kConsumers; ++w) M = fmaxf(M, sML[(w * GP + g) * 2]);
+                for (int w = 0; w < kGroupWarps; ++w) M = fmaxf(M, sML[(w * GP + g) * 2]);
                 float L = 0.f, A = 0.f;
 #pragma unroll
-                for (int w = 0; w < kConsumers; ++w) {
+                for (int w = 0; w < kGroupWarps; ++w) {
                     const float mw = sML[(w * GP + g) * 2];
                     const float wt = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
                     L += sML[(w * GP + g) * 2 + 1] * wt;
@@ -529,8 +618,13 @@ int encode_rows_map_3d(CUtensorMap* map, const void* base, uint64_t rows, uint32
     const cuuint64_t strides[2] = {(cuuint64_t)row_elems * 2, 128};  // bytes, dims 1 and 2
     const cuuint32_t box[3] = {64, box_rows, row_elems / 64};
     const cuuint32_t estr[3] = {1, 1, 1};
+    CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+    if (const char* e = getenv("REFLEX_B200_L2PROMO")) {  // temporary experiment hook
+        promo = e[0] == '0' ? CU_TENSOR_MAP_L2_PROMOTION_NONE : e[0] == '1' ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+              : e[0] == '2' ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+    }
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : (int)r;
 }
@@ -563,19 +657,22 @@ bool decode_mma_supported(const RfxPagedAttentionArgs* a) {
     if (a->q_start != nullptr || a->max_q_len > 1) return false;  // one query row per request
     const int64_t G = a->num_q_heads / a->num_kv_heads;
     if (G > 16) return false;
+    if ((G * a->head_dim * 2) % 16) return false;  // bulk copies move multiples of 16 bytes
     if (!box_rows_ok(a->block_size)) return false;
-    if (((uintptr_t)a->k_cache % 1024) || ((uintptr_t)a->v_cache % 1024) || ((uintptr_t)a->q % 4)) return false;
+    if (((uintptr_t)a->k_cache % 16) || ((uintptr_t)a->v_cache % 16) || ((uintptr_t)a->q % 16)) return false;
+    if (a->rope_cos && (((uintptr_t)a->rope_cos % 16) || ((uintptr_t)a->rope_sin % 16))) return false;
     if (a->num_blocks * a->num_kv_heads * a->block_size >= (1ll << 31)) return false;
     return true;
 }
 
 int decode_mma_ctas(const RfxPagedAttentionArgs*) { return sm_count(); }
 
-template <typename T, int HD, int GP, int STAGES>
-static int launch_decode_t(const RfxPagedAttentionArgs* a, const PlanPtrs& Pp, const CUtensorMap& km,
-                           const CUtensorMap& vm, const DecodeParams& P) {
+template <typename T, int HD, int GP, int STAGES, int GROUPS = 1>
+static int launch_decode_t(const RfxPagedAttentionArgs* a, const CUtensorMap& km, const CUtensorMap& vm,
+                           const DecodeParams& P) {
     using S = DecodeSmem<HD, GP, STAGES>;
-    auto kern = decode_mma_kernel<T, HD, GP, STAGES>;
+    static_assert(S::total <= 232448, "decode kernel shared memory exceeds the sm_100 per-CTA limit");
+    auto kern = decode_mma_kernel<T, HD, GP, STAGES, GROUPS>;
     static bool attr_set[64] = {};  // per instantiation and device
     int dev = 0;
     cudaGetDevice(&dev);
@@ -584,8 +681,7 @@ static int launch_decode_t(const RfxPagedAttentionArgs* a, const PlanPtrs& Pp, c
         if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "decode smem opt-in (%zu B): %s", S::total, cudaGetErrorString(e));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    (void)Pp;
-    kern<<<decode_mma_ctas(a), kDecodeThreads, S::total, as_stream(a->stream)>>>(km, vm, P);
+    kern<<<decode_mma_ctas(a), (kGroupWarps * GROUPS + 1) * 32, S::total, as_stream(a->stream)>>>(km, vm, P);
     return check_launch("rfx_paged_attention (decode MMA kernel)");
 }
 
@@ -616,7 +712,7 @@ int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const P
     DecodeParams P;
     P.q = a->q; P.block_table = a->block_table;
     P.rcos = a->rope_cos; P.rsin = a->rope_sin; P.rpos = a->rope_positions;
-    P.hdr = Pp.hdr; P.items = Pp.items; P.item_prow = Pp.item_prow;
+    P.hdr = Pp.hdr; P.part_first = Pp.part_first; P.items = Pp.items; P.item_prow = Pp.item_prow;
     P.pm = Pp.m; P.pl = Pp.l; P.pacc = Pp.acc;
     P.num_blocks = a->num_blocks; P.max_blocks = a->max_blocks; P.bt_sb = a->bt_stride_b;
     P.table_rows = a->table_rows;
@@ -624,14 +720,28 @@ int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const P
     P.block_size = (int)a->block_size; P.box_rows = R; P.rope_inter = a->rope_interleaved;
     P.scale_log2 = a->sm_scale * 1.4426950408889634f;
     P.map2d = map2d;
+    {
+        const char* e = getenv("REFLEX_B200_SKIP_MATH");
+        P.skip_math = e ? atoi(e) : 0;
+    }
 
 #define RFX_DECODE_CASE(T)                                                                   \
     if (HD == 128) {                                                                         \
-        if (G <= 8) return launch_decode_t<T, 128, 8, 6>(a, Pp, km, vm, P);                  \
-        return launch_decode_t<T, 128, 16, 5>(a, Pp, km, vm, P);                             \
+        if (G <= 8) return launch_decode_t<T, 128, 8, 6>(a, km, vm, P);                      \
+        return launch_decode_t<T, 128, 16, 5>(a, km, vm, P);                                 \
     } else {                                                                                 \
-        if (G <= 8) return launch_decode_t<T, 64, 8, 8>(a, Pp, km, vm, P);                   \
-        return launch_decode_t<T, 64, 16, 8>(a, Pp, km, vm, P);                              \
+        if (G <= 8) return launch_decode_t<T, 64, 8, 8>(a, km, vm, P);                       \
+        return launch_decode_t<T, 64, 16, 8>(a, km, vm, P);                                  \
+    }
+    {
+        // temporary experiment hook: ring depth
+        const char* e = getenv("REFLEX_B200_STAGES");
+        if (e && a->dtype == RFX_BF16 && HD == 128 && G <= 8) {
+            if (e[0] == '2') return launch_decode_t<__nv_bfloat16, 128, 8, 6, 2>(a, km, vm, P);
+            if (e[0] == '3') return launch_decode_t<__nv_bfloat16, 128, 8, 3>(a, km, vm, P);
+            if (e[0] == '4') return launch_decode_t<__nv_bfloat16, 128, 8, 4>(a, km, vm, P);
+            if (e[0] == '5') return launch_decode_t<__nv_bfloat16, 128, 8, 5>(a, km, vm, P);
+        }
     }
     if (a->dtype == RFX_BF16) { RFX_DECODE_CASE(__nv_bfloat16) }
     RFX_DECODE_CASE(__half)

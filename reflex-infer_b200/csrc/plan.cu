@@ -1,137 +1,119 @@
 // Split-K planning for paged attention, entirely on the device so a step needs no
-// device->host read of the context lengths: one CTA sums the lengths, picks the keys per
-// split, prefix-sums the splits and writes the (request, kv_head, key range) item list
-// that the persistent partial kernels pull from with an atomic work counter.
+// device->host read of the context lengths. One CTA lays the 64-key tiles of every
+// (request, kv_head) pair end to end, cuts that stream into equal runs (one per CTA of the
+// persistent partial kernel, so every CTA streams the same number of bytes whatever the mix
+// of request lengths), and writes the items -- the pieces of pairs inside one run.
 #include "paged_plan.cuh"
 
 namespace rfx {
 
 constexpr int kPlanThreads = 1024;
 
-__device__ inline long long block_sum_ll(long long v, long long* red) {
+// Exclusive scan of two values per thread across the CTA.
+__device__ inline void block_exscan2(long long& a, long long& b, long long (*red)[2], long long& tot_a,
+                                     long long& tot_b) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    __syncthreads();
-    if (lane == 0) red[warp] = v;
-    __syncthreads();
-    long long r = 0;
-    for (int i = 0; i < kPlanThreads / 32; ++i) r += red[i];
-    return r;
-}
-
-// Exclusive scan of one value per thread across the CTA; returns the prefix, *total gets the sum.
-__device__ inline long long block_exscan_ll(long long v, long long* red, long long* total) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    long long inc = v;
+    long long ia = a, ib = b;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-        long long t = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += t;
+        const long long ta = __shfl_up_sync(0xffffffffu, ia, o);
+        const long long tb = __shfl_up_sync(0xffffffffu, ib, o);
+        if (lane >= o) { ia += ta; ib += tb; }
     }
     __syncthreads();
-    if (lane == 31) red[warp] = inc;
+    if (lane == 31) { red[warp][0] = ia; red[warp][1] = ib; }
     __syncthreads();
-    long long base = 0, all = 0;
+    long long ba = 0, bb = 0;
+    tot_a = 0; tot_b = 0;
     for (int i = 0; i < kPlanThreads / 32; ++i) {
-        if (i < warp) base += red[i];
-        all += red[i];
+        if (i < warp) { ba += red[i][0]; bb += red[i][1]; }
+        tot_a += red[i][0]; tot_b += red[i][1];
     }
-    *total = all;
-    return base + inc - v;
+    a = ba + ia - a;
+    b = bb + ib - b;
 }
 
 __global__ void __launch_bounds__(kPlanThreads)
 plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_start, int B, int Hkv,
-            int G, long long max_items, long long cap_rows, long long target_chunk, int ctas,
-            int32_t* hdr, int32_t* split_base, int32_t* prow_base, int4* items, int32_t* item_prow) {
-    __shared__ long long red[kPlanThreads / 32];
-    __shared__ long long s_chunk;
+            int G, long long max_parts, long long target_chunk, int parts_hint, int32_t* hdr,
+            int32_t* pair_item_begin, int32_t* part_first, int4* items, int32_t* item_prow) {
+    __shared__ long long red[kPlanThreads / 32][2];
     const int tid = threadIdx.x;
     const int per = (B + kPlanThreads - 1) / kPlanThreads;  // requests per thread, contiguous
     const int b0 = min(B, tid * per), b1 = min(B, b0 + per);
 
-    long long my_tokens = 0;
-    for (int b = b0; b < b1; ++b) my_tokens += max(0, ctx_lens[b]);
-    const long long total_tokens = block_sum_ll(my_tokens, red);
+    // tiles before each request (per kv head), and in total
+    long long tile_pre = 0, unused = 0, tiles_all, t2;
+    for (int b = b0; b < b1; ++b) tile_pre += (max(0, ctx_lens[b]) + kPlanTile - 1) / kPlanTile;
+    block_exscan2(tile_pre, unused, red, tiles_all, t2);
+    const long long T = tiles_all * Hkv;
 
-    long long chunk;
-    if (target_chunk > 0) {
-        chunk = (target_chunk + 63) / 64 * 64;
-    } else {
-        // Keys per CTA, then the split length that balances per-item overhead (~48 keys'
-        // worth of time) against the tail left by the last item: sqrt(2*48*per_cta).
-        const double per_cta = (double)total_tokens * Hkv / (double)max(1, ctas);
-        chunk = (long long)(sqrt(96.0 * per_cta) / 64.0 + 0.5) * 64;
-        if (chunk < 128) chunk = 128;
-    }
-    // Grow the split length until items and partial rows fit the workspace.
-    for (int it = 0; it < 40; ++it) {
-        long long my_items = 0, my_rows = 0;
+    // tiles per run
+    long long parts = parts_hint;
+    if (target_chunk > 0) parts = (T + (target_chunk + kPlanTile - 1) / kPlanTile - 1) /
+                                  ((target_chunk + kPlanTile - 1) / kPlanTile);
+    if (parts > max_parts) parts = max_parts;
+    if (parts < 1) parts = 1;
+    const long long q = T > 0 ? (T + parts - 1) / parts : 1;
+    const long long n_parts = T > 0 ? (T + q - 1) / q : 0;
+
+    // items and partial rows before each request
+    long long item_pre = 0, row_pre = 0, n_items, n_rows;
+    {
+        long long pre = tile_pre;
         for (int b = b0; b < b1; ++b) {
-            const long long c = max(0, ctx_lens[b]);
-            const long long ns = c > 0 ? (c + chunk - 1) / chunk : 1;
+            const long long tb = (max(0, ctx_lens[b]) + kPlanTile - 1) / kPlanTile;
             const long long nq = q_start ? max(0, q_start[b + 1] - q_start[b]) : 1;
-            my_items += ns;
-            my_rows += ns * nq;
+            if (tb > 0)
+                for (int h = 0; h < Hkv; ++h) {
+                    const long long off = pre * Hkv + h * tb;
+                    const long long ni = (off + tb - 1) / q - off / q + 1;
+                    item_pre += ni;
+                    row_pre += ni * nq * G;
+                }
+            pre += tb;
         }
-        const long long n_items = block_sum_ll(my_items, red) * Hkv;
-        const long long n_rows = block_sum_ll(my_rows, red) * Hkv * G;
-        if (n_items <= max_items && n_rows <= cap_rows) break;
-        chunk *= 2;
     }
-    if (tid == 0) s_chunk = chunk;
-    __syncthreads();
-    chunk = s_chunk;
+    block_exscan2(item_pre, row_pre, red, n_items, n_rows);
 
-    long long my_splits = 0, my_rows = 0;
-    for (int b = b0; b < b1; ++b) {
-        const long long c = max(0, ctx_lens[b]);
-        const long long ns = c > 0 ? (c + chunk - 1) / chunk : 1;
-        const long long nq = q_start ? max(0, q_start[b + 1] - q_start[b]) : 1;
-        my_splits += ns;
-        my_rows += ns * nq * Hkv * G;
-    }
-    long long tot_splits, tot_rows;
-    long long sp = block_exscan_ll(my_splits, red, &tot_splits);
-    long long rw = block_exscan_ll(my_rows, red, &tot_rows);
-
+    long long pre = tile_pre, it = item_pre, rw = row_pre;
     for (int b = b0; b < b1; ++b) {
         const int c = max(0, ctx_lens[b]);
-        const int ns = c > 0 ? (int)((c + chunk - 1) / chunk) : 1;
-        const int nq = q_start ? max(0, q_start[b + 1] - q_start[b]) : 1;
-        split_base[b] = (int)sp;
-        prow_base[b] = (int)rw;
-        int len = (c + ns - 1) / ns;
-        len = (len + 63) / 64 * 64;
+        const long long tb = (c + kPlanTile - 1) / kPlanTile;
+        const long long nq = q_start ? max(0, q_start[b + 1] - q_start[b]) : 1;
         for (int h = 0; h < Hkv; ++h) {
-            for (int s = 0; s < ns; ++s) {
-                const long long item = (long long)Hkv * sp + (long long)h * ns + s;
-                const int kb = min(c, s * len), ke = min(c, (s + 1) * len);
-                items[item] = make_int4(b, h, kb, ke);
-                item_prow[item] = (int)(rw + ((long long)h * ns + s) * nq * G);
+            pair_item_begin[(long long)b * Hkv + h] = (int)it;
+            if (tb == 0) continue;
+            const long long off = pre * Hkv + h * tb;
+            const long long p0 = off / q, p1 = (off + tb - 1) / q;
+            for (long long p = p0; p <= p1; ++p) {
+                const long long s = max(off, p * q), e = min(off + tb, (p + 1) * q);
+                items[it] = make_int4(b, h, (int)((s - off) * kPlanTile), min(c, (int)((e - off) * kPlanTile)));
+                item_prow[it] = (int)rw;
+                if (s == p * q) part_first[p] = (int)it;
+                ++it;
+                rw += nq * G;
             }
         }
-        sp += ns;
-        rw += (long long)ns * nq * Hkv * G;
+        pre += tb;
     }
     if (tid == 0) {
-        split_base[B] = (int)tot_splits;
-        prow_base[B] = (int)tot_rows;
-        item_prow[tot_splits * Hkv] = (int)tot_rows;
-        hdr[HdrNumItems] = (int)(tot_splits * Hkv);
-        hdr[HdrChunk] = (int)chunk;
-        hdr[HdrWorkCounter] = 0;
+        pair_item_begin[(long long)B * Hkv] = (int)n_items;
+        part_first[n_parts] = (int)n_items;
+        item_prow[n_items] = (int)n_rows;
+        hdr[HdrNumItems] = (int)n_items;
+        hdr[HdrTilesPerPart] = (int)q;
+        hdr[HdrNumParts] = (int)n_parts;
         hdr[HdrStatus] = 0;
-        hdr[HdrTotalRows] = (int)tot_rows;
+        hdr[HdrTotalRows] = (int)n_rows;
     }
 }
 
-int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int ctas_hint) {
+int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int parts_hint) {
     const int G = (int)(a->num_q_heads / a->num_kv_heads);
     plan_kernel<<<1, kPlanThreads, 0, as_stream(a->stream)>>>(
-        a->context_lens, a->q_start, (int)a->batch, (int)a->num_kv_heads, G, L.max_items, L.cap_rows,
-        a->target_chunk, ctas_hint, P.hdr, P.split_base, P.prow_base, P.items, P.item_prow);
+        a->context_lens, a->q_start, (int)a->batch, (int)a->num_kv_heads, G, L.max_parts, a->target_chunk,
+        parts_hint, P.hdr, P.pair_item_begin, P.part_first, P.items, P.item_prow);
     return check_launch("rfx_paged_attention_plan");
 }
 

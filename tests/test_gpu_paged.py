@@ -141,6 +141,23 @@ def test_stale_tail_and_nan_pages_do_not_leak(native):
         torch.testing.assert_close(out.cpu().float(), ref.float(), atol=2e-2, rtol=2e-2)
 
 
+def test_tensor_core_kernel_is_selected(native):
+    """The benchmark shapes must run on the TMA/MMA kernel, the odd ones on the scalar one."""
+    from kernels.attention import PagedAttentionCall
+    def kind(dtype, bs, D, G, **kw):
+        kc = torch.zeros(8, 2, bs, D, dtype=dtype, device=DEV)
+        q = torch.zeros(3, 2 * G, D, dtype=dtype, device=DEV)
+        bt = torch.zeros(3, 2, dtype=torch.int64, device=DEV)
+        return PagedAttentionCall(q, kc, kc.clone(), bt, torch.ones(3, dtype=torch.int32, device=DEV), **kw).kernel_kind
+    assert kind(torch.bfloat16, 16, 128, 8) == 1      # configuration 2
+    assert kind(torch.bfloat16, 32, 128, 8) == 1      # configuration 4
+    assert kind(torch.bfloat16, 16, 128, 7) == 1      # configuration 5's head ratio
+    assert kind(torch.float16, 64, 64, 16) == 1
+    assert kind(torch.float32, 16, 64, 1) == 0        # configuration 1 is fp32
+    assert kind(torch.bfloat16, 4, 128, 8) == 0
+    assert kind(torch.bfloat16, 16, 128, 8, force_generic=True) == 0
+
+
 def test_empty_requests_give_zeros(native):
     kc = golden_io.pattern((8, 2, 16, 128), torch.bfloat16, 1).to(DEV)
     vc = golden_io.pattern((8, 2, 16, 128), torch.bfloat16, 2).to(DEV)
