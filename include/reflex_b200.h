@@ -259,6 +259,27 @@ int rfx_paged_attention_partials(const RfxPagedAttentionArgs* a);
 int rfx_paged_attention_kernel_kind(const RfxPagedAttentionArgs* a);
 int rfx_paged_attention_combine(const RfxPagedAttentionArgs* a);
 
+/* Paged attention for callers that cannot hand over a workspace. This entry point has no
+ * counterpart in the reference. Some hosts of this library may not allocate device memory
+ * at the point where they run attention: a runtime that took all of its memory up front and
+ * forbids allocation afterwards, a plugin called inside someone else's memory pool, code on
+ * a real-time path where cudaMalloc's implicit synchronisation is not acceptable. For them
+ * the split-K plan and partials live in an 8 MiB array that is part of the library image
+ * (rfx_paged_attention_static_capacity() bytes; every GPU that loads the library holds it
+ * until the process exits). `workspace`, `workspace_bytes` and `reuse_plan` are ignored;
+ * everything else is as for rfx_paged_attention, and so is the result. Problems whose
+ * rfx_paged_attention_workspace_bytes() exceeds the capacity are rejected with
+ * RFX_WORKSPACE_TOO_SMALL (an 8 MiB array covers e.g. 32 requests with 16 query / 2 kv heads
+ * of head_dim 128, one query row each). The call allocates and frees nothing.
+ * The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current; the driver may load the array into
+ * device memory at that moment); make that first call outside any stream capture. All calls on a device share the one array: it still holds the previous call's
+ * plan and partials when the next call starts (each call rewrites what it reads, the status
+ * word included), and two calls that overlap on the GPU -- different streams, or different
+ * host threads -- race on it. Serialise them, or give the others a workspace of their own. */
+size_t rfx_paged_attention_static_capacity(void);
+int rfx_paged_attention_static(const RfxPagedAttentionArgs* a);
+
 /* Split-K combine on caller-provided partials (the recurrence of
  * kernels/softmax/triton_softmax.py:84-89 with an accumulator,
  * triton_fused_attention.py:205-227): rows r = 0..rows-1 each own splits

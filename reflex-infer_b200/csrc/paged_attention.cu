@@ -104,6 +104,50 @@ extern "C" int rfx_paged_attention_combine(const RfxPagedAttentionArgs* a) {
     return rfx::run_stages(a, "rfx_paged_attention_combine", rfx::kStageCombine);
 }
 
+// ---- paged attention without a caller workspace ----------------------------------------
+// Scratch for rfx_paged_attention_static: one fixed array in device memory, part of the
+// library image. Every GPU that loads the library holds these bytes until the process exits.
+namespace rfx {
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+// Device address of the array per device ordinal, resolved on the first call on that device.
+static void* g_static_scratch_ptr[64] = {};
+}  // namespace rfx
+
+extern "C" size_t rfx_paged_attention_static_capacity(void) { return rfx::kStaticScratchBytes; }
+
+extern "C" int rfx_paged_attention_static(const RfxPagedAttentionArgs* a) {
+    using namespace rfx;
+    const char* name = "rfx_paged_attention_static";
+    int st = validate(a, name);
+    if (st != RFX_SUCCESS) return st;
+    st = check_device();
+    if (st != RFX_SUCCESS) return st;
+    const PlanLayout L = layout_of(a);
+    if (L.total > kStaticScratchBytes)
+        return fail(RFX_WORKSPACE_TOO_SMALL,
+                    "%s: this problem needs %zu B of scratch, the built-in array holds %zu B; use "
+                    "rfx_paged_attention with a caller workspace",
+                    name, L.total, kStaticScratchBytes);
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "%s: cudaGetDevice: %s", name, cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) return fail(RFX_UNSUPPORTED_DEVICE, "%s: device ordinal %d out of range", name, dev);
+    if (!g_static_scratch_ptr[dev]) {
+        // In host code the array's name is only a handle; a kernel needs its device address.
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p)
+            return fail(RFX_CUDA_ERROR, "%s: cudaGetSymbolAddress: %s", name, cudaGetErrorString(e));
+        g_static_scratch_ptr[dev] = p;
+    }
+    RfxPagedAttentionArgs b = *a;
+    b.workspace = g_static_scratch_ptr[dev];
+    b.workspace_bytes = kStaticScratchBytes;
+    b.reuse_plan = 0;  // the array is shared by every caller: always plan afresh
+    return run_stages(&b, name, kStagePlan | kStagePartials | kStageCombine);
+}
+
 extern "C" int rfx_paged_attention_status(const void* workspace, rfx_stream stream, int* status_word_host) {
     using namespace rfx;
     if (!workspace || !status_word_host) return fail(RFX_INVALID_ARGUMENT, "rfx_paged_attention_status: null pointer");

@@ -147,6 +147,8 @@ EXPORTS = {
     "rfx_paged_attention_partials": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_paged_attention_combine": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_paged_attention_kernel_kind": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
+    "rfx_paged_attention_static_capacity": (C.c_size_t, []),
+    "rfx_paged_attention_static": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_splitk_combine": (C.c_int, [C.POINTER(CombineArgs)]),
     "rfx_paged_attention_status": (C.c_int, [vp, vp, C.POINTER(C.c_int)]),
 }

@@ -225,6 +225,16 @@ class PagedAttentionCall:
         self._call(self._lib.rfx_paged_attention)
         return self.out
 
+    def run_static(self) -> torch.Tensor:
+        """Same result as ``run()``, but the plan and the split-K partials go to the 8 MiB
+        scratch array built into the library instead of this call's workspace, and nothing
+        is allocated. For hosts that may not allocate device memory when they run attention
+        (memory handed out up front, a foreign memory pool, a latency-critical thread).
+        Raises ``RuntimeError`` (WorkspaceTooSmall) when the problem needs more than the
+        array holds. All callers on a GPU share the array, so calls must not overlap there."""
+        self._call(self._lib.rfx_paged_attention_static)
+        return self.out
+
     def plan(self) -> None:
         self._call(self._lib.rfx_paged_attention_plan)
 
