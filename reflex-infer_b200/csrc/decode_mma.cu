@@ -2,23 +2,23 @@
 //
 // HBM-bound: every item (a run of 64-key tiles of one (request, kv_head) pair) streams its
 // K and V pages exactly once. One persistent CTA per SM owns one equal run of the tile
-// stream and has one producer warp and eight consumer warps in two groups:
+// stream and has one producer warp and one (optionally two) group of four consumer warps:
 //   producer : loads its run's item descriptors in one round trip, keeps the block-table
 //              entries of the current and the next item in registers (32 per lane-window),
 //              and issues one TMA tile copy per page for K and for V into a ring of 64-key
 //              stages; each copy lands the page as [half][row][128 B] with the 128-byte
 //              swizzle, completion counted on the stage's mbarrier. With an item's first
-//              stage it also bulk-copies the G query rows and the RoPE table row;
-//   consumers: stages alternate between the two groups, so two stages are in work at any
-//              time and the MMA/softmax latency of one hides behind the other. In a group
-//              each warp takes 16 of the 64 keys: S = Q.K^T with the G query heads as the
-//              (padded) 16 MMA rows, online softmax with quad shuffles, O += P.V, all through
-//              m16n8k16 warp MMAs fed by conflict-free ldmatrix. At the item's last stage the
-//              eight warps merge (m, l, acc) through shared memory and write one partial.
+//              stage it also bulk-copies the G query rows and the RoPE table rows;
+//   consumers: each warp takes 16 of the stage's 64 keys as the 16 MMA rows and the group's
+//              heads as the columns: S^T = K.Q^T, softmax down the columns, O^T += V^T.P^T,
+//              all through m16n8k16 warp MMAs fed by conflict-free ldmatrix. At the item's
+//              last stage the warps merge (m, l, acc) through shared memory and write one
+//              partial. With two groups, stages alternate between them.
 // RoPE is fused into the Q load with torch's per-op rounding.
 //
 // Algorithmic bytes per item: 2 * keys * D * e (K and V). Arithmetic is G FLOP/byte, far
-// below what the warp MMA path sustains, so the kernel's roofline is HBM bandwidth.
+// below what the warp MMA path sustains; the kernel's roofline is HBM bandwidth, and on a
+// 1000 W part streaming at full rate what is left to tune is the energy spent per byte.
 #include <stdlib.h>
 
 #include <type_traits>
