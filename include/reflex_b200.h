@@ -253,9 +253,11 @@ int rfx_paged_attention(const RfxPagedAttentionArgs* a);
  * CUDA graph, per-kernel timing): the split-K partial kernel over an existing plan, and
  * the combine that turns the partials into `out` and re-arms the plan for the next use. */
 int rfx_paged_attention_partials(const RfxPagedAttentionArgs* a);
-/* Which partial kernel the arguments select: 1 = TMA + tensor-core decode kernel (16-bit,
- * head_dim 64/128, one query row per request, group <= 16, page size a divisor or multiple
- * of 64 and >= 8), 0 = scalar kernel, negative = invalid arguments. */
+/* Which kernel the arguments select: 2 = tcgen05 prefill kernel (16-bit, head_dim 128, ragged
+ * query chunks given by q_start, queries already rotated, page size >= 8 dividing or a
+ * multiple of 128; it needs no plan and no combine), 1 = TMA + warp-MMA decode kernel
+ * (16-bit, head_dim 64/128, one query row per request, group <= 16, page size a divisor or
+ * multiple of 64 and >= 8), 0 = scalar kernel, negative = invalid arguments. */
 int rfx_paged_attention_kernel_kind(const RfxPagedAttentionArgs* a);
 int rfx_paged_attention_combine(const RfxPagedAttentionArgs* a);
 

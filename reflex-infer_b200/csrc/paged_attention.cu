@@ -71,6 +71,13 @@ static int run_stages(const RfxPagedAttentionArgs* a, const char* name, int stag
         return fail(RFX_WORKSPACE_TOO_SMALL, "%s: workspace %zu B < %zu B", name, a->workspace_bytes, L.total);
     RFX_REQUIRE(((uintptr_t)a->workspace % 256) == 0, "%s: workspace must be 256-byte aligned", name);
     const PlanPtrs P = plan_ptrs(a->workspace, L);
+    if (prefill_paged_supported(a)) {
+        // Query chunks on the tcgen05 kernel: whole rows per CTA, so no plan and no combine.
+        if (!(stages & kStagePartials)) return RFX_SUCCESS;
+        cudaError_t e = cudaMemsetAsync(P.hdr + HdrStatus, 0, sizeof(int32_t), as_stream(a->stream));
+        if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "%s: cudaMemsetAsync: %s", name, cudaGetErrorString(e));
+        return launch_prefill_paged(a, P.hdr + HdrStatus);
+    }
     const bool mma = decode_mma_supported(a);
     if (stages & kStagePlan) {
         st = launch_plan(a, L, P, mma ? decode_mma_ctas(a) : sm_count() * 4);
@@ -97,6 +104,7 @@ extern "C" int rfx_paged_attention_partials(const RfxPagedAttentionArgs* a) {
 
 extern "C" int rfx_paged_attention_kernel_kind(const RfxPagedAttentionArgs* a) {
     if (rfx::validate(a, "rfx_paged_attention_kernel_kind") != RFX_SUCCESS) return -1;
+    if (rfx::prefill_paged_supported(a)) return 2;
     return rfx::decode_mma_supported(a) ? 1 : 0;
 }
 

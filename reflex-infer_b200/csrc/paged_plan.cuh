@@ -96,5 +96,8 @@ int launch_paged_combine(const RfxPagedAttentionArgs* a, const PlanLayout& L, co
 bool decode_mma_supported(const RfxPagedAttentionArgs* a);
 int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P);
 int decode_mma_ctas(const RfxPagedAttentionArgs* a);
+// tcgen05 kernel for ragged query chunks (prefill_tc.cu).
+bool prefill_paged_supported(const RfxPagedAttentionArgs* a);
+int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word);
 
 }  // namespace rfx

@@ -1,0 +1,515 @@
+// Prefill / chunked-prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// One CTA owns one query tile: T consecutive query tokens of one request times the G query
+// heads that share one kv head, T*G <= 128 rows (row = one (token, head) pair), so a K/V tile
+// is read once for the whole GQA group. Six warps:
+//   warps 0-3  softmax: thread r owns row r (TMEM lane r). Reads S from TMEM, keeps the row
+//              maximum and sum in registers (no shuffles), writes P as bf16 back into the
+//              TMEM columns S occupied, and rescales O in TMEM only when a row maximum grew
+//              by more than 2^8 (stale maxima are exact as long as the final 1/l uses the
+//              same reference); epilogue O/l -> global.
+//   warp 4     TMA producer: Q once, then K and V tiles of 128 keys, one box per page (or
+//              one box per tile for dense K/V), two stages each, 128-byte swizzle.
+//   warp 5     MMA issuer: S_j = Q.K_j^T (8 x tcgen05.mma 128x128x16 from shared-memory
+//              descriptors) into one of two S buffers, then O += P_{j-1}.V_{j-1} with P read
+//              from TMEM and V as an MN-major shared-memory operand; S_j overlaps the softmax
+//              of tile j-1. Completion through tcgen05.commit on mbarriers.
+// TMEM: columns [0,128) S0/P0, [128,256) S1/P1, [256,384) O (fp32); 512 allocated.
+//
+// Causal masking is bottom-right aligned: token t of n sees keys 0..ctx-n+t; K tiles wholly
+// above the diagonal are never loaded. Tensor-pipe bound: 4*rows*keys*D FLOPs per tile pair.
+#include <stdlib.h>
+
+#include <type_traits>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace rfx {
+
+constexpr int kPfThreads = 192;
+constexpr int kPfKeys = 128;          // keys per K/V tile
+constexpr int kPfHD = 128;            // head_dim
+constexpr int kPfHalfBytes = 128 * 128;  // one 64-wide half of a 128-row tile
+constexpr int kPfTileBytes = 2 * kPfHalfBytes;
+constexpr int kPfKvStages = 2;
+constexpr float kPfRescaleTau = 8.0f;  // log2 units
+
+struct PrefillParams {
+    void* out;
+    int64_t out_tok_stride, out_head_stride;  // elements
+    const int64_t* block_table;                // paged K/V, or nullptr for dense
+    const int32_t* ctx_lens;                   // [B] keys per request (paged)
+    const int32_t* q_start;                    // [B+1] first query row per request (paged)
+    int32_t* status;                           // optional device status word
+    int64_t bt_sb, max_blocks, num_blocks;
+    int B, Hq, Hkv, G, T;                      // T = query tokens per tile = 128 / G
+    int Sq, Sk;                                // dense sizes (paged: Sq = host bound on rows per request)
+    int block_size, box_rows, boxes_per_tile;  // K/V boxes: rows per TMA box, boxes per 128-key tile
+    int n_qtiles;                              // tiles per request = ceil(Sq / T)
+    int head_major_rows;                       // 0: row = t*G + g (paged Q [N,Hq,D]); 1: row = g*T + t (dense [B,H,S,D])
+    int causal;
+    float scale_log2;
+};
+
+struct PfSmem {
+    static constexpr size_t off_q = 0;
+    static constexpr size_t off_k = kPfTileBytes;
+    static constexpr size_t off_v = off_k + (size_t)kPfKvStages * kPfTileBytes;
+    static constexpr size_t off_bars = off_v + (size_t)kPfKvStages * kPfTileBytes;
+    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2]
+    static constexpr int n_bars = 1 + 4 * kPfKvStages + 6;
+    static constexpr size_t off_misc = off_bars + 8 * n_bars;
+    static constexpr size_t total = off_misc + 64 + 1024;
+};
+
+enum PfBar { PF_QFULL = 0, PF_KFULL = 1, PF_KEMPTY = 3, PF_VFULL = 5, PF_VEMPTY = 7, PF_SFULL = 9, PF_PFULL = 11,
+             PF_PVDONE = 13 };
+
+template <typename T>
+__global__ void __launch_bounds__(kPfThreads, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+                  const __grid_constant__ CUtensorMap vmap, const PrefillParams P) {
+    constexpr bool BF = std::is_same<T, __nv_bfloat16>::value;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
+    unsigned char* sQ = smem + PfSmem::off_q;
+    unsigned char* sK = smem + PfSmem::off_k;
+    unsigned char* sV = smem + PfSmem::off_v;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PfSmem::off_bars);
+    uint32_t* misc = reinterpret_cast<uint32_t*>(smem + PfSmem::off_misc);  // [0] TMEM base, [1] abort flag
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- which tile: largest query tiles first (they have the most K tiles under causal masking)
+    const int pairs = P.B * P.Hkv;
+    const int qt = P.n_qtiles - 1 - (int)(blockIdx.x / pairs);
+    const int pair = (int)(blockIdx.x % pairs);
+    const int b = pair / P.Hkv, hkv = pair % P.Hkv;
+    const int q0 = P.q_start ? P.q_start[b] : 0;
+    const int n_q = P.q_start ? (P.q_start[b + 1] - q0) : P.Sq;
+    const int ctx = P.ctx_lens ? max(0, P.ctx_lens[b]) : P.Sk;
+    const int tok0 = qt * P.T;
+    if (tok0 >= n_q) return;  // uniform over the CTA; nothing allocated yet
+    const int off = ctx - n_q;                      // bottom-right: token t sees keys <= t + off
+    const int last_tok = min(n_q, tok0 + P.T) - 1;
+    const int kv_end = P.causal ? max(0, min(ctx, last_tok + off + 1)) : ctx;
+    const int n_kv = (kv_end + kPfKeys - 1) / kPfKeys;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < PfSmem::n_bars; ++i)
+            ptx::mbar_init(&bars[i], (i == PF_PFULL || i == PF_PFULL + 1) ? 128u : 1u);
+        misc[1] = 0;
+        ptx::fence_barrier_init();
+    }
+    if (warp == 5) ptx::tmem_alloc(&misc[0], 512);
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem = misc[0];
+    volatile uint32_t* abort_flag = &misc[1];
+
+    auto give_up = [&]() {
+        if (P.status) atomicOr(P.status, 1);
+        *abort_flag = 1;
+    };
+
+    if (warp == 4) {
+        // ------------------------------------------------------------------ TMA producer --
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&qmap);
+            ptx::prefetch_tensormap(&kmap);
+            ptx::prefetch_tensormap(&vmap);
+            // Q: two 64-wide halves; rows beyond T*G stay stale and are never stored
+            ptx::mbar_arrive_expect_tx(&bars[PF_QFULL], 2u * (uint32_t)(P.T * P.G) * 128u);
+            for (int h = 0; h < 2; ++h) {
+                if (P.head_major_rows)
+                    ptx::tma_load_3d(sQ + h * kPfHalfBytes, &qmap, &bars[PF_QFULL], h * 64, tok0, b * P.Hq + hkv * P.G);
+                else
+                    ptx::tma_load_3d(sQ + h * kPfHalfBytes, &qmap, &bars[PF_QFULL], h * 64, hkv * P.G, q0 + tok0);
+            }
+        }
+        const int R = P.box_rows;
+        for (int j = 0; j < n_kv; ++j) {
+            const int st = j % kPfKvStages;
+            const uint32_t par = (uint32_t)((j / kPfKvStages) & 1);
+            const int key0 = j * kPfKeys;
+            // rows of this tile's boxes: lane i owns box i
+            int row = -1;
+            if (lane < P.boxes_per_tile) {
+                const int key = key0 + lane * R;
+                if (key < kv_end) {
+                    if (P.block_table) {
+                        const int64_t lb = key / P.block_size;
+                        int64_t page = lb < P.max_blocks ? P.block_table[(int64_t)b * P.bt_sb + lb] : -1;
+                        if (page >= 0 && page < P.num_blocks)
+                            row = (int)((page * P.Hkv + hkv) * P.block_size + (key - lb * P.block_size));
+                        else if (P.status) atomicOr(P.status, 2);
+                    } else {
+                        row = (b * P.Hkv + hkv) * P.Sk + key;
+                    }
+                }
+            }
+            const unsigned have = __ballot_sync(0xffffffffu, row >= 0);
+            const uint32_t tx = (uint32_t)__popc(have) * (uint32_t)R * 128u * 2u;
+            for (int which = 0; which < 2; ++which) {  // 0: K, 1: V
+                uint64_t* fullb = &bars[(which ? PF_VFULL : PF_KFULL) + st];
+                uint64_t* emptyb = &bars[(which ? PF_VEMPTY : PF_KEMPTY) + st];
+                int ok = 1;
+                if (lane == 0) ok = ptx::mbar_wait_bounded(emptyb, par ^ 1u) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok || *abort_flag) { if (lane == 0) give_up(); goto done; }
+                if (lane == 0) ptx::mbar_arrive_expect_tx(fullb, tx);
+                __syncwarp();
+                if (row >= 0) {
+                    unsigned char* dst = (which ? sV : sK) + (size_t)st * kPfTileBytes + (size_t)lane * R * 128;
+                    const CUtensorMap* m = which ? &vmap : &kmap;
+                    ptx::tma_load_2d(dst, m, fullb, 0, row);
+                    ptx::tma_load_2d(dst + kPfHalfBytes, m, fullb, 64, row);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------- MMA issuer --
+        constexpr uint32_t idesc_s = ptx::umma_idesc_f16(128, 128, BF ? 1 : 0, 0, 0);   // Q, K both K-major
+        constexpr uint32_t idesc_o = ptx::umma_idesc_f16(128, 128, BF ? 1 : 0, 0, 1);   // P (TMEM), V MN-major
+        const uint32_t q_addr = ptx::smem_u32(sQ);
+        auto issue_pv = [&](int jj) -> bool {
+            const int bb = jj & 1, st = jj % kPfKvStages;
+            int ok = 1;
+            if (lane == 0) {
+                ok = ptx::mbar_wait_bounded(&bars[PF_PFULL + bb], (uint32_t)((jj >> 1) & 1)) &&
+                     ptx::mbar_wait_bounded(&bars[PF_VFULL + st], (uint32_t)((jj / kPfKvStages) & 1));
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok || *abort_flag) return false;
+            // keys at or past kv_end carry probability zero but may hold NaN patterns: clear those V rows
+            const int valid = kv_end - jj * kPfKeys;
+            if (valid < kPfKeys) {
+                unsigned char* vt = sV + (size_t)st * kPfTileBytes;
+                for (int i = lane; i < (kPfKeys - valid) * 16; i += 32) {
+                    const int r = valid + i / 16, c = i % 16;
+                    *reinterpret_cast<uint4*>(vt + (size_t)(c >> 3) * kPfHalfBytes + (size_t)r * 128 + (size_t)(c & 7) * 16) =
+                        make_uint4(0, 0, 0, 0);
+                }
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+            }
+            ptx::tc_fence_after_sync();
+            if (lane == 0) {
+                const uint32_t v_addr = ptx::smem_u32(sV + (size_t)st * kPfTileBytes);
+#pragma unroll
+                for (int ks = 0; ks < kPfKeys / 16; ++ks) {
+                    const uint64_t bd = ptx::umma_desc_sw128(v_addr + ks * 2048, kPfHalfBytes, 1024);
+                    ptx::umma_ts(tmem + 256, tmem + bb * 128 + ks * 8, bd, idesc_o, (jj > 0 || ks > 0) ? 1u : 0u);
+                }
+                ptx::umma_commit(&bars[PF_VEMPTY + st]);
+                ptx::umma_commit(&bars[PF_PVDONE + bb]);
+            }
+            __syncwarp();
+            return true;
+        };
+        {
+            int ok = 1;
+            if (lane == 0) ok = ptx::mbar_wait_bounded(&bars[PF_QFULL], 0) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) { if (lane == 0) give_up(); goto done; }
+        }
+        for (int j = 0; j < n_kv; ++j) {
+            const int bb = j & 1, st = j % kPfKvStages;
+            int ok = 1;
+            if (lane == 0) {
+                ok = ptx::mbar_wait_bounded(&bars[PF_KFULL + st], (uint32_t)((j / kPfKvStages) & 1)) ? 1 : 0;
+                // S buffer bb is free once P.V of tile j-2 has finished
+                if (ok && j >= 2) ok = ptx::mbar_wait_bounded(&bars[PF_PVDONE + bb], (uint32_t)(((j - 2) >> 1) & 1)) ? 1 : 0;
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok || *abort_flag) { if (lane == 0) give_up(); goto done; }
+            ptx::tc_fence_after_sync();
+            if (lane == 0) {
+                const uint32_t k_addr = ptx::smem_u32(sK + (size_t)st * kPfTileBytes);
+#pragma unroll
+                for (int ks = 0; ks < kPfHD / 16; ++ks) {
+                    const uint32_t o2 = (uint32_t)(ks >> 2) * kPfHalfBytes + (uint32_t)(ks & 3) * 32u;
+                    ptx::umma_ss(tmem + bb * 128, ptx::umma_desc_sw128(q_addr + o2, 16, 1024),
+                                 ptx::umma_desc_sw128(k_addr + o2, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+                }
+                ptx::umma_commit(&bars[PF_KEMPTY + st]);
+                ptx::umma_commit(&bars[PF_SFULL + bb]);
+            }
+            __syncwarp();
+            if (j >= 1 && !issue_pv(j - 1)) { if (lane == 0) give_up(); goto done; }
+        }
+        if (n_kv >= 1 && !issue_pv(n_kv - 1)) { if (lane == 0) give_up(); goto done; }
+    } else {
+        // ---------------------------------------------------------------- softmax warps --
+        const int r = warp * 32 + lane;                       // row of the tile = TMEM lane
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        const int rows_used = P.T * P.G;
+        const int t_loc = P.head_major_rows ? (r % P.T) : (r / P.G);
+        const int g = P.head_major_rows ? (r / P.T) : (r % P.G);
+        const int tok = tok0 + t_loc;
+        const bool row_live = r < rows_used && tok < n_q;
+        const int last_key = P.causal ? min(ctx - 1, tok + off) : ctx - 1;  // keys 0..last_key visible (live rows)
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok_all = true;
+        for (int j = 0; j < n_kv && ok_all; ++j) {
+            const int bb = j & 1;
+            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&bars[PF_SFULL + bb], (uint32_t)((j >> 1) & 1)) ? 1 : 0) ||
+                *abort_flag) {
+                if (lane == 0) give_up();
+                ok_all = false;
+                break;
+            }
+            ptx::tc_fence_after_sync();
+            const int key0 = j * kPfKeys;
+            const uint32_t s_addr = lane_base + bb * 128;
+            const bool need_mask = key0 + kPfKeys - 1 > last_key || !row_live;
+            // pass 1: row maximum of the scaled scores
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                ptx::tmem_ld32(s_addr + c * 32, v);
+                ptx::tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float x = __uint_as_float(v[i]);
+                    if (need_mask && (!row_live || key0 + c * 32 + i > last_key)) x = -INFINITY;
+                    mx = fmaxf(mx, x);
+                }
+            }
+            mx *= P.scale_log2;  // scale > 0, so the order of max and scale does not matter
+            const bool grow = mx > m_run + kPfRescaleTau;  // also true for the first finite maximum
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = fmaxf(m_run, mx);
+                const float alpha = (m_new == -INFINITY) ? 1.f : ptx::ex2(m_run - m_new);
+                if (j > 0) {
+                    // O holds tiles 0..j-1 once P.V of tile j-1 is done
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&bars[PF_PVDONE + ((j - 1) & 1)],
+                                                                       (uint32_t)(((j - 1) >> 1) & 1)) ? 1 : 0)) {
+                        if (lane == 0) give_up();
+                        ok_all = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t v[32];
+                        ptx::tmem_ld32(lane_base + 256 + c * 32, v);
+                        ptx::tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                        ptx::tmem_st32(lane_base + 256 + c * 32, v);
+                    }
+                    ptx::tmem_wait_st();
+                }
+                l_run *= alpha;
+                m_run = m_new;
+            }
+            const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
+            // pass 2: probabilities, packed to 16 bits, written over the S columns already consumed
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                ptx::tmem_ld32(s_addr + c * 32, v);
+                ptx::tmem_wait_ld();
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float x0 = fmaf(__uint_as_float(v[i]), P.scale_log2, -m_use);
+                    float x1 = fmaf(__uint_as_float(v[i + 1]), P.scale_log2, -m_use);
+                    if (need_mask) {
+                        if (!row_live || key0 + c * 32 + i > last_key) x0 = -INFINITY;
+                        if (!row_live || key0 + c * 32 + i + 1 > last_key) x1 = -INFINITY;
+                    }
+                    const float p0 = ptx::ex2(x0), p1 = ptx::ex2(x1);
+                    l_run += p0 + p1;
+                    if (BF) {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        pk[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                    } else {
+                        __half2 h = __floats2half2_rn(p0, p1);
+                        pk[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                }
+                ptx::tmem_st16(s_addr + c * 16, pk);
+            }
+            ptx::tmem_wait_st();
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(&bars[PF_PFULL + bb]);
+        }
+        // ---- epilogue: O / l -> global
+        if (ok_all && n_kv > 0) {
+            const int jl = n_kv - 1;
+            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&bars[PF_PVDONE + (jl & 1)], (uint32_t)((jl >> 1) & 1)) ? 1 : 0)) {
+                if (lane == 0) give_up();
+                ok_all = false;
+            }
+            ptx::tc_fence_after_sync();
+        }
+        if (ok_all) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            T* orow = reinterpret_cast<T*>(P.out) + (int64_t)(q0 + tok) * P.out_tok_stride +
+                      (int64_t)(hkv * P.G + g) * P.out_head_stride;
+            if (P.head_major_rows) orow = reinterpret_cast<T*>(P.out) + (int64_t)tok * P.out_tok_stride +
+                                          (int64_t)(b * P.Hq + hkv * P.G + g) * P.out_head_stride;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                if (n_kv > 0) {
+                    ptx::tmem_ld32(lane_base + 256 + c * 32, v);
+                    ptx::tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0;
+                }
+                if (row_live) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float a = __uint_as_float(v[i]) * inv, bq = __uint_as_float(v[i + 1]) * inv;
+                        if (BF) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(a, bq);
+                            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                        } else {
+                            __half2 h = __floats2half2_rn(a, bq);
+                            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) dst[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                }
+            }
+        }
+    }
+done:
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 5) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem, 512);
+    }
+}
+
+}  // namespace rfx
+
+// ---- host side -------------------------------------------------------------------------
+namespace rfx {
+
+template <typename T>
+static int launch_prefill_t(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm,
+                            const PrefillParams& P, int grid, cudaStream_t stream) {
+    auto kern = prefill_tc_kernel<T>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PfSmem::total);
+        if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "prefill smem opt-in: %s", cudaGetErrorString(e));
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    kern<<<grid, kPfThreads, PfSmem::total, stream>>>(qm, km, vm, P);
+    return check_launch("prefill_tc_kernel");
+}
+
+static bool kv_box_ok(int64_t bs) { return bs >= 8 && ((bs <= 128 && 128 % bs == 0) || bs % 128 == 0); }
+
+// Dense fused_attention on tensor cores: q [B,H,Sq,D], k/v [B,Hkv,Sk,D]. Returns
+// RFX_NOT_IMPLEMENTED for shapes the kernel does not cover (the caller then runs the scalar kernel).
+int launch_dense_tensor(const RfxAttentionArgs* a) {
+    if (getenv("REFLEX_B200_NO_TC")) return RFX_NOT_IMPLEMENTED;
+    if (a->dtype != RFX_BF16 && a->dtype != RFX_F16) return RFX_NOT_IMPLEMENTED;
+    if (a->head_dim != kPfHD || a->attn_mask) return RFX_NOT_IMPLEMENTED;
+    const int G = (int)(a->num_q_heads / a->num_kv_heads);
+    if (G > 128 || a->seq_k == 0) return RFX_NOT_IMPLEMENTED;
+    if (a->seq_q * G < 32) return RFX_NOT_IMPLEMENTED;                 // decode-like: not worth a 128-row tile
+    if (a->is_causal && a->seq_q != a->seq_k) return RFX_NOT_IMPLEMENTED;  // top-left causal on non-square
+    if (((uintptr_t)a->q % 16) || ((uintptr_t)a->k % 16) || ((uintptr_t)a->v % 16) || ((uintptr_t)a->out % 16))
+        return RFX_NOT_IMPLEMENTED;
+    if (a->batch * a->num_kv_heads * a->seq_k >= (1ll << 31) || a->batch * a->num_q_heads >= (1ll << 31))
+        return RFX_NOT_IMPLEMENTED;
+    const int T = 128 / G;
+    CUtensorMap qm, km, vm;
+    {
+        const uint64_t dims[3] = {(uint64_t)kPfHD, (uint64_t)a->seq_q, (uint64_t)(a->batch * a->num_q_heads)};
+        const uint64_t str[2] = {(uint64_t)kPfHD * 2, (uint64_t)a->seq_q * kPfHD * 2};
+        const uint32_t box[3] = {64, (uint32_t)T, (uint32_t)G};
+        if (encode_tiled_16bit(&qm, a->q, 3, dims, str, box)) return RFX_NOT_IMPLEMENTED;
+    }
+    {
+        const uint64_t dims[2] = {(uint64_t)kPfHD, (uint64_t)(a->batch * a->num_kv_heads * a->seq_k)};
+        const uint64_t str[1] = {(uint64_t)kPfHD * 2};
+        const uint32_t box[2] = {64, 128};
+        if (encode_tiled_16bit(&km, a->k, 2, dims, str, box)) return RFX_NOT_IMPLEMENTED;
+        if (encode_tiled_16bit(&vm, a->v, 2, dims, str, box)) return RFX_NOT_IMPLEMENTED;
+    }
+    PrefillParams P = {};
+    P.out = a->out; P.out_tok_stride = kPfHD; P.out_head_stride = a->seq_q * kPfHD;
+    P.block_table = nullptr; P.ctx_lens = nullptr; P.q_start = nullptr;
+    P.status = (a->workspace && a->workspace_bytes >= 4) ? (int32_t*)a->workspace : nullptr;
+    P.B = (int)a->batch; P.Hq = (int)a->num_q_heads; P.Hkv = (int)a->num_kv_heads; P.G = G; P.T = T;
+    P.Sq = (int)a->seq_q; P.Sk = (int)a->seq_k;
+    P.block_size = (int)a->seq_k; P.box_rows = 128; P.boxes_per_tile = 1;
+    P.n_qtiles = (int)((a->seq_q + T - 1) / T);
+    P.head_major_rows = 1; P.causal = a->is_causal;
+    P.scale_log2 = a->sm_scale * 1.4426950408889634f;
+    const int64_t grid = (int64_t)P.n_qtiles * P.B * P.Hkv;
+    if (grid >= (1ll << 31)) return RFX_NOT_IMPLEMENTED;
+    if (a->dtype == RFX_BF16) return launch_prefill_t<__nv_bfloat16>(qm, km, vm, P, (int)grid, as_stream(a->stream));
+    return launch_prefill_t<__half>(qm, km, vm, P, (int)grid, as_stream(a->stream));
+}
+
+// Paged (chunked) prefill: q [N,Hq,D] already rotated, K/V in the pool.
+bool prefill_paged_supported(const RfxPagedAttentionArgs* a) {
+    if (a->force_generic || getenv("REFLEX_B200_NO_TC")) return false;
+    if (a->dtype != RFX_BF16 && a->dtype != RFX_F16) return false;
+    if (a->head_dim != kPfHD || a->rope_cos) return false;
+    if (a->q_start == nullptr || a->max_q_len < 1) return false;
+    const int64_t G = a->num_q_heads / a->num_kv_heads;
+    if (G > 128 || !kv_box_ok(a->block_size)) return false;
+    if (((uintptr_t)a->q % 16) || ((uintptr_t)a->k_cache % 16) || ((uintptr_t)a->v_cache % 16) || ((uintptr_t)a->out % 16))
+        return false;
+    if (a->num_blocks * a->num_kv_heads * a->block_size >= (1ll << 31)) return false;
+    return true;
+}
+
+int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word) {
+    const int G = (int)(a->num_q_heads / a->num_kv_heads);
+    const int T = 128 / G;
+    const int R = (int)(a->block_size < 128 ? a->block_size : 128);
+    CUtensorMap qm, km, vm;
+    {
+        const uint64_t dims[3] = {(uint64_t)kPfHD, (uint64_t)a->num_q_heads, (uint64_t)a->n_q};
+        const uint64_t str[2] = {(uint64_t)kPfHD * 2, (uint64_t)a->num_q_heads * kPfHD * 2};
+        const uint32_t box[3] = {64, (uint32_t)G, (uint32_t)T};
+        int r = encode_tiled_16bit(&qm, a->q, 3, dims, str, box);
+        if (r) return fail(RFX_CUDA_ERROR, "cuTensorMapEncodeTiled(q) failed (%d)", r);
+    }
+    {
+        const uint64_t dims[2] = {(uint64_t)kPfHD, (uint64_t)(a->num_blocks * a->num_kv_heads * a->block_size)};
+        const uint64_t str[1] = {(uint64_t)kPfHD * 2};
+        const uint32_t box[2] = {64, (uint32_t)R};
+        int r1 = encode_tiled_16bit(&km, a->k_cache, 2, dims, str, box);
+        int r2 = encode_tiled_16bit(&vm, a->v_cache, 2, dims, str, box);
+        if (r1 || r2) return fail(RFX_CUDA_ERROR, "cuTensorMapEncodeTiled(kv) failed (%d, %d)", r1, r2);
+    }
+    PrefillParams P = {};
+    P.out = a->out; P.out_tok_stride = a->num_q_heads * kPfHD; P.out_head_stride = kPfHD;
+    P.block_table = a->block_table; P.ctx_lens = a->context_lens; P.q_start = a->q_start;
+    P.status = status_word;
+    P.bt_sb = a->bt_stride_b; P.max_blocks = a->max_blocks; P.num_blocks = a->num_blocks;
+    P.B = (int)a->batch; P.Hq = (int)a->num_q_heads; P.Hkv = (int)a->num_kv_heads; P.G = G; P.T = T;
+    P.Sq = (int)a->max_q_len; P.Sk = 0;
+    P.block_size = (int)a->block_size; P.box_rows = R; P.boxes_per_tile = 128 / R;
+    P.n_qtiles = (int)((a->max_q_len + T - 1) / T);
+    P.head_major_rows = 0; P.causal = a->is_causal;
+    P.scale_log2 = a->sm_scale * 1.4426950408889634f;
+    const int64_t grid = (int64_t)P.n_qtiles * P.B * P.Hkv;
+    if (grid >= (1ll << 31)) return fail(RFX_INVALID_ARGUMENT, "prefill grid too large");
+    if (a->dtype == RFX_BF16) return launch_prefill_t<__nv_bfloat16>(qm, km, vm, P, (int)grid, as_stream(a->stream));
+    return launch_prefill_t<__half>(qm, km, vm, P, (int)grid, as_stream(a->stream));
+}
+
+}  // namespace rfx
