@@ -1,20 +1,22 @@
 // Prefill / chunked-prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM).
 //
-// One CTA owns one query tile: T consecutive query tokens of one request times the G query
-// heads that share one kv head, T*G <= 128 rows (row = one (token, head) pair), so a K/V tile
-// is read once for the whole GQA group. Six warps:
-//   warps 0-3  softmax: thread r owns row r (TMEM lane r). Reads S from TMEM, keeps the row
-//              maximum and sum in registers (no shuffles), writes P as bf16 back into the
-//              TMEM columns S occupied, and rescales O in TMEM only when a row maximum grew
-//              by more than 2^8 (stale maxima are exact as long as the final 1/l uses the
-//              same reference); epilogue O/l -> global.
-//   warp 4     TMA producer: Q once, then K and V tiles of 128 keys, one box per page (or
-//              one box per tile for dense K/V), two stages each, 128-byte swizzle.
-//   warp 5     MMA issuer: S_j = Q.K_j^T (8 x tcgen05.mma 128x128x16 from shared-memory
-//              descriptors) into one of two S buffers, then O += P_{j-1}.V_{j-1} with P read
-//              from TMEM and V as an MN-major shared-memory operand; S_j overlaps the softmax
-//              of tile j-1. Completion through tcgen05.commit on mbarriers.
-// TMEM: columns [0,128) S0/P0, [128,256) S1/P1, [256,384) O (fp32); 512 allocated.
+// One CTA owns two query tiles of one (request, kv head): each tile is T consecutive query
+// tokens times the G query heads that share the kv head, T*G <= 128 rows (row = one
+// (token, head) pair), so a K/V tile is read once for the whole GQA group and for both tiles.
+// Ten warps:
+//   warps 0-3 / 4-7  softmax of tile a / tile b: thread r owns row r (TMEM lane r). Reads its
+//              128 scores from TMEM in one go, keeps the row maximum and sum in registers
+//              (no shuffles), writes P as bf16 back into the TMEM columns S occupied, and
+//              rescales O in TMEM only when a row maximum grew by more than 2^8 (a stale
+//              maximum is exact as long as the final 1/l uses the same reference).
+//   warp 8     TMA producer: both Q tiles once, then K and V tiles of 128 keys, one box per
+//              page (or one per tile for dense K/V), two stages each, 128-byte swizzle.
+//   warp 9     MMA issuer: S_x = Q_x.K_j^T (8 x tcgen05.mma 128x128x16 from shared-memory
+//              descriptors), O_x += P_x.V_j with P read from TMEM and V as an MN-major
+//              shared-memory operand. The two tiles ping-pong: while one tile's warps run
+//              their softmax the tensor core works for the other. Completion through
+//              tcgen05.commit on mbarriers.
+// TMEM: columns [0,128) S_a/P_a, [128,256) S_b/P_b, [256,384) O_a, [384,512) O_b (fp32).
 //
 // Causal masking is bottom-right aligned: token t of n sees keys 0..ctx-n+t; K tiles wholly
 // above the diagonal are never loaded. Tensor-pipe bound: 4*rows*keys*D FLOPs per tile pair.
@@ -27,7 +29,7 @@
 
 namespace rfx {
 
-constexpr int kPfThreads = 192;
+constexpr int kPfThreads = 320;
 constexpr int kPfKeys = 128;          // keys per K/V tile
 constexpr int kPfHD = 128;            // head_dim
 constexpr int kPfHalfBytes = 128 * 128;  // one 64-wide half of a 128-row tile
@@ -46,15 +48,15 @@ struct PrefillParams {
     int B, Hq, Hkv, G, T;                      // T = query tokens per tile = 128 / G
     int Sq, Sk;                                // dense sizes (paged: Sq = host bound on rows per request)
     int block_size, box_rows, boxes_per_tile;  // K/V boxes: rows per TMA box, boxes per 128-key tile
-    int n_qtiles;                              // tiles per request = ceil(Sq / T)
+    int n_qtiles;                              // CTAs per (request, kv head) = ceil(Sq / 2T)
     int head_major_rows;                       // 0: row = t*G + g (paged Q [N,Hq,D]); 1: row = g*T + t (dense [B,H,S,D])
     int causal;
     float scale_log2;
 };
 
 struct PfSmem {
-    static constexpr size_t off_q = 0;
-    static constexpr size_t off_k = kPfTileBytes;
+    static constexpr size_t off_q = 0;                                   // two query tiles
+    static constexpr size_t off_k = 2 * (size_t)kPfTileBytes;
     static constexpr size_t off_v = off_k + (size_t)kPfKvStages * kPfTileBytes;
     static constexpr size_t off_bars = off_v + (size_t)kPfKvStages * kPfTileBytes;
     // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2]
@@ -81,7 +83,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // ---- which tile: largest query tiles first (they have the most K tiles under causal masking)
+    // ---- which pair of tiles: the latest query tokens first (most K tiles under causal masking)
     const int pairs = P.B * P.Hkv;
     const int qt = P.n_qtiles - 1 - (int)(blockIdx.x / pairs);
     const int pair = (int)(blockIdx.x % pairs);
@@ -89,10 +91,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     const int q0 = P.q_start ? P.q_start[b] : 0;
     const int n_q = P.q_start ? (P.q_start[b + 1] - q0) : P.Sq;
     const int ctx = P.ctx_lens ? max(0, P.ctx_lens[b]) : P.Sk;
-    const int tok0 = qt * P.T;
+    const int tok0 = qt * 2 * P.T;                  // tile a: tok0.., tile b: tok0 + T..
     if (tok0 >= n_q) return;  // uniform over the CTA; nothing allocated yet
     const int off = ctx - n_q;                      // bottom-right: token t sees keys <= t + off
-    const int last_tok = min(n_q, tok0 + P.T) - 1;
+    const int last_tok = min(n_q, tok0 + 2 * P.T) - 1;
     const int kv_end = P.causal ? max(0, min(ctx, last_tok + off + 1)) : ctx;
     const int n_kv = (kv_end + kPfKeys - 1) / kPfKeys;
 
@@ -102,7 +104,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         misc[1] = 0;
         ptx::fence_barrier_init();
     }
-    if (warp == 5) ptx::tmem_alloc(&misc[0], 512);
+    if (warp == 9) ptx::tmem_alloc(&misc[0], 512);
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
@@ -114,20 +116,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         *abort_flag = 1;
     };
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------------------------------------------ TMA producer --
         if (lane == 0) {
             ptx::prefetch_tensormap(&qmap);
             ptx::prefetch_tensormap(&kmap);
             ptx::prefetch_tensormap(&vmap);
-            // Q: two 64-wide halves; rows beyond T*G stay stale and are never stored
-            ptx::mbar_arrive_expect_tx(&bars[PF_QFULL], 2u * (uint32_t)(P.T * P.G) * 128u);
-            for (int h = 0; h < 2; ++h) {
-                if (P.head_major_rows)
-                    ptx::tma_load_3d(sQ + h * kPfHalfBytes, &qmap, &bars[PF_QFULL], h * 64, tok0, b * P.Hq + hkv * P.G);
-                else
-                    ptx::tma_load_3d(sQ + h * kPfHalfBytes, &qmap, &bars[PF_QFULL], h * 64, hkv * P.G, q0 + tok0);
-            }
+            // Q: two tiles x two 64-wide halves; rows beyond T*G stay stale and are never stored
+            ptx::mbar_arrive_expect_tx(&bars[PF_QFULL], 4u * (uint32_t)(P.T * P.G) * 128u);
+            for (int x = 0; x < 2; ++x)
+                for (int h = 0; h < 2; ++h) {
+                    unsigned char* dst = sQ + x * kPfTileBytes + h * kPfHalfBytes;
+                    if (P.head_major_rows)
+                        ptx::tma_load_3d(dst, &qmap, &bars[PF_QFULL], h * 64, tok0 + x * P.T, b * P.Hq + hkv * P.G);
+                    else
+                        ptx::tma_load_3d(dst, &qmap, &bars[PF_QFULL], h * 64, hkv * P.G, q0 + tok0 + x * P.T);
+                }
         }
         const int R = P.box_rows;
         for (int j = 0; j < n_kv; ++j) {
@@ -169,93 +173,100 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------------------------------------------- MMA issuer --
         constexpr uint32_t idesc_s = ptx::umma_idesc_f16(128, 128, BF ? 1 : 0, 0, 0);   // Q, K both K-major
         constexpr uint32_t idesc_o = ptx::umma_idesc_f16(128, 128, BF ? 1 : 0, 0, 1);   // P (TMEM), V MN-major
         const uint32_t q_addr = ptx::smem_u32(sQ);
-        auto issue_pv = [&](int jj) -> bool {
-            const int bb = jj & 1, st = jj % kPfKvStages;
+        // lane 0 waits, every lane learns the outcome
+        auto wait_bar = [&](int bar, uint32_t parity) -> bool {
             int ok = 1;
-            if (lane == 0) {
-                ok = ptx::mbar_wait_bounded(&bars[PF_PFULL + bb], (uint32_t)((jj >> 1) & 1)) &&
-                     ptx::mbar_wait_bounded(&bars[PF_VFULL + st], (uint32_t)((jj / kPfKvStages) & 1));
-            }
+            if (lane == 0) ok = ptx::mbar_wait_bounded(&bars[bar], parity) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok || *abort_flag) return false;
-            // keys at or past kv_end carry probability zero but may hold NaN patterns: clear those V rows
-            const int valid = kv_end - jj * kPfKeys;
-            if (valid < kPfKeys) {
-                unsigned char* vt = sV + (size_t)st * kPfTileBytes;
-                for (int i = lane; i < (kPfKeys - valid) * 16; i += 32) {
-                    const int r = valid + i / 16, c = i % 16;
-                    *reinterpret_cast<uint4*>(vt + (size_t)(c >> 3) * kPfHalfBytes + (size_t)r * 128 + (size_t)(c & 7) * 16) =
-                        make_uint4(0, 0, 0, 0);
-                }
-                ptx::fence_proxy_async_smem();
-                __syncwarp();
-            }
-            ptx::tc_fence_after_sync();
-            if (lane == 0) {
-                const uint32_t v_addr = ptx::smem_u32(sV + (size_t)st * kPfTileBytes);
-#pragma unroll
-                for (int ks = 0; ks < kPfKeys / 16; ++ks) {
-                    const uint64_t bd = ptx::umma_desc_sw128(v_addr + ks * 2048, kPfHalfBytes, 1024);
-                    ptx::umma_ts(tmem + 256, tmem + bb * 128 + ks * 8, bd, idesc_o, (jj > 0 || ks > 0) ? 1u : 0u);
-                }
-                ptx::umma_commit(&bars[PF_VEMPTY + st]);
-                ptx::umma_commit(&bars[PF_PVDONE + bb]);
-            }
-            __syncwarp();
-            return true;
+            return ok && !*abort_flag;
         };
-        {
-            int ok = 1;
-            if (lane == 0) ok = ptx::mbar_wait_bounded(&bars[PF_QFULL], 0) ? 1 : 0;
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) { if (lane == 0) give_up(); goto done; }
-        }
-        for (int j = 0; j < n_kv; ++j) {
-            const int bb = j & 1, st = j % kPfKvStages;
-            int ok = 1;
+        auto issue_s = [&](int x, int jj) {  // S_x = Q_x . K_jj^T
             if (lane == 0) {
-                ok = ptx::mbar_wait_bounded(&bars[PF_KFULL + st], (uint32_t)((j / kPfKvStages) & 1)) ? 1 : 0;
-                // S buffer bb is free once P.V of tile j-2 has finished
-                if (ok && j >= 2) ok = ptx::mbar_wait_bounded(&bars[PF_PVDONE + bb], (uint32_t)(((j - 2) >> 1) & 1)) ? 1 : 0;
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok || *abort_flag) { if (lane == 0) give_up(); goto done; }
-            ptx::tc_fence_after_sync();
-            if (lane == 0) {
-                const uint32_t k_addr = ptx::smem_u32(sK + (size_t)st * kPfTileBytes);
+                const uint32_t k_addr = ptx::smem_u32(sK + (size_t)(jj % kPfKvStages) * kPfTileBytes);
 #pragma unroll
                 for (int ks = 0; ks < kPfHD / 16; ++ks) {
                     const uint32_t o2 = (uint32_t)(ks >> 2) * kPfHalfBytes + (uint32_t)(ks & 3) * 32u;
-                    ptx::umma_ss(tmem + bb * 128, ptx::umma_desc_sw128(q_addr + o2, 16, 1024),
+                    ptx::umma_ss(tmem + x * 128, ptx::umma_desc_sw128(q_addr + x * kPfTileBytes + o2, 16, 1024),
                                  ptx::umma_desc_sw128(k_addr + o2, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
                 }
-                ptx::umma_commit(&bars[PF_KEMPTY + st]);
-                ptx::umma_commit(&bars[PF_SFULL + bb]);
+                ptx::umma_commit(&bars[PF_SFULL + x]);
+                if (x == 1) ptx::umma_commit(&bars[PF_KEMPTY + jj % kPfKvStages]);
             }
             __syncwarp();
-            if (j >= 1 && !issue_pv(j - 1)) { if (lane == 0) give_up(); goto done; }
+        };
+        if (!wait_bar(PF_QFULL, 0)) { if (lane == 0) give_up(); goto done; }
+        if (n_kv > 0) {
+            if (!wait_bar(PF_KFULL + 0, 0)) { if (lane == 0) give_up(); goto done; }
+            ptx::tc_fence_after_sync();
+            issue_s(0, 0);
+            issue_s(1, 0);
         }
-        if (n_kv >= 1 && !issue_pv(n_kv - 1)) { if (lane == 0) give_up(); goto done; }
+        for (int j = 0; j < n_kv; ++j) {
+            const int st = j % kPfKvStages;
+            for (int x = 0; x < 2; ++x) {
+                if (!wait_bar(PF_PFULL + x, (uint32_t)(j & 1))) { if (lane == 0) give_up(); goto done; }
+                if (x == 0) {
+                    if (!wait_bar(PF_VFULL + st, (uint32_t)((j / kPfKvStages) & 1))) { if (lane == 0) give_up(); goto done; }
+                    // keys at or past kv_end carry probability zero but may hold NaN patterns: clear those V rows
+                    const int valid = kv_end - j * kPfKeys;
+                    if (valid < kPfKeys) {
+                        unsigned char* vt = sV + (size_t)st * kPfTileBytes;
+                        for (int i = lane; i < (kPfKeys - valid) * 16; i += 32) {
+                            const int r = valid + i / 16, c = i % 16;
+                            *reinterpret_cast<uint4*>(vt + (size_t)(c >> 3) * kPfHalfBytes + (size_t)r * 128 +
+                                                      (size_t)(c & 7) * 16) = make_uint4(0, 0, 0, 0);
+                        }
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                    }
+                }
+                ptx::tc_fence_after_sync();
+                if (lane == 0) {
+                    const uint32_t v_addr = ptx::smem_u32(sV + (size_t)st * kPfTileBytes);
+#pragma unroll
+                    for (int ks = 0; ks < kPfKeys / 16; ++ks) {
+                        const uint64_t bd = ptx::umma_desc_sw128(v_addr + ks * 2048, kPfHalfBytes, 1024);
+                        ptx::umma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    ptx::umma_commit(&bars[PF_PVDONE + x]);
+                    if (x == 1) ptx::umma_commit(&bars[PF_VEMPTY + st]);
+                }
+                __syncwarp();
+                // next S for this tile right behind its P.V: the tensor pipe runs them in order,
+                // so the new scores land only after P has been read
+                if (j + 1 < n_kv) {
+                    if (x == 0 && !wait_bar(PF_KFULL + (j + 1) % kPfKvStages, (uint32_t)(((j + 1) / kPfKvStages) & 1))) {
+                        if (lane == 0) give_up();
+                        goto done;
+                    }
+                    ptx::tc_fence_after_sync();
+                    issue_s(x, j + 1);
+                }
+            }
+        }
     } else {
         // ---------------------------------------------------------------- softmax warps --
-        const int r = warp * 32 + lane;                       // row of the tile = TMEM lane
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        const int x = warp >> 2;                                // which query tile
+        const int r = (warp & 3) * 32 + lane;                   // row of the tile = TMEM lane
+        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t s_addr = lane_base + x * 128;
+        const uint32_t o_addr = lane_base + 256 + x * 128;
         const int rows_used = P.T * P.G;
         const int t_loc = P.head_major_rows ? (r % P.T) : (r / P.G);
         const int g = P.head_major_rows ? (r / P.T) : (r % P.G);
-        const int tok = tok0 + t_loc;
+        const int tok = tok0 + x * P.T + t_loc;
         const bool row_live = r < rows_used && tok < n_q;
-        const int last_key = P.causal ? min(ctx - 1, tok + off) : ctx - 1;  // keys 0..last_key visible (live rows)
+        // keys 0..last_key are visible to this row; -1 for a dead row masks everything
+        const int last_key = row_live ? (P.causal ? min(ctx - 1, tok + off) : ctx - 1) : -1;
         float m_run = -INFINITY, l_run = 0.f;
         bool ok_all = true;
         for (int j = 0; j < n_kv && ok_all; ++j) {
-            const int bb = j & 1;
-            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&bars[PF_SFULL + bb], (uint32_t)((j >> 1) & 1)) ? 1 : 0) ||
+            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&bars[PF_SFULL + x], (uint32_t)(j & 1)) ? 1 : 0) ||
                 *abort_flag) {
                 if (lane == 0) give_up();
                 ok_all = false;
@@ -263,31 +274,31 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             }
             ptx::tc_fence_after_sync();
             const int key0 = j * kPfKeys;
-            const uint32_t s_addr = lane_base + bb * 128;
-            const bool need_mask = key0 + kPfKeys - 1 > last_key || !row_live;
-            // pass 1: row maximum of the scaled scores
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                ptx::tmem_ld32(s_addr + c * 32, v);
-                ptx::tmem_wait_ld();
+            const bool need_mask = key0 + kPfKeys - 1 > last_key;
+            uint32_t v[128];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float x = __uint_as_float(v[i]);
-                    if (need_mask && (!row_live || key0 + c * 32 + i > last_key)) x = -INFINITY;
-                    mx = fmaxf(mx, x);
+            for (int c = 0; c < 4; ++c) ptx::tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+            ptx::tmem_wait_ld();
+            float mx = -INFINITY;
+            if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < 128; ++i) {
+                    if (key0 + i > last_key) v[i] = 0xff800000u;  // -inf
+                    mx = fmaxf(mx, __uint_as_float(v[i]));
                 }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
             }
-            mx *= P.scale_log2;  // scale > 0, so the order of max and scale does not matter
+            mx *= P.scale_log2;  // scale > 0, so max and scale commute
             const bool grow = mx > m_run + kPfRescaleTau;  // also true for the first finite maximum
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = fmaxf(m_run, mx);
                 const float alpha = (m_new == -INFINITY) ? 1.f : ptx::ex2(m_run - m_new);
                 if (j > 0) {
                     // O holds tiles 0..j-1 once P.V of tile j-1 is done
-                    if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&bars[PF_PVDONE + ((j - 1) & 1)],
-                                                                       (uint32_t)(((j - 1) >> 1) & 1)) ? 1 : 0)) {
+                    if (!__all_sync(0xffffffffu,
+                                    ptx::mbar_wait_bounded(&bars[PF_PVDONE + x], (uint32_t)((j - 1) & 1)) ? 1 : 0)) {
                         if (lane == 0) give_up();
                         ok_all = false;
                         break;
@@ -295,12 +306,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                     ptx::tc_fence_after_sync();
 #pragma unroll 1
                     for (int c = 0; c < 4; ++c) {
-                        uint32_t v[32];
-                        ptx::tmem_ld32(lane_base + 256 + c * 32, v);
+                        uint32_t w[32];
+                        ptx::tmem_ld32(o_addr + c * 32, w);
                         ptx::tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                        ptx::tmem_st32(lane_base + 256 + c * 32, v);
+                        for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(__uint_as_float(w[i]) * alpha);
+                        ptx::tmem_st32(o_addr + c * 32, w);
                     }
                     ptx::tmem_wait_st();
                 }
@@ -308,23 +319,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 m_run = m_new;
             }
             const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-            // pass 2: probabilities, packed to 16 bits, written over the S columns already consumed
-#pragma unroll 1
+            // probabilities, packed to 16 bits, written over the S columns (all already in registers)
+            float lsum = 0.f;
+#pragma unroll
             for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                ptx::tmem_ld32(s_addr + c * 32, v);
-                ptx::tmem_wait_ld();
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float x0 = fmaf(__uint_as_float(v[i]), P.scale_log2, -m_use);
-                    float x1 = fmaf(__uint_as_float(v[i + 1]), P.scale_log2, -m_use);
-                    if (need_mask) {
-                        if (!row_live || key0 + c * 32 + i > last_key) x0 = -INFINITY;
-                        if (!row_live || key0 + c * 32 + i + 1 > last_key) x1 = -INFINITY;
-                    }
-                    const float p0 = ptx::ex2(x0), p1 = ptx::ex2(x1);
-                    l_run += p0 + p1;
+                    const float p0 = ptx::ex2(fmaf(__uint_as_float(v[c * 32 + i]), P.scale_log2, -m_use));
+                    const float p1 = ptx::ex2(fmaf(__uint_as_float(v[c * 32 + i + 1]), P.scale_log2, -m_use));
+                    lsum += p0 + p1;
                     if (BF) {
                         __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                         pk[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
@@ -335,14 +339,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 }
                 ptx::tmem_st16(s_addr + c * 16, pk);
             }
+            l_run += lsum;
             ptx::tmem_wait_st();
             ptx::tc_fence_before_sync();
-            ptx::mbar_arrive(&bars[PF_PFULL + bb]);
+            ptx::mbar_arrive(&bars[PF_PFULL + x]);
         }
         // ---- epilogue: O / l -> global
         if (ok_all && n_kv > 0) {
-            const int jl = n_kv - 1;
-            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&bars[PF_PVDONE + (jl & 1)], (uint32_t)((jl >> 1) & 1)) ? 1 : 0)) {
+            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&bars[PF_PVDONE + x], (uint32_t)((n_kv - 1) & 1)) ? 1 : 0)) {
                 if (lane == 0) give_up();
                 ok_all = false;
             }
@@ -350,25 +354,26 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         }
         if (ok_all) {
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            T* orow = reinterpret_cast<T*>(P.out) + (int64_t)(q0 + tok) * P.out_tok_stride +
-                      (int64_t)(hkv * P.G + g) * P.out_head_stride;
-            if (P.head_major_rows) orow = reinterpret_cast<T*>(P.out) + (int64_t)tok * P.out_tok_stride +
-                                          (int64_t)(b * P.Hq + hkv * P.G + g) * P.out_head_stride;
+            T* orow = P.head_major_rows
+                          ? reinterpret_cast<T*>(P.out) + (int64_t)tok * P.out_tok_stride +
+                                (int64_t)(b * P.Hq + hkv * P.G + g) * P.out_head_stride
+                          : reinterpret_cast<T*>(P.out) + (int64_t)(q0 + tok) * P.out_tok_stride +
+                                (int64_t)(hkv * P.G + g) * P.out_head_stride;
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
+                uint32_t w[32];
                 if (n_kv > 0) {
-                    ptx::tmem_ld32(lane_base + 256 + c * 32, v);
+                    ptx::tmem_ld32(o_addr + c * 32, w);
                     ptx::tmem_wait_ld();
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = 0;
+                    for (int i = 0; i < 32; ++i) w[i] = 0;
                 }
                 if (row_live) {
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        const float a = __uint_as_float(v[i]) * inv, bq = __uint_as_float(v[i + 1]) * inv;
+                        const float a = __uint_as_float(w[i]) * inv, bq = __uint_as_float(w[i + 1]) * inv;
                         if (BF) {
                             __nv_bfloat162 h = __floats2bfloat162_rn(a, bq);
                             pk[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
@@ -387,7 +392,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 done:
     ptx::tc_fence_before_sync();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem, 512);
     }
@@ -452,7 +457,7 @@ int launch_dense_tensor(const RfxAttentionArgs* a) {
     P.B = (int)a->batch; P.Hq = (int)a->num_q_heads; P.Hkv = (int)a->num_kv_heads; P.G = G; P.T = T;
     P.Sq = (int)a->seq_q; P.Sk = (int)a->seq_k;
     P.block_size = (int)a->seq_k; P.box_rows = 128; P.boxes_per_tile = 1;
-    P.n_qtiles = (int)((a->seq_q + T - 1) / T);
+    P.n_qtiles = (int)((a->seq_q + 2 * T - 1) / (2 * T));
     P.head_major_rows = 1; P.causal = a->is_causal;
     P.scale_log2 = a->sm_scale * 1.4426950408889634f;
     const int64_t grid = (int64_t)P.n_qtiles * P.B * P.Hkv;
@@ -503,7 +508,7 @@ int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word) {
     P.B = (int)a->batch; P.Hq = (int)a->num_q_heads; P.Hkv = (int)a->num_kv_heads; P.G = G; P.T = T;
     P.Sq = (int)a->max_q_len; P.Sk = 0;
     P.block_size = (int)a->block_size; P.box_rows = R; P.boxes_per_tile = 128 / R;
-    P.n_qtiles = (int)((a->max_q_len + T - 1) / T);
+    P.n_qtiles = (int)((a->max_q_len + 2 * T - 1) / (2 * T));
     P.head_major_rows = 0; P.causal = a->is_causal;
     P.scale_log2 = a->sm_scale * 1.4426950408889634f;
     const int64_t grid = (int64_t)P.n_qtiles * P.B * P.Hkv;
