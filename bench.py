@@ -97,8 +97,16 @@ class ClockSampler:
 
     def __init__(self, gpu_index: int):
         self.proc = None
-        self.lines = []
+        self.lines = []   # (arrival time, text)
         self.gpu = gpu_index
+        self.window = [None, None]  # wall-clock bounds of the timed regions
+
+    def mark_begin(self):
+        if self.window[0] is None:
+            self.window[0] = time.time()
+
+    def mark_end(self):
+        self.window[1] = time.time()
 
     def start(self):
         try:
@@ -112,7 +120,7 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -125,7 +133,9 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        lo, hi = self.window
+        inside = [ln for t, ln in self.lines if lo is not None and hi is not None and lo <= t <= hi + 0.06]
+        for ln in (inside if inside else [ln for _, ln in self.lines]):
             parts = [x.strip() for x in ln.split(",")]
             if len(parts) < 7:
                 continue
@@ -138,7 +148,7 @@ class ClockSampler:
                     reasons.add(nm)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "power_w_median": statistics.median(pw) if pw else None, "power_w_max": max(pw) if pw else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "samples_inside_timed_regions": len(inside), "reasons": sorted(reasons)}
 
 
 # ---- CPU legs (oracle: the only place besides tests that may import it) -------------------
@@ -327,7 +337,7 @@ def build_batch(workload, device, seed, shard, rank, world, requests=0):
     return b
 
 
-def measure(workload, args, device, rank, world, dist, want_e2e=True):
+def measure(workload, args, device, rank, world, dist, want_e2e=True, sampler=None):
     seed_base = {"cfg4": 3, "cfg2": 1}[workload]
     # replica: every rank draws its own batch; request/head: all ranks draw the same one, then cut it
     seed = seed_base + (1000 * rank if args.shard == "replica" else 0)
@@ -352,6 +362,8 @@ def measure(workload, args, device, rank, world, dist, want_e2e=True):
         if gather is not None:
             gather.run(out)
 
+    if sampler:
+        sampler.mark_begin()
     total_ms, kern_ms = timed_steps(run, args.steps, args.warmup, flush, dist, with_kernel_events=True)
     status = step.ws.status()
     res = {"tokens": tokens, "kv_bytes": kv_bytes, "total_ms": total_ms, "kernel_ms": statistics.mean(kern_ms),
@@ -361,9 +373,54 @@ def measure(workload, args, device, rank, world, dist, want_e2e=True):
         host = HostDrivenStep(step)
         e2e_ms, _ = timed_steps(host.run, args.steps, args.warmup, flush, dist)
         res.update(e2e_ms=e2e_ms, h2d=host.h2d, d2h=host.d2h)
+    if sampler:
+        sampler.mark_end()
     res["batch"] = batch
     res["step"] = step
     return res
+
+
+def measure_prefill(args, device):
+    """Configuration 3 (causal paged prefill, 8 x 2048 new tokens, 32q/8kv heads, D=128, page 16):
+    one step = fused RoPE + append of every new token (Q rotated too) + causal attention from
+    the pool on the tcgen05 kernel. Tensor-pipe roofline on the attention kernel."""
+    import workloads
+    from kernels.attention import PagedAttentionCall, RopeAppendCall
+    b = workloads.cfg3(device=device)
+    q_rot = torch.empty_like(b.q_new)
+    ra = RopeAppendCall(b.k_new, b.v_new, b.k_cache, b.v_cache, b.slot_mapping, b.positions, b.cos, b.sin,
+                        q=b.q_new, q_out=q_rot)
+    attn = PagedAttentionCall(q_rot, b.k_cache, b.v_cache, b.block_table, b.context_lens, q_start=b.q_start,
+                              max_q_len=b.max_q_len)
+
+    def run(ev0=None, ev1=None):
+        ra.run()
+        if ev0 is not None:
+            ev0.record()
+        attn.run()
+        if ev1 is not None:
+            ev1.record()
+
+    total_ms, kern_ms = timed_steps(run, args.steps, args.warmup, None, None, with_kernel_events=True)
+    S = int(b.n_new[0])
+    flops = 4.0 * b.B * b.Hq * b.D * S * (S + 1) / 2  # causal count; the reference's own count has no discount
+    km = statistics.mean(kern_ms)
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        pass
+    burst = float(peaks.get("bf16_tflops", 1590.0))
+    return {"config": "cfg3: bf16 causal paged prefill, 8 x 2048 new tokens on an empty cache, 32q/8kv heads, D=128, "
+                      "page 16, theta 1e6",
+            "value": b.n_tokens * args.steps / (total_ms * 1e-3), "unit": UNIT, "ms_per_step": total_ms / args.steps,
+            "kernel": "prefill_tc_kernel" if attn.kernel_kind == 2 else "scalar",
+            "kernel_ms": km, "roofline": {"bound": "tensor", "achieved": flops / (km * 1e-3) / 1e12, "peak": burst,
+                                          "unit": "TFLOP/s", "frac": flops / (km * 1e-3) / 1e12 / burst,
+                                          "peak_sustained": peaks.get("bf16_tflops_sustained"),
+                                          "flops_causal": flops, "flops_reference_count": 2 * flops * S / (S + 1)},
+            "append_gigabytes_moved": 2.0 * b.n_tokens * (b.Hq + 2 * b.Hkv) * b.D * 2 / 1e9,
+            "status": attn.workspace.status()}
 
 
 def check_against_oracle(res, n_req=2):
@@ -411,7 +468,7 @@ def run_ours(args):
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
-    res = measure(args.workload, args, device, rank, world, dist)
+    res = measure(args.workload, args, device, rank, world, dist, sampler=sampler)
     clocks = sampler.stop() if sampler else None
 
     # whole-job numbers: tokens of all ranks over the slowest rank's time
@@ -481,6 +538,9 @@ def run_ours(args):
             "unit": UNIT, "ms_per_step": r2["total_ms"] / args.steps, "e2e_ms_per_step": r2["e2e_ms"] / args.steps,
             "roofline_achieved_gbs": ach2, "roofline_frac": ach2 / peak, "kernel_ms": r2["kernel_ms"],
             "l2": r2["flush"]}}
+        del r2
+        torch.cuda.empty_cache()
+        line["other_workloads"]["cfg3"] = measure_prefill(args, device)
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()

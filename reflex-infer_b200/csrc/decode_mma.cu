@@ -30,7 +30,6 @@ namespace rfx {
 
 constexpr int kTile = kPlanTile;    // keys per stage
 constexpr int kGroupWarps = 4;      // warps per consumer group, 16 keys each
-constexpr int kMaxGroups = 2;
 constexpr int kAccPad = 4;          // floats of padding per merge row (bank spread)
 
 struct StageMeta {
@@ -55,7 +54,6 @@ struct DecodeParams {
     float* pacc;
     int64_t num_blocks, max_blocks, bt_sb, table_rows;
     int Hq, Hkv, G, block_size, box_rows, rope_inter;
-    int skip_math;     // debugging aid: consumers release stages without computing
     int map2d;         // 1: the maps are 2-D [rows, D] with {64, box_rows} boxes, one copy per 128-byte half
     float scale_log2;  // sm_scale * log2(e)
 };
@@ -398,7 +396,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     for (int i = 0; i < 4; ++i) o[j][nt][i] = 0.f;
         }
         const int slice0 = wq * 16;
-        if (group == turn && slice0 < meta.n_valid && P.skip_math != 1) {
+        if (group == turn && slice0 < meta.n_valid) {
             const uint32_t kst = sK_u32 + (uint32_t)stage * S::kTileBytes;
             const uint32_t vst = sV_u32 + (uint32_t)stage * S::kTileBytes;
             const bool tail = meta.n_valid < slice0 + 16;
@@ -424,7 +422,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
-            if (P.skip_math != 3)
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
                 const uint32_t chunk = (uint32_t)(2 * ks + (mat >> 1));
@@ -484,7 +481,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 pb[nt][1] = ptx::movmatrix_trans(Pack2<T>::pack(p2, p3));  // keys 8-15
             }
             // ---- O^T += V^T.P^T : rows = 16 dims per tile, cols = heads
-            if (P.skip_math != 2)
 #pragma unroll
             for (int j = 0; j < HD / 16; ++j) {
                 const uint32_t chunk = (uint32_t)(2 * j + (mat & 1));
@@ -632,13 +628,8 @@ int encode_rows_map_3d(CUtensorMap* map, const void* base, uint64_t rows, uint32
     const cuuint64_t strides[2] = {(cuuint64_t)row_elems * 2, 128};  // bytes, dims 1 and 2
     const cuuint32_t box[3] = {64, box_rows, row_elems / 64};
     const cuuint32_t estr[3] = {1, 1, 1};
-    CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
-    if (const char* e = getenv("REFLEX_B200_L2PROMO")) {  // temporary experiment hook
-        promo = e[0] == '0' ? CU_TENSOR_MAP_L2_PROMOTION_NONE : e[0] == '1' ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
-              : e[0] == '2' ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
-    }
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : (int)r;
 }
@@ -734,10 +725,6 @@ int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const P
     P.block_size = (int)a->block_size; P.box_rows = R; P.rope_inter = a->rope_interleaved;
     P.scale_log2 = a->sm_scale * 1.4426950408889634f;
     P.map2d = map2d;
-    {
-        const char* e = getenv("REFLEX_B200_SKIP_MATH");
-        P.skip_math = e ? atoi(e) : 0;
-    }
 
 #define RFX_DECODE_CASE(T)                                                                   \
     if (HD == 128) {                                                                         \
@@ -746,16 +733,6 @@ int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const P
     } else {                                                                                 \
         if (G <= 8) return launch_decode_t<T, 64, 8, 8>(a, km, vm, P);                       \
         return launch_decode_t<T, 64, 16, 8>(a, km, vm, P);                                  \
-    }
-    {
-        // temporary experiment hook: ring depth
-        const char* e = getenv("REFLEX_B200_STAGES");
-        if (e && a->dtype == RFX_BF16 && HD == 128 && G <= 8) {
-            if (e[0] == '2') return launch_decode_t<__nv_bfloat16, 128, 8, 6, 2>(a, km, vm, P);
-            if (e[0] == '3') return launch_decode_t<__nv_bfloat16, 128, 8, 3>(a, km, vm, P);
-            if (e[0] == '4') return launch_decode_t<__nv_bfloat16, 128, 8, 4>(a, km, vm, P);
-            if (e[0] == '5') return launch_decode_t<__nv_bfloat16, 128, 8, 5>(a, km, vm, P);
-        }
     }
     if (a->dtype == RFX_BF16) { RFX_DECODE_CASE(__nv_bfloat16) }
     RFX_DECODE_CASE(__half)

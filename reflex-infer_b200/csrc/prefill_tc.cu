@@ -68,7 +68,7 @@ struct PfSmem {
 enum PfBar { PF_QFULL = 0, PF_KFULL = 1, PF_KEMPTY = 3, PF_VFULL = 5, PF_VEMPTY = 7, PF_SFULL = 9, PF_PFULL = 11,
              PF_PVDONE = 13 };
 
-template <typename T, int VARIANT>
+template <typename T>
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                   const __grid_constant__ CUtensorMap vmap, const PrefillParams P) {
@@ -327,13 +327,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     const float p0 = ptx::ex2(fmaf(__uint_as_float(v[c * 32 + i]), P.scale_log2, -m_use));
-                    const float a1 = fmaf(__uint_as_float(v[c * 32 + i + 1]), P.scale_log2, -m_use);
-                    // VARIANT bit 0: every second exponential on the FMA pipe instead of the MUFU
-                    const float p1 = (VARIANT & 1) ? ptx::ex2_poly(a1) : ptx::ex2(a1);
+                    const float p1 = ptx::ex2(fmaf(__uint_as_float(v[c * 32 + i + 1]), P.scale_log2, -m_use));
                     lsum += p0 + p1;
-                    if (BF && (VARIANT & 2)) {
-                        pk[i >> 1] = ptx::pack_bf16_int(p0, p1);  // VARIANT bit 1: pack on the integer pipe
-                    } else if (BF) {
+                    if (BF) {
                         __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                         pk[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
                     } else {
@@ -407,10 +403,10 @@ done:
 // ---- host side -------------------------------------------------------------------------
 namespace rfx {
 
-template <typename T, int VARIANT = 0>
-static int launch_prefill_v(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm,
+template <typename T>
+static int launch_prefill_t(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm,
                             const PrefillParams& P, int grid, cudaStream_t stream) {
-    auto kern = prefill_tc_kernel<T, VARIANT>;
+    auto kern = prefill_tc_kernel<T>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -421,22 +417,6 @@ static int launch_prefill_v(const CUtensorMap& qm, const CUtensorMap& km, const 
     }
     kern<<<grid, kPfThreads, PfSmem::total, stream>>>(qm, km, vm, P);
     return check_launch("prefill_tc_kernel");
-}
-
-template <typename T>
-static int launch_prefill_t(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm,
-                            const PrefillParams& P, int grid, cudaStream_t stream) {
-    static int variant = -1;  // REFLEX_B200_PF_VARIANT: experiment switch, see the kernel
-    if (variant < 0) {
-        const char* e = getenv("REFLEX_B200_PF_VARIANT");
-        variant = e ? atoi(e) & 3 : 0;
-    }
-    switch (variant) {
-        case 1: return launch_prefill_v<T, 1>(qm, km, vm, P, grid, stream);
-        case 2: return launch_prefill_v<T, 2>(qm, km, vm, P, grid, stream);
-        case 3: return launch_prefill_v<T, 3>(qm, km, vm, P, grid, stream);
-        default: return launch_prefill_v<T, 0>(qm, km, vm, P, grid, stream);
-    }
 }
 
 static bool kv_box_ok(int64_t bs) { return bs >= 8 && ((bs <= 128 && 128 % bs == 0) || bs % 128 == 0); }

@@ -118,28 +118,6 @@ __device__ __forceinline__ float ex2(float x) {
     return r;
 }
 
-// 2^x for x <= 0 (and a few units above) on the FMA/ALU pipes instead of the MUFU: split
-// x = n + f with n = round-to-nearest integer, 2^f by a degree-4 polynomial on [-0.5, 0.5]
-// (relative error ~4e-6, far below the 2^-9 of a bf16 probability), exponent added as
-// integer. Inputs below -126 (incl. -inf) give 0.
-__device__ __forceinline__ float ex2_poly(float x) {
-    const float xc = fmaxf(x, -126.0f);
-    const float t = xc + 12582912.0f;          // 1.5 * 2^23: the low mantissa bits of t hold round(xc)
-    const float f = xc - (t - 12582912.0f);
-    float p = fmaf(f, 0.009618129f, 0.05550411f);
-    p = fmaf(p, f, 0.2402265f);
-    p = fmaf(p, f, 0.6931472f);
-    p = fmaf(p, f, 1.0f);
-    const float r = __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-    return x < -126.0f ? 0.f : r;
-}
-
-// Two fp32 -> one register of two bf16 (round half up on the dropped bits), integer pipe only.
-__device__ __forceinline__ uint32_t pack_bf16_int(float lo, float hi) {
-    const uint32_t a = __float_as_uint(lo) + 0x8000u, b = __float_as_uint(hi) + 0x8000u;
-    return __byte_perm(a, b, 0x7632);
-}
-
 // Transposes an 8x8 matrix of 16-bit elements held in the standard fragment layout
 // (lane holds row lane/4, columns 2*(lane%4)+{0,1}).
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {

@@ -152,8 +152,6 @@ rope_table_kernel(T* __restrict__ cosb, T* __restrict__ sinb, const float* __res
     }
 }
 
-static inline bool al(const void* p, size_t a) { return ((uintptr_t)p % a) == 0; }
-
 static int grid_for(int64_t total_threads) {
     int64_t blocks = ceil_div<int64_t>(total_threads, 256);
     const int64_t cap = (int64_t)sm_count() * 16;
