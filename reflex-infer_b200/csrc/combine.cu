@@ -6,6 +6,7 @@
 // One warp per output row, lanes across head_dim. Traffic: (D+2)*4 bytes per partial
 // row read, D*e bytes per output row written.
 #include "paged_plan.cuh"
+#include "ptx.cuh"
 
 namespace rfx {
 
@@ -19,6 +20,39 @@ __device__ inline void combine_row(int ns, PartialRow prow_of, const float* __re
                                    const float* __restrict__ pl, const float* __restrict__ pacc, int D,
                                    T* __restrict__ orow) {
     const int lane = threadIdx.x & 31;
+    if (ns <= 4 && (D & 3) == 0 && D <= 128) {
+        // Few splits (the usual case): issue every load at once -- statistics and the lane's
+        // four dims of each split -- so the row costs one memory round trip.
+        const int d = lane * 4;
+        float m[4], l[4];
+        float4 a[4];
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+            m[s] = -INFINITY; l[s] = 0.f; a[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (s < ns) {
+                const long long pr = prow_of(s);
+                m[s] = pm[pr];
+                l[s] = pl[pr];
+                if (d < D) a[s] = *reinterpret_cast<const float4*>(pacc + pr * D + d);
+            }
+        }
+        const float M = fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
+        float L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+            const float w = (m[s] == -INFINITY) ? 0.f : expf(m[s] - M);
+            L = fmaf(l[s], w, L);
+            acc.x = fmaf(w, a[s].x, acc.x); acc.y = fmaf(w, a[s].y, acc.y);
+            acc.z = fmaf(w, a[s].z, acc.z); acc.w = fmaf(w, a[s].w, acc.w);
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        if (d < D) {
+            orow[d] = Num<T>::from_f(acc.x * inv); orow[d + 1] = Num<T>::from_f(acc.y * inv);
+            orow[d + 2] = Num<T>::from_f(acc.z * inv); orow[d + 3] = Num<T>::from_f(acc.w * inv);
+        }
+        return;
+    }
     float M = -INFINITY;
     for (int s0 = 0; s0 < ns; s0 += 32) {
         const int s = s0 + lane;
@@ -80,9 +114,10 @@ __device__ inline void combine_row(int ns, PartialRow prow_of, const float* __re
 template <typename T>
 __global__ void __launch_bounds__(kCombineWarps * 32)
 paged_combine_kernel(T* __restrict__ out, const int32_t* __restrict__ q_start, int B, int64_t n_q, int Hq,
-                     int Hkv, int D, const int32_t* __restrict__ pair_item_begin,
+                     int Hkv, int D, int rows_follow_items, const int32_t* __restrict__ pair_item_begin,
                      const int32_t* __restrict__ item_prow, const float* __restrict__ pm,
                      const float* __restrict__ pl, const float* __restrict__ pacc) {
+    ptx::pdl_wait();  // partials come from the kernel just before this one
     const int warp = threadIdx.x >> 5;
     const int G = Hq / Hkv;
     const int64_t rows = n_q * Hq;
@@ -108,8 +143,11 @@ paged_combine_kernel(T* __restrict__ out, const int32_t* __restrict__ q_start, i
         const int item0 = pair_item_begin[pair];
         const int ns = pair_item_begin[pair + 1] - item0;
         const int within = qi * G + g;
-        combine_row<T>(ns, [&](int s) { return (long long)item_prow[item0 + s] + within; }, pm, pl, pacc, D,
-                       out + orow * D);
+        if (rows_follow_items)  // one query row per request: item i owns partial rows [i*G, i*G + G)
+            combine_row<T>(ns, [&](int s) { return (long long)(item0 + s) * G + g; }, pm, pl, pacc, D, out + orow * D);
+        else
+            combine_row<T>(ns, [&](int s) { return (long long)item_prow[item0 + s] + within; }, pm, pl, pacc, D,
+                           out + orow * D);
     }
 }
 
@@ -133,9 +171,13 @@ int launch_paged_combine(const RfxPagedAttentionArgs* a, const PlanLayout& L, co
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     RFX_DISPATCH_DTYPE(a->dtype, T, {
-        paged_combine_kernel<T><<<(int)blocks, kCombineWarps * 32, 0, as_stream(a->stream)>>>(
-            (T*)a->out, a->q_start, (int)a->batch, a->n_q, (int)a->num_q_heads, (int)a->num_kv_heads,
-            (int)a->head_dim, P.pair_item_begin, P.item_prow, P.m, P.l, P.acc);
+        cudaError_t le = launch_pdl(paged_combine_kernel<T>, dim3((int)blocks), dim3(kCombineWarps * 32), 0,
+                                    as_stream(a->stream), (T*)a->out, a->q_start, (int)a->batch, (int64_t)a->n_q,
+                                    (int)a->num_q_heads, (int)a->num_kv_heads, (int)a->head_dim,
+                                    a->q_start == nullptr ? 1 : 0, (const int32_t*)P.pair_item_begin,
+                                    (const int32_t*)P.item_prow, (const float*)P.m, (const float*)P.l,
+                                    (const float*)P.acc);
+        if (le != cudaSuccess) return fail(RFX_CUDA_ERROR, "combine launch: %s", cudaGetErrorString(le));
     });
     return check_launch("rfx_paged_attention (combine)");
 }

@@ -197,6 +197,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         ptx::fence_barrier_init();
     }
     __syncthreads();
+    ptx::pdl_trigger();  // the combine kernel may be scheduled behind this one already
+    ptx::pdl_wait();     // everything below reads what earlier kernels wrote (plan, pool, Q)
 
     if (warp == kConsumers) {  // the last warp
         // ------------------------------------------------------------ producer --
@@ -686,7 +688,9 @@ static int launch_decode_t(const RfxPagedAttentionArgs* a, const CUtensorMap& km
         if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "decode smem opt-in (%zu B): %s", S::total, cudaGetErrorString(e));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    kern<<<decode_mma_ctas(a), (kGroupWarps * GROUPS + 1) * 32, S::total, as_stream(a->stream)>>>(km, vm, P);
+    cudaError_t le = launch_pdl(kern, dim3(decode_mma_ctas(a)), dim3((kGroupWarps * GROUPS + 1) * 32), S::total,
+                                as_stream(a->stream), km, vm, P);
+    if (le != cudaSuccess) return fail(RFX_CUDA_ERROR, "decode kernel launch: %s", cudaGetErrorString(le));
     return check_launch("rfx_paged_attention (decode MMA kernel)");
 }
 

@@ -4,6 +4,7 @@
 // persistent partial kernel, so every CTA streams the same number of bytes whatever the mix
 // of request lengths), and writes the items -- the pieces of pairs inside one run.
 #include "paged_plan.cuh"
+#include "ptx.cuh"
 
 namespace rfx {
 
@@ -38,13 +39,22 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
             int G, long long max_parts, long long target_chunk, int parts_hint, int32_t* hdr,
             int32_t* pair_item_begin, int32_t* part_first, int4* items, int32_t* item_prow) {
     __shared__ long long red[kPlanThreads / 32][2];
+    ptx::pdl_trigger();  // the partial kernel may set itself up while the plan is computed
     const int tid = threadIdx.x;
     const int per = (B + kPlanThreads - 1) / kPlanThreads;  // requests per thread, contiguous
     const int b0 = min(B, tid * per), b1 = min(B, b0 + per);
 
+    // With one request per thread (B <= 1024) its length and row count live in registers, so
+    // the three passes below cost one global round trip, not three.
+    const bool single = per == 1 && b0 < b1;
+    const int ctx_reg = single ? max(0, ctx_lens[b0]) : 0;
+    const int nq_reg = single ? (q_start ? max(0, q_start[b0 + 1] - q_start[b0]) : 1) : 0;
+    auto ctx_of = [&](int b) { return single ? ctx_reg : max(0, ctx_lens[b]); };
+    auto nq_of = [&](int b) -> long long { return single ? nq_reg : (q_start ? max(0, q_start[b + 1] - q_start[b]) : 1); };
+
     // tiles before each request (per kv head), and in total
     long long tile_pre = 0, unused = 0, tiles_all, t2;
-    for (int b = b0; b < b1; ++b) tile_pre += (max(0, ctx_lens[b]) + kPlanTile - 1) / kPlanTile;
+    for (int b = b0; b < b1; ++b) tile_pre += (ctx_of(b) + kPlanTile - 1) / kPlanTile;
     block_exscan2(tile_pre, unused, red, tiles_all, t2);
     const long long T = tiles_all * Hkv;
 
@@ -62,8 +72,8 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
     {
         long long pre = tile_pre;
         for (int b = b0; b < b1; ++b) {
-            const long long tb = (max(0, ctx_lens[b]) + kPlanTile - 1) / kPlanTile;
-            const long long nq = q_start ? max(0, q_start[b + 1] - q_start[b]) : 1;
+            const long long tb = (ctx_of(b) + kPlanTile - 1) / kPlanTile;
+            const long long nq = nq_of(b);
             if (tb > 0)
                 for (int h = 0; h < Hkv; ++h) {
                     const long long off = pre * Hkv + h * tb;
@@ -78,9 +88,9 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
 
     long long pre = tile_pre, it = item_pre, rw = row_pre;
     for (int b = b0; b < b1; ++b) {
-        const int c = max(0, ctx_lens[b]);
+        const int c = ctx_of(b);
         const long long tb = (c + kPlanTile - 1) / kPlanTile;
-        const long long nq = q_start ? max(0, q_start[b + 1] - q_start[b]) : 1;
+        const long long nq = nq_of(b);
         for (int h = 0; h < Hkv; ++h) {
             pair_item_begin[(long long)b * Hkv + h] = (int)it;
             if (tb == 0) continue;
@@ -107,13 +117,18 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
         hdr[HdrStatus] = 0;
         hdr[HdrTotalRows] = (int)n_rows;
     }
+    // The plan reads nothing its predecessor wrote, but its successor (the partial kernel) does
+    // (the pool pages just appended): do not complete before the predecessor has.
+    ptx::pdl_wait();
 }
 
 int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int parts_hint) {
     const int G = (int)(a->num_q_heads / a->num_kv_heads);
-    plan_kernel<<<1, kPlanThreads, 0, as_stream(a->stream)>>>(
-        a->context_lens, a->q_start, (int)a->batch, (int)a->num_kv_heads, G, L.max_parts, a->target_chunk,
-        parts_hint, P.hdr, P.pair_item_begin, P.part_first, P.items, P.item_prow);
+    cudaError_t e = launch_pdl(plan_kernel, dim3(1), dim3(kPlanThreads), 0, as_stream(a->stream), a->context_lens,
+                               a->q_start, (int)a->batch, (int)a->num_kv_heads, G, (long long)L.max_parts,
+                               (long long)a->target_chunk, parts_hint, P.hdr, P.pair_item_begin, P.part_first, P.items,
+                               P.item_prow);
+    if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "rfx_paged_attention_plan: %s", cudaGetErrorString(e));
     return check_launch("rfx_paged_attention_plan");
 }
 

@@ -261,11 +261,35 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n, int ab_fmt, 
            ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization
+// attribute may start while its predecessor in the stream still runs; pdl_wait() blocks until
+// the predecessor has completed and its writes are visible (a no-op for a plain launch);
+// pdl_trigger() lets the successor start launching.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 }  // namespace ptx
+
+// Launch with the programmatic-stream-serialization attribute (see pdl_wait / pdl_trigger).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 // ---- host side: tensor-map encoding through the runtime's driver entry point -----
 // Encodes a map over a row-major [rows, row_elems] 16-bit matrix seen as

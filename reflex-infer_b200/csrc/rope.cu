@@ -86,6 +86,7 @@ rope_append_kernel(const T* __restrict__ k_in, const T* __restrict__ v_in, const
                    const T* __restrict__ cosb, const T* __restrict__ sinb,
                    int64_t N, int Hq, int Hkv, int D, int pieces, int64_t num_slots, int block_size,
                    int64_t table_rows, int64_t c_sblk, int64_t c_sh, int64_t c_spos) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the split-K plan may start alongside
     const int rows_per_tok = 2 * Hkv + Hq;
     const int64_t total = N * rows_per_tok * pieces;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
