@@ -266,21 +266,41 @@ class DecodeStep:
         return self.out
 
 
-class HostDrivenStep:
-    """The same step fed from pinned host buffers, result read back to pinned host memory."""
+def pack_step_inputs(batch):
+    """Re-homes the per-step inputs (q, k, v, slots, positions) as views of ONE device buffer,
+    so a host-driven step uploads them with a single copy. Returns (packed device buffer, batch)."""
+    import dataclasses
+    names = ["q_new", "k_new", "v_new", "slot_mapping", "positions"]
+    offs, total = {}, 0
+    for n in names:
+        t = getattr(batch, n)
+        offs[n] = total
+        total += (t.numel() * t.element_size() + 255) // 256 * 256
+    buf = torch.empty(total, dtype=torch.uint8, device=batch.q_new.device)
+    views = {}
+    for n in names:
+        t = getattr(batch, n)
+        nb = t.numel() * t.element_size()
+        v = buf[offs[n]:offs[n] + nb].view(t.dtype).view(t.shape)
+        v.copy_(t)
+        views[n] = v
+    return buf, dataclasses.replace(batch, **views)
 
-    def __init__(self, step: DecodeStep):
-        b = step.b
+
+class HostDrivenStep:
+    """The same step fed from one pinned host buffer (all of the step's inputs), result read
+    back to pinned host memory."""
+
+    def __init__(self, step: DecodeStep, packed: torch.Tensor):
         self.step = step
-        self.dev = [b.q_new, b.k_new, b.v_new, b.slot_mapping, b.positions]
-        self.host = [t.cpu().pin_memory() for t in self.dev]
+        self.dev = packed
+        self.host = packed.cpu().pin_memory()
         self.out_host = torch.empty(step.out.shape, dtype=step.out.dtype).pin_memory()
-        self.h2d = sum(t.numel() * t.element_size() for t in self.host)
+        self.h2d = self.host.numel()
         self.d2h = self.out_host.numel() * self.out_host.element_size()
 
     def run(self):
-        for d, h in zip(self.dev, self.host):
-            d.copy_(h, non_blocking=True)
+        self.dev.copy_(self.host, non_blocking=True)
         out = self.step.run()
         self.out_host.copy_(out, non_blocking=True)
 
@@ -342,6 +362,7 @@ def measure(workload, args, device, rank, world, dist, want_e2e=True, sampler=No
     # replica: every rank draws its own batch; request/head: all ranks draw the same one, then cut it
     seed = seed_base + (1000 * rank if args.shard == "replica" else 0)
     batch = build_batch(workload, device, seed, args.shard, rank, world, args.requests if workload == args.workload else 0)
+    packed, batch = pack_step_inputs(batch)
     step = DecodeStep(batch, chunk=args.chunk)
     kv_bytes = batch.kv_bytes()
     tokens = batch.n_tokens
@@ -375,7 +396,7 @@ def measure(workload, args, device, rank, world, dist, want_e2e=True, sampler=No
            "kernel_ms_min": min(kern_ms), "status": status, "flush": flush_note, "kernel_kind": step.attn.kernel_kind,
            "launches": step.kernel_launches * args.steps}
     if want_e2e:
-        host = HostDrivenStep(step)
+        host = HostDrivenStep(step, packed)
         e2e_ms, _ = timed_steps(host.run, args.steps, args.warmup, flush, dist)
         res.update(e2e_ms=e2e_ms, h2d=host.h2d, d2h=host.d2h)
     if sampler:
