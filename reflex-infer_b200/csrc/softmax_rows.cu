@@ -1,13 +1,19 @@
-// Row softmax / log-softmax (the public online_softmax op). One CTA per row; the row is
-// read from HBM once into shared memory as fp32 (rows up to 50k elements fit the 227 KB
-// of an sm_100 CTA), reduced with warp shuffles, and written once: 2*numel*e bytes of
-// traffic, which is the reference's own byte accounting (benchmark/bench_softmax.py:34).
-// Rows too long for shared memory take three passes over global memory instead.
+// Row softmax / log-softmax (the public online_softmax op). Bandwidth-bound: 2*numel*e
+// bytes (benchmark/bench_softmax.py:34), every element read once and written once.
+//   * rows whose 16-byte vectors divide evenly (and up to 16 K elements): one CTA of 256
+//     threads per row, the row lives in registers as fp32 (up to 8 vectors per thread),
+//     two block reductions (max, sum), vector stores;
+//   * other rows up to 51 200 elements: one CTA per row, the row staged in shared memory as
+//     fp32; loads and stores are 16-byte vectors over the aligned body of the row with scalar
+//     head and tail, so odd lengths (50 257) and unaligned rows still move full sectors;
+//   * longer rows: three passes over global memory.
 #include "common.cuh"
 
 namespace rfx {
 
 constexpr int kSoftmaxMaxSmemFloats = 51200;  // 200 KiB
+constexpr int kVecThreads = 256;
+constexpr int kVecItems = 8;                  // vectors per thread in the register kernel
 
 __device__ inline float block_reduce(float v, bool is_max, float* red) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
@@ -20,6 +26,114 @@ __device__ inline float block_reduce(float v, bool is_max, float* red) {
     return r;
 }
 
+template <typename T> struct alignas(16) Vec16 { T v[16 / sizeof(T)]; };
+
+// Register kernel: n % V == 0, rows 16-byte aligned, n <= TPR * kVecItems * V. TPR threads
+// share a row: a whole CTA (two block reductions) or one warp (shuffles only, eight rows
+// per CTA). exp through ex2 of the pre-scaled difference, one reciprocal per row.
+template <typename T, int TPR>
+__global__ void __launch_bounds__(kVecThreads)
+softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n, int causal, int is_log) {
+    constexpr int V = 16 / sizeof(T);
+    constexpr int RPC = kVecThreads / TPR;  // rows per CTA
+    constexpr float kLog2e = 1.4426950408889634f;
+    __shared__ float red[32];
+    const int nvec = n / V;
+    const int tr = threadIdx.x % TPR;
+    const int sub = threadIdx.x / TPR;
+    const int64_t row_groups = (rows + RPC - 1) / RPC;
+    for (int64_t grp = blockIdx.x; grp < row_groups; grp += gridDim.x) {
+        const int64_t row = grp * RPC + sub;
+        const bool live = row < rows;
+        const Vec16<T>* xr = reinterpret_cast<const Vec16<T>*>(x + row * (int64_t)n);
+        Vec16<T>* yr = reinterpret_cast<Vec16<T>*>(y + row * (int64_t)n);
+        const int valid = causal ? (int)(row % n) + 1 : n;  // columns [0, valid) take part
+        float f[kVecItems][V];
+        float m = -INFINITY;
+#pragma unroll
+        for (int it = 0; it < kVecItems; ++it) {
+            const int vi = it * TPR + tr;
+            if (live && vi < nvec) {
+                const Vec16<T> p = xr[vi];
+#pragma unroll
+                for (int j = 0; j < V; ++j) {
+                    float v = Num<T>::to_f(p.v[j]);
+                    if (vi * V + j >= valid) v = -INFINITY;
+                    f[it][j] = v;
+                    m = fmaxf(m, v);
+                }
+            }
+        }
+        m = (TPR == 32) ? warp_max(m) : block_reduce(m, true, red);
+        const float mb = m * kLog2e;
+        float l = 0.f;
+#pragma unroll
+        for (int it = 0; it < kVecItems; ++it) {
+            const int vi = it * TPR + tr;
+            if (live && vi < nvec) {
+#pragma unroll
+                for (int j = 0; j < V; ++j) {
+                    const float e = exp2f(fmaf(f[it][j], kLog2e, -mb));  // 0 for masked columns
+                    l += e;
+                    if (!is_log) f[it][j] = e;
+                }
+            }
+        }
+        l = (TPR == 32) ? warp_sum(l) : block_reduce(l, false, red);
+        const float logl = logf(l);
+        const float inv = 1.0f / l;
+#pragma unroll
+        for (int it = 0; it < kVecItems; ++it) {
+            const int vi = it * TPR + tr;
+            if (live && vi < nvec) {
+                Vec16<T> o;
+#pragma unroll
+                for (int j = 0; j < V; ++j) {
+                    const float r = is_log ? (f[it][j] - m) - logl : f[it][j] * inv;
+                    o.v[j] = Num<T>::from_f(r);
+                }
+                yr[vi] = o;
+            }
+        }
+    }
+}
+
+// Visits elements [0, count) of a row: scalar head up to the first 16-byte boundary, vector
+// body, scalar tail. `fn(index, value)` for loads.
+template <typename T, typename F>
+__device__ inline void for_each_load(const T* row, int count, F fn) {
+    constexpr int V = 16 / sizeof(T);
+    const int mis = (int)(((uintptr_t)row % 16) / sizeof(T));
+    const int head = min(count, mis ? V - mis : 0);
+    for (int i = threadIdx.x; i < head; i += blockDim.x) fn(i, Num<T>::to_f(row[i]));
+    const int nbody = (count - head) / V;
+    const Vec16<T>* body = reinterpret_cast<const Vec16<T>*>(row + head);
+    for (int vi = threadIdx.x; vi < nbody; vi += blockDim.x) {
+        const Vec16<T> p = body[vi];
+#pragma unroll
+        for (int j = 0; j < V; ++j) fn(head + vi * V + j, Num<T>::to_f(p.v[j]));
+    }
+    for (int i = head + nbody * V + threadIdx.x; i < count; i += blockDim.x) fn(i, Num<T>::to_f(row[i]));
+}
+
+// Writes elements [0, count) of a row from `val(index)` with the same head/body/tail split.
+template <typename T, typename F>
+__device__ inline void for_each_store(T* row, int count, F val) {
+    constexpr int V = 16 / sizeof(T);
+    const int mis = (int)(((uintptr_t)row % 16) / sizeof(T));
+    const int head = min(count, mis ? V - mis : 0);
+    for (int i = threadIdx.x; i < head; i += blockDim.x) row[i] = Num<T>::from_f(val(i));
+    const int nbody = (count - head) / V;
+    Vec16<T>* body = reinterpret_cast<Vec16<T>*>(row + head);
+    for (int vi = threadIdx.x; vi < nbody; vi += blockDim.x) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) o.v[j] = Num<T>::from_f(val(head + vi * V + j));
+        body[vi] = o;
+    }
+    for (int i = head + nbody * V + threadIdx.x; i < count; i += blockDim.x) row[i] = Num<T>::from_f(val(i));
+}
+
 template <typename T, bool STAGED>
 __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n,
                                     int causal, int is_log) {
@@ -30,33 +144,36 @@ __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, 
         T* yr = y + row * (int64_t)n;
         const int valid = causal ? (int)(row % n) + 1 : n;  // columns [0, valid) take part
         float m = -INFINITY;
-        for (int i = threadIdx.x; i < valid; i += blockDim.x) {
-            const float v = Num<T>::to_f(xr[i]);
+        for_each_load<T>(xr, valid, [&](int i, float v) {
             if (STAGED) srow[i] = v;
             m = fmaxf(m, v);
-        }
-        m = block_reduce(m, true, red);
+        });
+        m = block_reduce(m, true, red);  // also orders the smem writes before the reads below
         float l = 0.f;
-        for (int i = threadIdx.x; i < valid; i += blockDim.x) {
-            const float v = STAGED ? srow[i] : Num<T>::to_f(xr[i]);
-            const float e = expf(v - m);
-            if (STAGED && !is_log) srow[i] = e;
-            l += e;
+        if (STAGED) {
+            for (int i = threadIdx.x; i < valid; i += blockDim.x) {
+                const float e = expf(srow[i] - m);
+                if (!is_log) srow[i] = e;
+                l += e;
+            }
+        } else {
+            for_each_load<T>(xr, valid, [&](int, float v) { l += expf(v - m); });
         }
         l = block_reduce(l, false, red);
         const float logl = logf(l);
-        for (int i = threadIdx.x; i < n; i += blockDim.x) {
-            float o;
-            if (i >= valid) {
-                o = is_log ? -INFINITY : 0.f;
-            } else if (is_log) {
-                const float v = STAGED ? srow[i] : Num<T>::to_f(xr[i]);
-                o = (v - m) - logl;
-            } else {
-                const float e = STAGED ? srow[i] : expf(Num<T>::to_f(xr[i]) - m);
-                o = e / l;
+        if (STAGED) {
+            for_each_store<T>(yr, n, [&](int i) -> float {
+                if (i >= valid) return is_log ? -INFINITY : 0.f;
+                return is_log ? (srow[i] - m) - logl : srow[i] / l;
+            });
+        } else {
+            for (int i = threadIdx.x; i < n; i += blockDim.x) {
+                float o;
+                if (i >= valid) o = is_log ? -INFINITY : 0.f;
+                else if (is_log) o = (Num<T>::to_f(xr[i]) - m) - logl;
+                else o = expf(Num<T>::to_f(xr[i]) - m) / l;
+                yr[i] = Num<T>::from_f(o);
             }
-            yr[i] = Num<T>::from_f(o);
         }
         __syncthreads();  // srow is reused by the next row
     }
@@ -80,19 +197,38 @@ extern "C" int rfx_online_softmax(const RfxSoftmaxArgs* a) {
     if (st != RFX_SUCCESS) return st;
 
     const int n = (int)a->n;
-    int threads = n <= 512 ? 64 : n <= 4096 ? 128 : n <= 16384 ? 256 : 512;
-    const bool staged = n <= kSoftmaxMaxSmemFloats;
-    const size_t smem = staged ? (size_t)n * sizeof(float) : 0;
+    const size_t e = dtype_size(a->dtype);
+    const int V = (int)(16 / e);
+    cudaStream_t s = as_stream(a->stream);
     int64_t grid = a->rows;
     const int64_t cap = (int64_t)sm_count() * 32;
     if (grid > cap) grid = cap;
-    cudaStream_t s = as_stream(a->stream);
+
+    const bool reg_ok = n % V == 0 && n <= kVecThreads * kVecItems * V && ((uintptr_t)a->x % 16) == 0 &&
+                        ((uintptr_t)a->y % 16) == 0;
+    if (reg_ok) {
+        const bool warp_rows = n <= 32 * kVecItems * V;  // a warp per row, eight rows per CTA
+        int64_t g2 = warp_rows ? (a->rows + 7) / 8 : a->rows;
+        if (g2 > cap) g2 = cap;
+        RFX_DISPATCH_DTYPE(a->dtype, T, {
+            if (warp_rows)
+                softmax_rows_reg_kernel<T, 32><<<(int)g2, kVecThreads, 0, s>>>((const T*)a->x, (T*)a->y, a->rows, n,
+                                                                               a->is_causal, a->log);
+            else
+                softmax_rows_reg_kernel<T, kVecThreads><<<(int)g2, kVecThreads, 0, s>>>(
+                    (const T*)a->x, (T*)a->y, a->rows, n, a->is_causal, a->log);
+        });
+        return check_launch(name);
+    }
+    const int threads = n <= 512 ? 64 : n <= 4096 ? 128 : n <= 16384 ? 256 : 1024;
+    const bool staged = n <= kSoftmaxMaxSmemFloats;
+    const size_t smem = staged ? (size_t)n * sizeof(float) : 0;
     RFX_DISPATCH_DTYPE(a->dtype, T, {
         if (staged) {
             auto kern = softmax_rows_kernel<T, true>;
             if (smem > 48 * 1024) {
-                cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "%s: smem opt-in: %s", name, cudaGetErrorString(e));
+                cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (ce != cudaSuccess) return fail(RFX_CUDA_ERROR, "%s: smem opt-in: %s", name, cudaGetErrorString(ce));
             }
             kern<<<(int)grid, threads, smem, s>>>((const T*)a->x, (T*)a->y, a->rows, n, a->is_causal, a->log);
         } else {
