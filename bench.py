@@ -62,6 +62,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary configuration block")
     ap.add_argument("--chunk", type=int, default=0, help="keys per split (0 = planner's choice)")
+    ap.add_argument("--graph", action="store_true",
+                    help="replay the step from a CUDA graph in the step-timing pass (launch overhead off the clock)")
     ap.add_argument("--requests", type=int, default=0,
                     help="profiling aid: shrink the batch to this many requests (0 = the configuration's own)")
     return ap.parse_args()
@@ -389,7 +391,18 @@ def measure(workload, args, device, rank, world, dist, want_e2e=True, sampler=No
     # launches (an event record between two kernels would keep the second from being launched
     # programmatically behind the first); the second brackets the partial kernel with its own
     # event pair for the roofline.
-    total_ms, _ = timed_steps(lambda: run(), args.steps, args.warmup, flush, dist)
+    step_fn = lambda: run()  # noqa: E731
+    if args.graph and gather is None:
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            run()
+            torch.cuda.synchronize()
+            cg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cg, stream=side):
+                run()
+        torch.cuda.synchronize()
+        step_fn = cg.replay
+    total_ms, _ = timed_steps(step_fn, args.steps, args.warmup, flush, dist)
     _, kern_ms = timed_steps(run, args.steps, 1, flush, dist, with_kernel_events=True)
     status = step.ws.status()
     res = {"tokens": tokens, "kv_bytes": kv_bytes, "total_ms": total_ms, "kernel_ms": statistics.mean(kern_ms),
@@ -530,6 +543,7 @@ def run_ours(args):
         "data": "synthetic",
         "config": {**workload_desc(args.workload), "shard": args.shard, "l2": res["flush"],
                    **({"requests_override": args.requests} if args.requests else {}),
+                   **({"cuda_graph": True} if args.graph else {}),
                    "timing": "CUDA events per step on the launch stream, max over ranks"},
         "e2e": {"value": all_tokens * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"],
