@@ -241,7 +241,7 @@ typedef struct {
     int dtype;
     int reuse_plan;              /* 1: workspace already holds a plan for these lengths */
     int force_generic;           /* 1: use the scalar kernel (debug / parity cross-check) */
-    int64_t target_chunk;        /* 0 = choose; else keys per split (rounded to 64) */
+    int64_t target_chunk;        /* 0 = choose; >0 keys per split (rounded to 64); <0 query chunks are not split */
     void* workspace;
     size_t workspace_bytes;
     rfx_stream stream;

@@ -51,7 +51,11 @@ extern "C" int rfx_paged_attention_plan(const RfxPagedAttentionArgs* a) {
         return fail(RFX_WORKSPACE_TOO_SMALL, "%s: workspace %zu B < %zu B", name, a->workspace_bytes, L.total);
     RFX_REQUIRE(((uintptr_t)a->workspace % 256) == 0, "%s: workspace must be 256-byte aligned", name);
     const PlanPtrs P = plan_ptrs(a->workspace, L);
-    const int ctas = decode_mma_supported(a) ? decode_mma_ctas(a) : sm_count() * 4;
+    int ctas = decode_mma_supported(a) ? decode_mma_ctas(a) : sm_count() * 4;
+    if (prefill_paged_supported(a)) {
+        if (!prefill_paged_split(a)) return RFX_SUCCESS;  // that kernel needs no plan
+        ctas = prefill_paged_parts(a);
+    }
     return launch_plan(a, L, P, ctas);
 }
 
@@ -72,11 +76,24 @@ static int run_stages(const RfxPagedAttentionArgs* a, const char* name, int stag
     RFX_REQUIRE(((uintptr_t)a->workspace % 256) == 0, "%s: workspace must be 256-byte aligned", name);
     const PlanPtrs P = plan_ptrs(a->workspace, L);
     if (prefill_paged_supported(a)) {
-        // Query chunks on the tcgen05 kernel: whole rows per CTA, so no plan and no combine.
-        if (!(stages & kStagePartials)) return RFX_SUCCESS;
-        cudaError_t e = cudaMemsetAsync(P.hdr + HdrStatus, 0, sizeof(int32_t), as_stream(a->stream));
-        if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "%s: cudaMemsetAsync: %s", name, cudaGetErrorString(e));
-        return launch_prefill_paged(a, P.hdr + HdrStatus);
+        // Query chunks on the tcgen05 kernel.
+        if (!prefill_paged_split(a)) {
+            // whole rows per CTA: no plan and no combine
+            if (!(stages & kStagePartials)) return RFX_SUCCESS;
+            cudaError_t e = cudaMemsetAsync(P.hdr + HdrStatus, 0, sizeof(int32_t), as_stream(a->stream));
+            if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "%s: cudaMemsetAsync: %s", name, cudaGetErrorString(e));
+            return launch_prefill_paged(a, P.hdr + HdrStatus, &L, nullptr);
+        }
+        if (stages & kStagePlan) {
+            st = launch_plan(a, L, P, prefill_paged_parts(a));
+            if (st != RFX_SUCCESS) return st;
+        }
+        if (stages & kStagePartials) {
+            st = launch_prefill_paged(a, P.hdr + HdrStatus, &L, &P);
+            if (st != RFX_SUCCESS) return st;
+        }
+        if (stages & kStageCombine) return launch_paged_combine(a, L, P);
+        return RFX_SUCCESS;
     }
     const bool mma = decode_mma_supported(a);
     if (stages & kStagePlan) {

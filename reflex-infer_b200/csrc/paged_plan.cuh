@@ -98,6 +98,10 @@ int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout& L, const
 int decode_mma_ctas(const RfxPagedAttentionArgs* a);
 // tcgen05 kernel for ragged query chunks (prefill_tc.cu).
 bool prefill_paged_supported(const RfxPagedAttentionArgs* a);
-int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word);
+bool prefill_paged_split(const RfxPagedAttentionArgs* a);  // split-K over the plan's items?
+int prefill_paged_parts(const RfxPagedAttentionArgs* a);
+// `split` = nullptr: whole rows per CTA, output written directly; else partials for the combine.
+int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, const PlanLayout* L,
+                         const PlanPtrs* split);
 
 }  // namespace rfx

@@ -24,7 +24,7 @@
 
 #include <type_traits>
 
-#include "common.cuh"
+#include "paged_plan.cuh"
 #include "ptx.cuh"
 
 namespace rfx {
@@ -44,6 +44,15 @@ struct PrefillParams {
     const int32_t* ctx_lens;                   // [B] keys per request (paged)
     const int32_t* q_start;                    // [B+1] first query row per request (paged)
     int32_t* status;                           // optional device status word
+    // split-K mode (items != nullptr): a CTA handles one plan item (request, kv head, key range)
+    // and leaves un-normalised (m, l, acc) partial rows for the combine kernel
+    const int4* items;
+    const int32_t* item_prow;
+    const int32_t* hdr;
+    float* pm;
+    float* pl;
+    float* pacc;
+    int items_cap;
     int64_t bt_sb, max_blocks, num_blocks;
     int B, Hq, Hkv, G, T;                      // T = query tokens per tile = 128 / G
     int Sq, Sk;                                // dense sizes (paged: Sq = host bound on rows per request)
@@ -84,10 +93,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // ---- which pair of tiles: the latest query tokens first (most K tiles under causal masking)
-    const int pairs = P.B * P.Hkv;
-    const int qt = P.n_qtiles - 1 - (int)(blockIdx.x / pairs);
-    const int pair = (int)(blockIdx.x % pairs);
-    const int b = pair / P.Hkv, hkv = pair % P.Hkv;
+    int qt, b, hkv, kb = 0, ke_item = 0x7fffffff, prow = 0;
+    if (P.items) {
+        const int item = (int)(blockIdx.x % P.items_cap);
+        if (item >= P.hdr[0]) return;  // hdr[0] = number of items
+        qt = (int)(blockIdx.x / P.items_cap);
+        const int4 d = P.items[item];
+        b = d.x; hkv = d.y; kb = d.z; ke_item = d.w;
+        prow = P.item_prow[item];
+    } else {
+        const int pairs = P.B * P.Hkv;
+        qt = P.n_qtiles - 1 - (int)(blockIdx.x / pairs);
+        const int pair = (int)(blockIdx.x % pairs);
+        b = pair / P.Hkv; hkv = pair % P.Hkv;
+    }
     const int q0 = P.q_start ? P.q_start[b] : 0;
     const int n_q = P.q_start ? (P.q_start[b + 1] - q0) : P.Sq;
     const int ctx = P.ctx_lens ? max(0, P.ctx_lens[b]) : P.Sk;
@@ -95,8 +114,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     if (tok0 >= n_q) return;  // uniform over the CTA; nothing allocated yet
     const int off = ctx - n_q;                      // bottom-right: token t sees keys <= t + off
     const int last_tok = min(n_q, tok0 + 2 * P.T) - 1;
-    const int kv_end = P.causal ? max(0, min(ctx, last_tok + off + 1)) : ctx;
-    const int n_kv = (kv_end + kPfKeys - 1) / kPfKeys;
+    // keys [kb, kv_end) are streamed: the item's range cut at the causal bound of the last row
+    const int kv_end = min(ke_item, P.causal ? max(0, min(ctx, last_tok + off + 1)) : ctx);
+    const int n_kv = kv_end > kb ? (kv_end - kb + kPfKeys - 1) / kPfKeys : 0;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < PfSmem::n_bars; ++i)
@@ -137,7 +157,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         for (int j = 0; j < n_kv; ++j) {
             const int st = j % kPfKvStages;
             const uint32_t par = (uint32_t)((j / kPfKvStages) & 1);
-            const int key0 = j * kPfKeys;
+            const int key0 = kb + j * kPfKeys;
             // rows of this tile's boxes: lane i owns box i
             int row = -1;
             if (lane < P.boxes_per_tile) {
@@ -213,7 +233,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 if (x == 0) {
                     if (!wait_bar(PF_VFULL + st, (uint32_t)((j / kPfKvStages) & 1))) { if (lane == 0) give_up(); goto done; }
                     // keys at or past kv_end carry probability zero but may hold NaN patterns: clear those V rows
-                    const int valid = kv_end - j * kPfKeys;
+                    const int valid = kv_end - (kb + j * kPfKeys);
                     if (valid < kPfKeys) {
                         unsigned char* vt = sV + (size_t)st * kPfTileBytes;
                         for (int i = lane; i < (kPfKeys - valid) * 16; i += 32) {
@@ -262,7 +282,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         const int tok = tok0 + x * P.T + t_loc;
         const bool row_live = r < rows_used && tok < n_q;
         // keys 0..last_key are visible to this row; -1 for a dead row masks everything
-        const int last_key = row_live ? (P.causal ? min(ctx - 1, tok + off) : ctx - 1) : -1;
+        const int last_key = row_live ? min(kv_end - 1, P.causal ? min(ctx - 1, tok + off) : ctx - 1) : -1;
         float m_run = -INFINITY, l_run = 0.f;
         bool ok_all = true;
         for (int j = 0; j < n_kv && ok_all; ++j) {
@@ -273,7 +293,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 break;
             }
             ptx::tc_fence_after_sync();
-            const int key0 = j * kPfKeys;
+            const int key0 = kb + j * kPfKeys;
             const bool need_mask = key0 + kPfKeys - 1 > last_key;
             uint32_t v[128];
 #pragma unroll
@@ -352,7 +372,31 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             }
             ptx::tc_fence_after_sync();
         }
-        if (ok_all) {
+        if (ok_all && P.items) {
+            // split-K: un-normalised partial of this row; the running maximum goes back to natural logs
+            const int64_t pr = (int64_t)prow + (int64_t)tok * P.G + g;
+            if (row_live) {
+                P.pm[pr] = m_run * 0.6931471805599453f;
+                P.pl[pr] = l_run;
+            }
+            float* arow = P.pacc + pr * kPfHD;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t w[32];
+                if (n_kv > 0) {  // uniform over the CTA; the load is warp-collective
+                    ptx::tmem_ld32(o_addr + c * 32, w);
+                    ptx::tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) w[i] = 0;
+                }
+                if (row_live) {
+                    uint4* dst = reinterpret_cast<uint4*>(arow + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+                }
+            }
+        } else if (ok_all) {
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             T* orow = P.head_major_rows
                           ? reinterpret_cast<T*>(P.out) + (int64_t)tok * P.out_tok_stride +
@@ -480,7 +524,18 @@ bool prefill_paged_supported(const RfxPagedAttentionArgs* a) {
     return true;
 }
 
-int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word) {
+// Split-K over the plan's items pays when the query chunks are short (a CTA per (request, kv
+// head, tile pair) would otherwise stream a whole context, however uneven the contexts are).
+// It needs key ranges that start on a K/V box boundary: items start at multiples of 64 keys.
+bool prefill_paged_split(const RfxPagedAttentionArgs* a) {
+    if (a->target_chunk < 0 || getenv("REFLEX_B200_PREFILL_NOSPLIT")) return false;
+    return a->block_size <= kPlanTile && kPlanTile % a->block_size == 0 && a->max_q_len <= 512;
+}
+
+int prefill_paged_parts(const RfxPagedAttentionArgs* a) { (void)a; return 2 * sm_count(); }
+
+int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, const PlanLayout* L,
+                         const PlanPtrs* split) {
     const int G = (int)(a->num_q_heads / a->num_kv_heads);
     const int T = 128 / G;
     const int R = (int)(a->block_size < 128 ? a->block_size : 128);
@@ -511,7 +566,16 @@ int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word) {
     P.n_qtiles = (int)((a->max_q_len + 2 * T - 1) / (2 * T));
     P.head_major_rows = 0; P.causal = a->is_causal;
     P.scale_log2 = a->sm_scale * 1.4426950408889634f;
-    const int64_t grid = (int64_t)P.n_qtiles * P.B * P.Hkv;
+    int64_t grid = (int64_t)P.n_qtiles * P.B * P.Hkv;
+    if (split) {
+        P.items = split->items; P.item_prow = split->item_prow; P.hdr = split->hdr;
+        P.pm = split->m; P.pl = split->l; P.pacc = split->acc;
+        // the plan makes at most one item per pair plus one per run boundary
+        int64_t cap = a->batch * a->num_kv_heads + (a->target_chunk > 0 ? L->max_parts : prefill_paged_parts(a));
+        if (cap > L->max_items) cap = L->max_items;
+        P.items_cap = (int)cap;
+        grid = (int64_t)P.n_qtiles * cap;
+    }
     if (grid >= (1ll << 31)) return fail(RFX_INVALID_ARGUMENT, "prefill grid too large");
     if (a->dtype == RFX_BF16) return launch_prefill_t<__nv_bfloat16>(qm, km, vm, P, (int)grid, as_stream(a->stream));
     return launch_prefill_t<__half>(qm, km, vm, P, (int)grid, as_stream(a->stream));

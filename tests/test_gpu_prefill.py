@@ -101,6 +101,12 @@ def test_chunked_prefill_mixed_batch_tensor_core(bs, native):
     torch.testing.assert_close(out.cpu().float(), ref.float(), atol=2e-2, rtol=2e-2)
     out_s = paged_attention(q_rot.to(DEV), kc.to(DEV), vc.to(DEV), g.block_table, g.context_lens, force_generic=True, **kw)
     torch.testing.assert_close(out.float(), out_s.float(), atol=2e-2, rtol=2e-2)
+    # key ranges cut at other places (192-key pieces) and not cut at all (whole rows per CTA)
+    for chunk in (192, -1):
+        out_c = paged_attention(q_rot.to(DEV), kc.to(DEV), vc.to(DEV), g.block_table, g.context_lens,
+                                target_chunk=chunk, **kw)
+        assert ws.status() == 0 and torch.isfinite(out_c).all()
+        torch.testing.assert_close(out_c.cpu().float(), ref.float(), atol=2e-2, rtol=2e-2)
 
 
 def test_cfg3_full_request_properties(native):
