@@ -57,6 +57,9 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg4", choices=["cfg4", "cfg2"])
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="--shard head: assemble the heads inside the combine kernel (peer stores) or with an "
+                         "NCCL all-gather")
     ap.add_argument("--shard", default="replica", choices=["replica", "request", "head"])
     ap.add_argument("--cpu-sample", type=int, default=0, help="requests in the CPU-baseline sample (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -255,6 +258,7 @@ class DecodeStep:
                                        rope_positions=batch.positions, workspace=self.ws, target_chunk=chunk)
         self.out = self.attn.out
         self.kernel_launches = 4
+        self.gather = None  # a sharding.FusedHeadGather: the combine then writes every rank's full output
 
     def run(self, ev0=None, ev1=None):
         self.append.run()
@@ -264,6 +268,8 @@ class DecodeStep:
         self.attn.partials()
         if ev1 is not None:
             ev1.record()
+        if self.gather is not None:
+            return self.attn.combine_gather(self.gather)
         self.attn.combine()
         return self.out
 
@@ -297,7 +303,8 @@ class HostDrivenStep:
         self.step = step
         self.dev = packed
         self.host = packed.cpu().pin_memory()
-        self.out_host = torch.empty(step.out.shape, dtype=step.out.dtype).pin_memory()
+        shape = step.gather.shape if step.gather is not None else step.out.shape
+        self.out_host = torch.empty(shape, dtype=step.out.dtype).pin_memory()
         self.h2d = self.host.numel()
         self.d2h = self.out_host.numel() * self.out_host.element_size()
 
@@ -376,9 +383,18 @@ def measure(workload, args, device, rank, world, dist, want_e2e=True, sampler=No
         flush_note = "512 MiB memset between timed steps flushes L2 (outside the timed events)"
 
     gather = None
+    gather_check = None
     if world > 1 and args.shard == "head":
-        from sharding import HeadGather
+        from sharding import FusedHeadGather, HeadGather
         gather = HeadGather(step.out, dist)
+        if args.gather == "fused":
+            # same step twice: NCCL all-gather of the local heads, then the gathering combine
+            want = gather.run(step.run()).clone()
+            step.gather = FusedHeadGather(step.out.shape[0], batch.Hq, batch.D, batch.dtype, device, dist)
+            got = step.run()
+            torch.cuda.synchronize()
+            gather_check = "equal to the NCCL all-gather" if torch.equal(got, want) else "DIFFERS from the NCCL all-gather"
+            gather = None
 
     def run(ev0=None, ev1=None):
         out = step.run(ev0, ev1)
@@ -407,7 +423,7 @@ def measure(workload, args, device, rank, world, dist, want_e2e=True, sampler=No
     status = step.ws.status()
     res = {"tokens": tokens, "kv_bytes": kv_bytes, "total_ms": total_ms, "kernel_ms": statistics.mean(kern_ms),
            "kernel_ms_min": min(kern_ms), "status": status, "flush": flush_note, "kernel_kind": step.attn.kernel_kind,
-           "launches": step.kernel_launches * args.steps}
+           "launches": step.kernel_launches * args.steps, "gather_check": gather_check}
     if want_e2e:
         host = HostDrivenStep(step, packed)
         e2e_ms, _ = timed_steps(host.run, args.steps, args.warmup, flush, dist)
@@ -607,6 +623,8 @@ def run_ours(args):
         "dtype": "bf16",
         "data": "synthetic",
         "config": {**workload_desc(args.workload), "shard": args.shard, "l2": res["flush"],
+                   **({"head_gather": args.gather, "head_gather_check": res["gather_check"]}
+                      if args.shard == "head" and world > 1 else {}),
                    **({"requests_override": args.requests} if args.requests else {}),
                    **({"cuda_graph": True} if args.graph else {}),
                    "timing": "CUDA events per step on the launch stream, max over ranks"},

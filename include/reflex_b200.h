@@ -52,7 +52,8 @@ typedef void* rfx_stream; /* cudaStream_t; mirrors StreamHandle, include/reflex/
 int rfx_abi_version(void);
 /* sizeof() of the args struct with the given index (0 RfxKvAppendArgs, 1 RfxKvLookupArgs,
  * 2 RfxRopeArgs, 3 RfxRopeTableArgs, 4 RfxRopeAppendArgs, 5 RfxSoftmaxArgs,
- * 6 RfxAttentionArgs, 7 RfxPagedAttentionArgs, 8 RfxCombineArgs; 0 for anything else), so
+ * 6 RfxAttentionArgs, 7 RfxPagedAttentionArgs, 8 RfxCombineArgs, 9 RfxHeadGatherArgs,
+ * 10 RfxPeerHandle; 0 for anything else), so
  * a foreign-function binding can verify its struct mirrors before the first call. */
 size_t rfx_args_size(int which);
 const char* rfx_status_string(int status);
@@ -302,6 +303,48 @@ int rfx_splitk_combine(const RfxCombineArgs* a);
  * (0 = ok; bit 0 = a bounded wait expired; bit 1 = a page index outside the pool was
  * skipped). Synchronises the stream; meant for tests and debugging. */
 int rfx_paged_attention_status(const void* workspace, rfx_stream stream, int* status_word_host);
+
+/* ---- head-sharded output gather fused into the combine (no counterpart in the reference,
+ * which has no multi-GPU code; the stock form of this step is an NCCL all-gather) ----------
+ * Rank r of `world` ranks computes query heads [r*Hq, (r+1)*Hq) of every row, Hq =
+ * num_q_heads of its RfxPagedAttentionArgs. With RfxHeadGatherArgs the combine kernel stores
+ * each finished row slice straight into every rank's full output [n_q, world*Hq, D] through
+ * peer-mapped pointers (plain stores over NVLink; nothing is read from a peer), then the last
+ * CTA publishes `epoch` in every rank's flag array and, if `wait` is set, spins -- with an
+ * iteration limit -- until every rank's flag on this GPU has reached `epoch`. When the kernel
+ * has completed, peer_out[rank] holds all heads. `a->out` is not written.
+ *
+ * The caller owns every buffer. Because a peer may begin step k+1 while this rank still reads
+ * the output of step k, alternate between two output buffers (epoch parity); the flags need
+ * no reset: epochs only grow. On expiry of the wait bit 0 of the workspace status word is set
+ * (rfx_paged_attention_status) and the kernel returns; the context stays usable.
+ *
+ * rfx_peer_export / rfx_peer_open / rfx_peer_close wrap the CUDA IPC calls that make a
+ * cudaMalloc'ed buffer of another process addressable here (one process per GPU). */
+#define RFX_MAX_PEERS 16
+typedef struct {
+    int world, rank;
+    void* peer_out[RFX_MAX_PEERS];       /* [n_q, world*Hq, D] on each rank, as mapped in this process */
+    uint32_t* peer_flags[RFX_MAX_PEERS]; /* [world] uint32 on each rank; slot [rank] is written by this rank */
+    uint32_t* arrival_counter;           /* local device word, zero before the first use */
+    uint32_t epoch;                      /* > 0, strictly increasing from step to step */
+    int wait;                            /* 1: do not complete before every rank has published epoch */
+    int64_t spin_limit;                  /* polls (about 100 ns each) before giving up; 0 = 10 million */
+} RfxHeadGatherArgs;
+/* Combine stage of rfx_paged_attention (after rfx_paged_attention_partials) with the gather. */
+int rfx_paged_attention_combine_gather(const RfxPagedAttentionArgs* a, const RfxHeadGatherArgs* g);
+/* All stages of rfx_paged_attention with the gathering combine. */
+int rfx_paged_attention_gather(const RfxPagedAttentionArgs* a, const RfxHeadGatherArgs* g);
+
+typedef struct {
+    unsigned char handle[64]; /* cudaIpcMemHandle_t of the allocation that holds the pointer */
+    int64_t offset;           /* of the pointer inside that allocation, bytes */
+} RfxPeerHandle;
+int rfx_peer_export(const void* device_ptr, RfxPeerHandle* out);
+/* `mapped` = the exporting process's pointer as addressable here; `mapped_base` is what
+ * rfx_peer_close takes. Must be called by a process other than the exporter. */
+int rfx_peer_open(const RfxPeerHandle* h, void** mapped, void** mapped_base);
+int rfx_peer_close(void* mapped_base);
 
 #ifdef __cplusplus
 }

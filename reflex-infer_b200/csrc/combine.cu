@@ -12,13 +12,54 @@ namespace rfx {
 
 constexpr int kCombineWarps = 4;
 
+// Where a combined row goes: put(d, v, n) takes n (1..4) consecutive dims starting at d.
+template <typename T>
+struct LocalRow {
+    T* row;
+    __device__ inline void put(int d, const float4& v, int n) const {
+        row[d] = Num<T>::from_f(v.x);
+        if (n > 1) row[d + 1] = Num<T>::from_f(v.y);
+        if (n > 2) row[d + 2] = Num<T>::from_f(v.z);
+        if (n > 3) row[d + 3] = Num<T>::from_f(v.w);
+    }
+};
+
+// Device-side form of RfxHeadGatherArgs.
+struct HeadGatherDev {
+    void* out[RFX_MAX_PEERS];
+    uint32_t* flags[RFX_MAX_PEERS];
+    uint32_t* counter;
+    int32_t* status;
+    long long spin_limit;
+    uint32_t epoch;
+    int world, rank, wait;
+};
+
+// The same row slice stored into every rank's full output (plain stores through peer mappings).
+template <typename T>
+struct PeerRows {
+    const HeadGatherDev* hg;
+    int64_t elem;  // offset of the row slice inside a full output
+    __device__ inline void put(int d, const float4& v, int n) const {
+        T t[4] = {Num<T>::from_f(v.x), Num<T>::from_f(v.y), Num<T>::from_f(v.z), Num<T>::from_f(v.w)};
+        for (int p = 0; p < hg->world; ++p) {
+            T* row = reinterpret_cast<T*>(hg->out[p]) + elem;
+            if (n == 4 && sizeof(T) == 2) {
+                *reinterpret_cast<uint2*>(row + d) = *reinterpret_cast<const uint2*>(t);  // d % 4 == 0
+            } else {
+                for (int i = 0; i < n; ++i) row[d + i] = t[i];
+            }
+        }
+    }
+};
+
 // `prow_of(s)` gives the partial row of split s. Lanes first fetch the splits' rows and
 // statistics side by side (one round trip for up to 32 splits), then walk the splits with
 // every lane owning four consecutive dims, the loads of successive splits independent.
-template <typename T, typename PartialRow>
+template <typename T, typename PartialRow, typename Sink>
 __device__ inline void combine_row(int ns, PartialRow prow_of, const float* __restrict__ pm,
                                    const float* __restrict__ pl, const float* __restrict__ pacc, int D,
-                                   T* __restrict__ orow) {
+                                   const Sink& sink) {
     const int lane = threadIdx.x & 31;
     if (ns <= 4 && (D & 3) == 0 && D <= 128) {
         // Few splits (the usual case): issue every load at once -- statistics and the lane's
@@ -47,10 +88,7 @@ __device__ inline void combine_row(int ns, PartialRow prow_of, const float* __re
             acc.z = fmaf(w, a[s].z, acc.z); acc.w = fmaf(w, a[s].w, acc.w);
         }
         const float inv = L > 0.f ? 1.f / L : 0.f;
-        if (d < D) {
-            orow[d] = Num<T>::from_f(acc.x * inv); orow[d + 1] = Num<T>::from_f(acc.y * inv);
-            orow[d + 2] = Num<T>::from_f(acc.z * inv); orow[d + 3] = Num<T>::from_f(acc.w * inv);
-        }
+        if (d < D) sink.put(d, make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv), 4);
         return;
     }
     float M = -INFINITY;
@@ -103,17 +141,16 @@ __device__ inline void combine_row(int ns, PartialRow prow_of, const float* __re
     for (int r = 0; r < 2; ++r) {
         const int d = r * 128 + lane * 4;
         if (d >= D) continue;
-        orow[d] = Num<T>::from_f(acc[r].x * inv);
-        if (d + 1 < D) orow[d + 1] = Num<T>::from_f(acc[r].y * inv);
-        if (d + 2 < D) orow[d + 2] = Num<T>::from_f(acc[r].z * inv);
-        if (d + 3 < D) orow[d + 3] = Num<T>::from_f(acc[r].w * inv);
+        sink.put(d, make_float4(acc[r].x * inv, acc[r].y * inv, acc[r].z * inv, acc[r].w * inv), min(4, D - d));
     }
 }
 
-// Output rows = n_q * Hq, row = (query row r, head h).
-template <typename T>
+// Output rows = n_q * Hq, row = (query row r, head h). GATHER: rows go to every rank's full
+// output instead of `out`, and the last CTA to finish publishes the epoch (see RfxHeadGatherArgs).
+template <typename T, bool GATHER>
 __global__ void __launch_bounds__(kCombineWarps * 32)
-paged_combine_kernel(T* __restrict__ out, const int32_t* __restrict__ q_start, int B, int64_t n_q, int Hq,
+paged_combine_kernel(T* __restrict__ out, const __grid_constant__ HeadGatherDev hg,
+                     const int32_t* __restrict__ q_start, int B, int64_t n_q, int Hq,
                      int Hkv, int D, int rows_follow_items, const int32_t* __restrict__ pair_item_begin,
                      const int32_t* __restrict__ item_prow, const float* __restrict__ pm,
                      const float* __restrict__ pl, const float* __restrict__ pacc) {
@@ -143,11 +180,47 @@ paged_combine_kernel(T* __restrict__ out, const int32_t* __restrict__ q_start, i
         const int item0 = pair_item_begin[pair];
         const int ns = pair_item_begin[pair + 1] - item0;
         const int within = qi * G + g;
-        if (rows_follow_items)  // one query row per request: item i owns partial rows [i*G, i*G + G)
-            combine_row<T>(ns, [&](int s) { return (long long)(item0 + s) * G + g; }, pm, pl, pacc, D, out + orow * D);
+        auto run = [&](const auto& sink) {
+            if (rows_follow_items)  // one query row per request: item i owns partial rows [i*G, i*G + G)
+                combine_row<T>(ns, [&](int s) { return (long long)(item0 + s) * G + g; }, pm, pl, pacc, D, sink);
+            else
+                combine_row<T>(ns, [&](int s) { return (long long)item_prow[item0 + s] + within; }, pm, pl, pacc, D,
+                               sink);
+        };
+        if (GATHER)
+            run(PeerRows<T>{&hg, (r * ((int64_t)hg.world * Hq) + (int64_t)hg.rank * Hq + h) * D});
         else
-            combine_row<T>(ns, [&](int s) { return (long long)item_prow[item0 + s] + within; }, pm, pl, pacc, D,
-                           out + orow * D);
+            run(LocalRow<T>{out + orow * D});
+    }
+    if (GATHER) {
+        // Every thread's stores are visible system-wide before its CTA is counted.
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned prev = atomicAdd(hg.counter, 1u);
+            if (prev == gridDim.x - 1) {  // all CTAs of this rank have stored their rows
+                __threadfence();
+                *hg.counter = 0;  // for the next launch on this stream
+                __threadfence_system();
+                for (int p = 0; p < hg.world; ++p)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(hg.flags[p] + hg.rank), "r"(hg.epoch) : "memory");
+                if (hg.wait) {
+                    bool expired = false;
+                    for (int q = 0; q < hg.world && !expired; ++q) {
+                        const uint32_t* f = hg.flags[hg.rank] + q;
+                        long long polls = 0;
+                        for (;;) {
+                            uint32_t v;
+                            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                            if ((int32_t)(v - hg.epoch) >= 0) break;
+                            if (++polls > hg.spin_limit) { expired = true; break; }
+                            __nanosleep(100);
+                        }
+                    }
+                    if (expired && hg.status) atomicOr(hg.status, kStatusWaitExpired);
+                }
+            }
+        }
     }
 }
 
@@ -160,19 +233,40 @@ splitk_combine_kernel(T* __restrict__ out, const int32_t* __restrict__ split_beg
     for (int64_t r = (int64_t)blockIdx.x * kCombineWarps + warp; r < rows;
          r += (int64_t)gridDim.x * kCombineWarps) {
         const int s0 = split_begin[r], ns = split_begin[r + 1] - s0;
-        combine_row<T>(ns, [&](int s) { return (long long)(s0 + s); }, pm, pl, pacc, D, out + r * D);
+        combine_row<T>(ns, [&](int s) { return (long long)(s0 + s); }, pm, pl, pacc, D, LocalRow<T>{out + r * D});
     }
 }
 
-int launch_paged_combine(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P) {
+int launch_paged_combine(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P,
+                         const RfxHeadGatherArgs* g) {
     const int64_t rows = a->n_q * a->num_q_heads;
     int64_t blocks = ceil_div<int64_t>(rows, kCombineWarps);
     const int64_t cap = (int64_t)sm_count() * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
+    HeadGatherDev hg = {};
+    if (g) {
+        const char* name = "rfx_paged_attention_combine_gather";
+        RFX_REQUIRE(g->world >= 1 && g->world <= RFX_MAX_PEERS && g->rank >= 0 && g->rank < g->world,
+                    "%s: rank %d of %d (at most %d ranks)", name, g->rank, g->world, RFX_MAX_PEERS);
+        RFX_REQUIRE(g->epoch > 0 && g->arrival_counter, "%s: epoch must be > 0 and arrival_counter set", name);
+        for (int p = 0; p < g->world; ++p) {
+            RFX_REQUIRE(g->peer_out[p] && g->peer_flags[p], "%s: null pointer for rank %d", name, p);
+            RFX_REQUIRE(((uintptr_t)g->peer_out[p] % 16) == 0 && ((uintptr_t)g->peer_flags[p] % 4) == 0,
+                        "%s: misaligned buffer for rank %d", name, p);
+            hg.out[p] = g->peer_out[p];
+            hg.flags[p] = g->peer_flags[p];
+        }
+        hg.counter = g->arrival_counter;
+        hg.status = P.hdr + HdrStatus;
+        hg.spin_limit = g->spin_limit > 0 ? g->spin_limit : 10000000ll;
+        hg.epoch = g->epoch;
+        hg.world = g->world; hg.rank = g->rank; hg.wait = g->wait ? 1 : 0;
+    }
     RFX_DISPATCH_DTYPE(a->dtype, T, {
-        cudaError_t le = launch_pdl(paged_combine_kernel<T>, dim3((int)blocks), dim3(kCombineWarps * 32), 0,
-                                    as_stream(a->stream), (T*)a->out, a->q_start, (int)a->batch, (int64_t)a->n_q,
+        auto kern = g ? paged_combine_kernel<T, true> : paged_combine_kernel<T, false>;
+        cudaError_t le = launch_pdl(kern, dim3((int)blocks), dim3(kCombineWarps * 32), 0,
+                                    as_stream(a->stream), (T*)a->out, hg, a->q_start, (int)a->batch, (int64_t)a->n_q,
                                     (int)a->num_q_heads, (int)a->num_kv_heads, (int)a->head_dim,
                                     a->q_start == nullptr ? 1 : 0, (const int32_t*)P.pair_item_begin,
                                     (const int32_t*)P.item_prow, (const float*)P.m, (const float*)P.l,

@@ -92,6 +92,8 @@ size_t rfx_args_size(int which) {
         case 6: return sizeof(RfxAttentionArgs);
         case 7: return sizeof(RfxPagedAttentionArgs);
         case 8: return sizeof(RfxCombineArgs);
+        case 9: return sizeof(RfxHeadGatherArgs);
+        case 10: return sizeof(RfxPeerHandle);
         default: return 0;
     }
 }

@@ -62,11 +62,13 @@ extern "C" int rfx_paged_attention_plan(const RfxPagedAttentionArgs* a) {
 namespace rfx {
 enum : int { kStagePlan = 1, kStagePartials = 2, kStageCombine = 4 };
 
-static int run_stages(const RfxPagedAttentionArgs* a, const char* name, int stages) {
+static int run_stages(const RfxPagedAttentionArgs* a, const char* name, int stages,
+                      const RfxHeadGatherArgs* gather = nullptr) {
     int st = validate(a, name);
     if (st != RFX_SUCCESS) return st;
     if (a->batch == 0 || a->n_q == 0) return RFX_SUCCESS;
-    RFX_REQUIRE(a->q && a->out && a->k_cache && a->v_cache && a->block_table && a->context_lens && a->workspace,
+    RFX_REQUIRE(a->q && (a->out || gather) && a->k_cache && a->v_cache && a->block_table && a->context_lens &&
+                    a->workspace,
                 "%s: null pointer", name);
     st = check_device();
     if (st != RFX_SUCCESS) return st;
@@ -79,6 +81,7 @@ static int run_stages(const RfxPagedAttentionArgs* a, const char* name, int stag
         // Query chunks on the tcgen05 kernel.
         if (!prefill_paged_split(a)) {
             // whole rows per CTA: no plan and no combine
+            if (gather) return fail(RFX_NOT_IMPLEMENTED, "%s: the head gather rides on the combine kernel", name);
             if (!(stages & kStagePartials)) return RFX_SUCCESS;
             cudaError_t e = cudaMemsetAsync(P.hdr + HdrStatus, 0, sizeof(int32_t), as_stream(a->stream));
             if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "%s: cudaMemsetAsync: %s", name, cudaGetErrorString(e));
@@ -92,7 +95,7 @@ static int run_stages(const RfxPagedAttentionArgs* a, const char* name, int stag
             st = launch_prefill_paged(a, P.hdr + HdrStatus, &L, &P);
             if (st != RFX_SUCCESS) return st;
         }
-        if (stages & kStageCombine) return launch_paged_combine(a, L, P);
+        if (stages & kStageCombine) return launch_paged_combine(a, L, P, gather);
         return RFX_SUCCESS;
     }
     const bool mma = decode_mma_supported(a);
@@ -104,7 +107,7 @@ static int run_stages(const RfxPagedAttentionArgs* a, const char* name, int stag
         st = mma ? launch_decode_mma(a, L, P) : launch_paged_generic(a, L, P);
         if (st != RFX_SUCCESS) return st;
     }
-    if (stages & kStageCombine) return launch_paged_combine(a, L, P);
+    if (stages & kStageCombine) return launch_paged_combine(a, L, P, gather);
     return RFX_SUCCESS;
 }
 }  // namespace rfx
@@ -127,6 +130,18 @@ extern "C" int rfx_paged_attention_kernel_kind(const RfxPagedAttentionArgs* a) {
 
 extern "C" int rfx_paged_attention_combine(const RfxPagedAttentionArgs* a) {
     return rfx::run_stages(a, "rfx_paged_attention_combine", rfx::kStageCombine);
+}
+
+extern "C" int rfx_paged_attention_combine_gather(const RfxPagedAttentionArgs* a, const RfxHeadGatherArgs* g) {
+    if (!g) return rfx::fail(RFX_INVALID_ARGUMENT, "rfx_paged_attention_combine_gather: null gather args");
+    return rfx::run_stages(a, "rfx_paged_attention_combine_gather", rfx::kStageCombine, g);
+}
+
+extern "C" int rfx_paged_attention_gather(const RfxPagedAttentionArgs* a, const RfxHeadGatherArgs* g) {
+    using namespace rfx;
+    if (!g) return fail(RFX_INVALID_ARGUMENT, "rfx_paged_attention_gather: null gather args");
+    const int plan = (a && a->reuse_plan) ? 0 : kStagePlan;
+    return run_stages(a, "rfx_paged_attention_gather", plan | kStagePartials | kStageCombine, g);
 }
 
 // ---- paged attention without a caller workspace ----------------------------------------

@@ -92,7 +92,9 @@ inline PlanPtrs plan_ptrs(void* ws, const PlanLayout& L) {
 // partial kernel wants (its CTA count).
 int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int parts_hint);
 int launch_paged_generic(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P);
-int launch_paged_combine(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P);
+// `gather` != nullptr: rows go to every rank's full output (see RfxHeadGatherArgs).
+int launch_paged_combine(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P,
+                         const RfxHeadGatherArgs* gather = nullptr);
 bool decode_mma_supported(const RfxPagedAttentionArgs* a);
 int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P);
 int decode_mma_ctas(const RfxPagedAttentionArgs* a);

@@ -13,9 +13,14 @@
 //              page (or one per tile for dense K/V), two stages each, 128-byte swizzle.
 //   warp 9     MMA issuer: S_x = Q_x.K_j^T (8 x tcgen05.mma 128x128x16 from shared-memory
 //              descriptors), O_x += P_x.V_j with P read from TMEM and V as an MN-major
-//              shared-memory operand. The two tiles ping-pong: while one tile's warps run
-//              their softmax the tensor core works for the other. Completion through
-//              tcgen05.commit on mbarriers.
+//              shared-memory operand, in the fixed order [P_a.V, S_a'] [P_b.V, S_b'] ...: the two
+//              tiles ping-pong, one tile's warps run their softmax while the tensor core works
+//              for the other (two independent issuers fall into lock-step and lose that
+//              overlap). A barrier poll by the issuing thread costs hundreds of cycles (it
+//              competes with the tensor core's operand reads for shared memory), so the issuer
+//              waits only for P_x ready, which also carries the producer's vote that V_j and
+//              K_{j+1} have landed.
+//              Completion through tcgen05.commit on mbarriers.
 // TMEM: columns [0,128) S_a/P_a, [128,256) S_b/P_b, [256,384) O_a, [384,512) O_b (fp32).
 //
 // Causal masking is bottom-right aligned: token t of n sees keys 0..ctx-n+t; K tiles wholly
@@ -120,7 +125,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < PfSmem::n_bars; ++i)
-            ptx::mbar_init(&bars[i], (i == PF_PFULL || i == PF_PFULL + 1) ? 128u : 1u);
+            // P ready: the tile's 128 softmax threads and the producer's vote (see `landed`)
+            ptx::mbar_init(&bars[i], (i == PF_PFULL || i == PF_PFULL + 1) ? 129u : 1u);
         misc[1] = 0;
         ptx::fence_barrier_init();
     }
@@ -134,6 +140,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     auto give_up = [&]() {
         if (P.status) atomicOr(P.status, 1);
         *abort_flag = 1;
+    };
+    // Bounded wait. The abort flag is looked at only once the wait drags on: a shared-memory
+    // load costs > 100 cycles while the tensor core streams operands.
+    auto wait_phase = [&](int bar, uint32_t parity) -> bool {
+        for (uint32_t i = 0; i < (1u << 22); ++i) {
+            if (ptx::mbar_try_wait(&bars[bar], parity)) return true;
+            if (i > 1024) {
+                if (*abort_flag) return false;
+                __nanosleep(32);
+            }
+        }
+        return false;
     };
 
     if (warp == 8) {
@@ -154,6 +172,25 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 }
         }
         const int R = P.box_rows;
+        // The producer's vote on P_i ready (both tiles): V_i and K_{i+1} have landed. A barrier
+        // poll costs a few hundred cycles while the tensor core streams operands from shared
+        // memory, so it is kept out of the issuer's and the softmax warps' loops; this warp has
+        // the time.
+        auto landed = [&](int i) -> bool {
+            int ok = 1;
+            if (lane == 0) {
+                ok = wait_phase(PF_VFULL + i % kPfKvStages, (uint32_t)((i / kPfKvStages) & 1)) ? 1 : 0;
+                if (ok && i + 1 < n_kv)
+                    ok = wait_phase(PF_KFULL + (i + 1) % kPfKvStages, (uint32_t)(((i + 1) / kPfKvStages) & 1)) ? 1 : 0;
+                if (ok) {
+                    ptx::mbar_arrive(&bars[PF_PFULL + 0]);
+                    ptx::mbar_arrive(&bars[PF_PFULL + 1]);
+                } else {
+                    give_up();
+                }
+            }
+            return __shfl_sync(0xffffffffu, ok, 0) != 0;
+        };
         for (int j = 0; j < n_kv; ++j) {
             const int st = j % kPfKvStages;
             const uint32_t par = (uint32_t)((j / kPfKvStages) & 1);
@@ -178,11 +215,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             const uint32_t tx = (uint32_t)__popc(have) * (uint32_t)R * 128u * 2u;
             for (int which = 0; which < 2; ++which) {  // 0: K, 1: V
                 uint64_t* fullb = &bars[(which ? PF_VFULL : PF_KFULL) + st];
-                uint64_t* emptyb = &bars[(which ? PF_VEMPTY : PF_KEMPTY) + st];
                 int ok = 1;
-                if (lane == 0) ok = ptx::mbar_wait_bounded(emptyb, par ^ 1u) ? 1 : 0;
+                if (lane == 0) ok = wait_phase((which ? PF_VEMPTY : PF_KEMPTY) + st, par ^ 1u) ? 1 : 0;
                 ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok || *abort_flag) { if (lane == 0) give_up(); goto done; }
+                if (!ok) { if (lane == 0) give_up(); goto done; }
                 if (lane == 0) ptx::mbar_arrive_expect_tx(fullb, tx);
                 __syncwarp();
                 if (row >= 0) {
@@ -192,7 +228,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                     ptx::tma_load_2d(dst + kPfHalfBytes, m, fullb, 64, row);
                 }
             }
+            if (j > 0 && !landed(j - 1)) goto done;
         }
+        if (n_kv > 1) {
+            // The vote for the last tile must not fall into the phase of the tile before it (inside
+            // the loop the wait for a free V stage orders the votes): that phase is over once the
+            // P.V of tile n_kv-2 has released its V stage, which is what a load of tile n_kv would
+            // wait for.
+            int ok = 1;
+            if (lane == 0) {
+                ok = wait_phase(PF_VEMPTY + n_kv % kPfKvStages, (uint32_t)(((n_kv / kPfKvStages) & 1) ^ 1)) ? 1 : 0;
+                if (!ok) give_up();
+            }
+            if (!__shfl_sync(0xffffffffu, ok, 0)) goto done;
+        }
+        if (n_kv > 0 && !landed(n_kv - 1)) goto done;
     } else if (warp == 9) {
         // ------------------------------------------------------------------- MMA issuer --
         constexpr uint32_t idesc_s = ptx::umma_idesc_f16(128, 128, BF ? 1 : 0, 0, 0);   // Q, K both K-major
@@ -201,9 +251,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         // lane 0 waits, every lane learns the outcome
         auto wait_bar = [&](int bar, uint32_t parity) -> bool {
             int ok = 1;
-            if (lane == 0) ok = ptx::mbar_wait_bounded(&bars[bar], parity) ? 1 : 0;
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            return ok && !*abort_flag;
+            if (lane == 0) ok = wait_phase(bar, parity) ? 1 : 0;
+            return __shfl_sync(0xffffffffu, ok, 0) != 0;
         };
         auto issue_s = [&](int x, int jj) {  // S_x = Q_x . K_jj^T
             if (lane == 0) {
@@ -217,7 +266,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 ptx::umma_commit(&bars[PF_SFULL + x]);
                 if (x == 1) ptx::umma_commit(&bars[PF_KEMPTY + jj % kPfKvStages]);
             }
-            __syncwarp();
         };
         if (!wait_bar(PF_QFULL, 0)) { if (lane == 0) give_up(); goto done; }
         if (n_kv > 0) {
@@ -228,22 +276,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         }
         for (int j = 0; j < n_kv; ++j) {
             const int st = j % kPfKvStages;
+            // No waits for V_j and K_{j+1} here: the producer warp adds its vote to P_j ready only
+            // when both have landed.
+            const int valid = kv_end - (kb + j * kPfKeys);
             for (int x = 0; x < 2; ++x) {
                 if (!wait_bar(PF_PFULL + x, (uint32_t)(j & 1))) { if (lane == 0) give_up(); goto done; }
-                if (x == 0) {
-                    if (!wait_bar(PF_VFULL + st, (uint32_t)((j / kPfKvStages) & 1))) { if (lane == 0) give_up(); goto done; }
+                if (x == 0 && valid < kPfKeys) {
                     // keys at or past kv_end carry probability zero but may hold NaN patterns: clear those V rows
-                    const int valid = kv_end - (kb + j * kPfKeys);
-                    if (valid < kPfKeys) {
-                        unsigned char* vt = sV + (size_t)st * kPfTileBytes;
-                        for (int i = lane; i < (kPfKeys - valid) * 16; i += 32) {
-                            const int r = valid + i / 16, c = i % 16;
-                            *reinterpret_cast<uint4*>(vt + (size_t)(c >> 3) * kPfHalfBytes + (size_t)r * 128 +
-                                                      (size_t)(c & 7) * 16) = make_uint4(0, 0, 0, 0);
-                        }
-                        ptx::fence_proxy_async_smem();
-                        __syncwarp();
+                    unsigned char* vt = sV + (size_t)st * kPfTileBytes;
+                    for (int i = lane; i < (kPfKeys - valid) * 16; i += 32) {
+                        const int r = valid + i / 16, c = i % 16;
+                        *reinterpret_cast<uint4*>(vt + (size_t)(c >> 3) * kPfHalfBytes + (size_t)r * 128 +
+                                                  (size_t)(c & 7) * 16) = make_uint4(0, 0, 0, 0);
                     }
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
                 }
                 ptx::tc_fence_after_sync();
                 if (lane == 0) {
@@ -256,17 +303,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                     ptx::umma_commit(&bars[PF_PVDONE + x]);
                     if (x == 1) ptx::umma_commit(&bars[PF_VEMPTY + st]);
                 }
-                __syncwarp();
                 // next S for this tile right behind its P.V: the tensor pipe runs them in order,
                 // so the new scores land only after P has been read
-                if (j + 1 < n_kv) {
-                    if (x == 0 && !wait_bar(PF_KFULL + (j + 1) % kPfKvStages, (uint32_t)(((j + 1) / kPfKvStages) & 1))) {
-                        if (lane == 0) give_up();
-                        goto done;
-                    }
-                    ptx::tc_fence_after_sync();
-                    issue_s(x, j + 1);
-                }
+                if (j + 1 < n_kv) issue_s(x, j + 1);
             }
         }
     } else {
@@ -286,8 +325,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         float m_run = -INFINITY, l_run = 0.f;
         bool ok_all = true;
         for (int j = 0; j < n_kv && ok_all; ++j) {
-            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&bars[PF_SFULL + x], (uint32_t)(j & 1)) ? 1 : 0) ||
-                *abort_flag) {
+            if (!__all_sync(0xffffffffu, wait_phase(PF_SFULL + x, (uint32_t)(j & 1)) ? 1 : 0)) {
                 if (lane == 0) give_up();
                 ok_all = false;
                 break;
@@ -299,17 +337,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 #pragma unroll
             for (int c = 0; c < 4; ++c) ptx::tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
             ptx::tmem_wait_ld();
-            float mx = -INFINITY;
             if (need_mask) {
 #pragma unroll
-                for (int i = 0; i < 128; ++i) {
+                for (int i = 0; i < 128; ++i)
                     if (key0 + i > last_key) v[i] = 0xff800000u;  // -inf
-                    mx = fmaxf(mx, __uint_as_float(v[i]));
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
             }
+            // row maximum over eight independent chains (a single chain is 128 dependent steps)
+            float m8[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) m8[k] = __uint_as_float(v[k]);
+#pragma unroll
+            for (int i = 8; i < 128; i += 8) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) m8[k] = fmaxf(m8[k], __uint_as_float(v[i + k]));
+            }
+            float mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])),
+                             fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
             mx *= P.scale_log2;  // scale > 0, so max and scale commute
             const bool grow = mx > m_run + kPfRescaleTau;  // also true for the first finite maximum
             if (__any_sync(0xffffffffu, grow)) {
@@ -318,7 +361,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 if (j > 0) {
                     // O holds tiles 0..j-1 once P.V of tile j-1 is done
                     if (!__all_sync(0xffffffffu,
-                                    ptx::mbar_wait_bounded(&bars[PF_PVDONE + x], (uint32_t)((j - 1) & 1)) ? 1 : 0)) {
+                                    wait_phase(PF_PVDONE + x, (uint32_t)((j - 1) & 1)) ? 1 : 0)) {
                         if (lane == 0) give_up();
                         ok_all = false;
                         break;
@@ -340,7 +383,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             }
             const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
             // probabilities, packed to 16 bits, written over the S columns (all already in registers)
-            float lsum = 0.f;
+            float ls[4] = {0.f, 0.f, 0.f, 0.f};  // independent partial sums
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint32_t pk[16];
@@ -348,7 +391,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 for (int i = 0; i < 32; i += 2) {
                     const float p0 = ptx::ex2(fmaf(__uint_as_float(v[c * 32 + i]), P.scale_log2, -m_use));
                     const float p1 = ptx::ex2(fmaf(__uint_as_float(v[c * 32 + i + 1]), P.scale_log2, -m_use));
-                    lsum += p0 + p1;
+                    ls[(i >> 1) & 3] += p0 + p1;
                     if (BF) {
                         __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                         pk[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
@@ -359,14 +402,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 }
                 ptx::tmem_st16(s_addr + c * 16, pk);
             }
-            l_run += lsum;
+            l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
             ptx::tmem_wait_st();
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(&bars[PF_PFULL + x]);
         }
         // ---- epilogue: O / l -> global
         if (ok_all && n_kv > 0) {
-            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&bars[PF_PVDONE + x], (uint32_t)((n_kv - 1) & 1)) ? 1 : 0)) {
+            if (!__all_sync(0xffffffffu, wait_phase(PF_PVDONE + x, (uint32_t)((n_kv - 1) & 1)) ? 1 : 0)) {
                 if (lane == 0) give_up();
                 ok_all = false;
             }

@@ -126,6 +126,21 @@ class CombineArgs(C.Structure):
     ]
 
 
+RFX_MAX_PEERS = 16
+
+
+class HeadGatherArgs(C.Structure):
+    _fields_ = [
+        ("world", C.c_int), ("rank", C.c_int),
+        ("peer_out", vp * RFX_MAX_PEERS), ("peer_flags", vp * RFX_MAX_PEERS),
+        ("arrival_counter", vp), ("epoch", C.c_uint32), ("wait", C.c_int), ("spin_limit", i64),
+    ]
+
+
+class PeerHandle(C.Structure):
+    _fields_ = [("handle", C.c_ubyte * 64), ("offset", i64)]
+
+
 # Every symbol include/reflex_b200.h declares: (name, restype, argtypes).
 EXPORTS = {
     "rfx_abi_version": (C.c_int, []),
@@ -151,12 +166,17 @@ EXPORTS = {
     "rfx_paged_attention_static": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_splitk_combine": (C.c_int, [C.POINTER(CombineArgs)]),
     "rfx_paged_attention_status": (C.c_int, [vp, vp, C.POINTER(C.c_int)]),
+    "rfx_paged_attention_combine_gather": (C.c_int, [C.POINTER(PagedAttentionArgs), C.POINTER(HeadGatherArgs)]),
+    "rfx_paged_attention_gather": (C.c_int, [C.POINTER(PagedAttentionArgs), C.POINTER(HeadGatherArgs)]),
+    "rfx_peer_export": (C.c_int, [vp, C.POINTER(PeerHandle)]),
+    "rfx_peer_open": (C.c_int, [C.POINTER(PeerHandle), C.POINTER(vp), C.POINTER(vp)]),
+    "rfx_peer_close": (C.c_int, [vp]),
 }
 
 
 # Index of each mirror in rfx_args_size().
 ARG_STRUCTS = [KvAppendArgs, KvLookupArgs, RopeArgs, RopeTableArgs, RopeAppendArgs, SoftmaxArgs,
-               AttentionArgs, PagedAttentionArgs, CombineArgs]
+               AttentionArgs, PagedAttentionArgs, CombineArgs, HeadGatherArgs, PeerHandle]
 
 
 def library_path() -> Path:
@@ -242,3 +262,27 @@ def call(name: str, args: C.Structure, dev: torch.device) -> None:
     fn = getattr(lib(), name)
     with torch.cuda.device(dev):
         check(fn(C.byref(args)))
+
+
+def peer_export(device_ptr: int, dev: torch.device) -> bytes:
+    """Handle (bytes, picklable) under which another process can map the allocation holding
+    ``device_ptr``; see ``peer_open``."""
+    h = PeerHandle()
+    with torch.cuda.device(dev):
+        check(lib().rfx_peer_export(device_ptr, C.byref(h)))
+    return bytes(h)
+
+
+def peer_open(handle: bytes, dev: torch.device):
+    """Maps a buffer exported by another process. Returns ``(pointer, base)``; ``base`` goes to
+    ``peer_close``."""
+    h = PeerHandle.from_buffer_copy(handle)
+    mapped, base = vp(), vp()
+    with torch.cuda.device(dev):
+        check(lib().rfx_peer_open(C.byref(h), C.byref(mapped), C.byref(base)))
+    return int(mapped.value), int(base.value)
+
+
+def peer_close(base: int, dev: torch.device) -> None:
+    with torch.cuda.device(dev):
+        check(lib().rfx_peer_close(base))

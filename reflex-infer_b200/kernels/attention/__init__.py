@@ -245,6 +245,28 @@ class PagedAttentionCall:
         self._call(self._lib.rfx_paged_attention_combine)
         return self.out
 
+    def run_gather(self, gather, reuse_plan: bool = False) -> torch.Tensor:
+        """``run()`` for a rank that holds a slice of the heads: the combine kernel stores this
+        rank's heads into every rank's full output and the ranks meet inside the kernel
+        (``gather``: a ``sharding.FusedHeadGather``). Returns this rank's full ``[N, H_q_total, D]``
+        output of the step; it stays valid until the step after the next one."""
+        import ctypes as C
+        g, full = gather.next_args()
+        self._args.reuse_plan = int(bool(reuse_plan))
+        self._args.stream = N.stream_handle(self.device)
+        with torch.cuda.device(self.device):
+            N.check(self._lib.rfx_paged_attention_gather(self._ref, C.byref(g)))
+        return full
+
+    def combine_gather(self, gather) -> torch.Tensor:
+        """The combine stage alone, with the gather (after ``plan()`` and ``partials()``)."""
+        import ctypes as C
+        g, full = gather.next_args()
+        self._args.stream = N.stream_handle(self.device)
+        with torch.cuda.device(self.device):
+            N.check(self._lib.rfx_paged_attention_combine_gather(self._ref, C.byref(g)))
+        return full
+
 
 def paged_attention(
     q: torch.Tensor,

@@ -111,6 +111,96 @@ class HeadGather:
         return self.full
 
 
+class FusedHeadGather:
+    """The head gather without a collective call: each rank's combine kernel stores its head
+    slice of every output row straight into all ranks' full outputs through peer-mapped
+    pointers, and the ranks meet at a flag barrier inside the same kernel (bounded wait).
+
+    One buffer per rank holds the flag array and two full outputs (used alternately: a peer may
+    already write step k+1 while this rank still reads step k). It is exported once through
+    CUDA IPC; the handles travel through ``dist.all_gather_object``. One process per GPU."""
+
+    FLAG_BYTES = 256
+
+    def __init__(self, n_rows: int, local_heads: int, head_dim: int, dtype: torch.dtype, device, dist,
+                 spin_limit: int = 0, emulate_world: int = 0):
+        from kernels import _native as N
+        self.dist = dist
+        self.world = dist.get_world_size() if dist is not None else max(1, emulate_world)
+        self.rank = dist.get_rank() if dist is not None else 0
+        if self.world > N.RFX_MAX_PEERS:
+            raise ValueError(f"at most {N.RFX_MAX_PEERS} ranks, got {self.world}")
+        self.shape = (n_rows, self.world * local_heads, head_dim)
+        elt = torch.empty((), dtype=dtype).element_size()
+        self.out_bytes = -(-n_rows * self.world * local_heads * head_dim * elt // 256) * 256
+        self.buf = torch.zeros(self.FLAG_BYTES + 2 * self.out_bytes, dtype=torch.uint8, device=device)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.full = [self.buf[self.FLAG_BYTES + i * self.out_bytes:][:n_rows * self.shape[1] * head_dim * elt]
+                     .view(dtype).view(self.shape) for i in range(2)]
+        torch.cuda.synchronize(device)  # the zeros are in place before any peer can write
+        self._bases = []
+        self.ptrs = [0] * self.world
+        if self.world > 1 and dist is not None:
+            mine = N.peer_export(self.buf.data_ptr(), device)
+            handles = [None] * self.world
+            dist.all_gather_object(handles, mine)
+            for p, h in enumerate(handles):
+                if p == self.rank:
+                    self.ptrs[p] = self.buf.data_ptr()
+                else:
+                    mapped, base = N.peer_open(h, device)
+                    self.ptrs[p] = mapped
+                    self._bases.append(base)
+            dist.barrier()
+        else:
+            self.ptrs[0] = self.buf.data_ptr()
+        self.epoch = 0
+        self.device = device
+        self._args = N.HeadGatherArgs()
+        self._bind(spin_limit)
+
+    def _bind(self, spin_limit: int = 0, wait: bool = True) -> None:
+        a = self._args
+        a.world, a.rank = self.world, self.rank
+        a.arrival_counter = self.counter.data_ptr()
+        a.wait = int(bool(wait))
+        a.spin_limit = int(spin_limit)
+        for p in range(self.world):
+            a.peer_flags[p] = self.ptrs[p]
+
+    @classmethod
+    def over_local_buffers(cls, members, rank: int, wait: bool, spin_limit: int = 0):
+        """A member of a group whose buffers all live in this process (``members``: one gather
+        per emulated rank, each built with ``dist=None, emulate_world=len(members)``). For
+        single-GPU tests of the addressing and the flags; emulated ranks run one after another
+        and only the last one may wait."""
+        g = members[rank]
+        g.rank = rank
+        g.ptrs = [m.buf.data_ptr() for m in members]
+        g._args = type(g._args)()
+        g._bind(spin_limit, wait)
+        return g
+
+    def next_args(self):
+        """Arguments of the next step (advances the epoch) and the tensor that will hold its output."""
+        self.epoch += 1
+        a = self._args
+        a.epoch = self.epoch
+        off = self.FLAG_BYTES + (self.epoch & 1) * self.out_bytes
+        for p in range(self.world):
+            a.peer_out[p] = self.ptrs[p] + off
+        return a, self.full[self.epoch & 1]
+
+    def close(self) -> None:
+        from kernels import _native as N
+        torch.cuda.synchronize(self.device)
+        if self.dist is not None and self.world > 1:
+            self.dist.barrier()  # nobody unmaps while a peer may still store
+        for base in self._bases:
+            N.peer_close(base, self.device)
+        self._bases = []
+
+
 def merge_request_outputs(parts: Sequence[torch.Tensor], assignment: Sequence[Sequence[int]], q_start) -> torch.Tensor:
     """Host-side reassembly of request-sharded outputs (used by tests; a deployment keeps the
     rows where they are): parts[r] holds the rows of assignment[r]'s requests in order."""
