@@ -297,21 +297,27 @@ def pack_step_inputs(batch):
 
 class HostDrivenStep:
     """The same step fed from one pinned host buffer (all of the step's inputs), result read
-    back to pinned host memory."""
+    back to pinned host memory. With head sharding the step includes the gather (`post`: the
+    NCCL variant; the fused variant is inside the step) and rank 0 alone reads back the
+    assembled output, as a serving rank would."""
 
-    def __init__(self, step: DecodeStep, packed: torch.Tensor):
+    def __init__(self, step: DecodeStep, packed: torch.Tensor, post=None, read_back: bool = True):
         self.step = step
+        self.post = post
         self.dev = packed
         self.host = packed.cpu().pin_memory()
-        shape = step.gather.shape if step.gather is not None else step.out.shape
-        self.out_host = torch.empty(shape, dtype=step.out.dtype).pin_memory()
+        shape = step.gather.shape if step.gather is not None else (post.full.shape if post is not None else step.out.shape)
+        self.out_host = torch.empty(shape, dtype=step.out.dtype).pin_memory() if read_back else None
         self.h2d = self.host.numel()
-        self.d2h = self.out_host.numel() * self.out_host.element_size()
+        self.d2h = self.out_host.numel() * self.out_host.element_size() if read_back else 0
 
     def run(self):
         self.dev.copy_(self.host, non_blocking=True)
         out = self.step.run()
-        self.out_host.copy_(out, non_blocking=True)
+        if self.post is not None:
+            out = self.post.run(out)
+        if self.out_host is not None:
+            self.out_host.copy_(out, non_blocking=True)
 
 
 def timed_steps(fn, steps, warmup, flush=None, dist=None, with_kernel_events=False):
@@ -425,7 +431,8 @@ def measure(workload, args, device, rank, world, dist, want_e2e=True, sampler=No
            "kernel_ms_min": min(kern_ms), "status": status, "flush": flush_note, "kernel_kind": step.attn.kernel_kind,
            "launches": step.kernel_launches * args.steps, "gather_check": gather_check}
     if want_e2e:
-        host = HostDrivenStep(step, packed)
+        head_mode = world > 1 and args.shard == "head"
+        host = HostDrivenStep(step, packed, post=gather, read_back=(rank == 0 or not head_mode))
         e2e_ms, _ = timed_steps(host.run, args.steps, args.warmup, flush, dist)
         res.update(e2e_ms=e2e_ms, h2d=host.h2d, d2h=host.d2h)
     if sampler:
@@ -547,6 +554,7 @@ def check_against_oracle(res, n_req=2):
     """Cheap sanity outside every timed region: first requests of the batch vs the CPU oracle."""
     import oracle
     b = res["batch"]
+    res["step"].gather = None  # this check runs on one rank alone: local heads, plain combine
     out = res["step"].run()
     torch.cuda.synchronize()
     n = min(n_req, b.B)
