@@ -54,21 +54,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Hardware named barrier `id` (1..15; 0 is __syncthreads) over `nthreads` threads (a multiple of
-// 32, whole warps), returning the OR of the participants' predicates: a sync and a vote in one.
-__device__ __forceinline__ bool named_barrier_or(int id, int nthreads, bool pred) {
-    uint32_t r;
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "setp.ne.u32 p, %1, 0;\n\t"
-        "bar.red.or.pred q, %2, %3, p;\n\t"
-        "selp.u32 %0, 1, 0, q;\n\t}"
-        : "=r"(r)
-        : "r"((uint32_t)pred), "r"(id), "r"(nthreads)
-        : "memory");
-    return r != 0;
-}
-
 // Bounded wait: false after ~2^22 unsuccessful polls (each poll itself blocks for a
 // hardware-defined slice), so a lost completion can never hang the GPU.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
