@@ -476,7 +476,7 @@ def measure_prefill(args, device):
     return {"config": "cfg3: bf16 causal paged prefill, 8 x 2048 new tokens on an empty cache, 32q/8kv heads, D=128, "
                       "page 16, theta 1e6",
             "value": b.n_tokens * args.steps / (total_ms * 1e-3), "unit": UNIT, "ms_per_step": total_ms / args.steps,
-            "kernel": "prefill_tc_kernel" if attn.kernel_kind == 2 else "scalar",
+            "kernel": "prefill_tc_kernel" if attn.kernel_kind in (2, 3) else "scalar",
             "kernel_ms": km, "roofline": {"bound": "tensor", "achieved": flops / (km * 1e-3) / 1e12, "peak": burst,
                                           "unit": "TFLOP/s", "frac": flops / (km * 1e-3) / 1e12 / burst,
                                           "peak_sustained": peaks.get("bf16_tflops_sustained"),
@@ -543,7 +543,8 @@ def measure_mixed(args, device):
     return {"config": "cfg5: bf16 mixed batch, 64 requests x U[1,64] new tokens on contexts U[0,16384], 28q/4kv "
                       "heads, D=128, page 16, 1,048,576-page pool (40 % free), 10 % of requests compacted",
             "value": b.n_tokens * args.steps / (total_ms * 1e-3), "unit": UNIT, "ms_per_step": total_ms / args.steps,
-            "kernel": {2: "prefill_tc_kernel", 1: "decode_mma_kernel"}.get(attn.kernel_kind, "scalar"),
+            "kernel": {3: "prefill_tc_kernel + decode_mma_kernel (one-row requests)", 2: "prefill_tc_kernel",
+                       1: "decode_mma_kernel"}.get(attn.kernel_kind, "scalar"),
             "kernel_ms": km, "kv_gigabytes": kv / 1e9, "hbm_gbs": kv / (km * 1e-3) / 1e9,
             "hbm_frac": kv / (km * 1e-3) / 1e9 / peak, "tflops": flops / (km * 1e-3) / 1e12,
             "compaction_requests": len(move), "compaction_gigabytes_moved": moved / 1e9,

@@ -256,9 +256,11 @@ int rfx_paged_attention(const RfxPagedAttentionArgs* a);
 int rfx_paged_attention_partials(const RfxPagedAttentionArgs* a);
 /* Which kernel the arguments select: 2 = tcgen05 prefill kernel (16-bit, head_dim 128, ragged
  * query chunks given by q_start, queries already rotated, page size >= 8 dividing or a
- * multiple of 128; it needs no plan and no combine), 1 = TMA + warp-MMA decode kernel
- * (16-bit, head_dim 64/128, one query row per request, group <= 16, page size a divisor or
- * multiple of 64 and >= 8), 0 = scalar kernel, negative = invalid arguments. */
+ * multiple of 128; whole rows per CTA, or split over the keys with plan and combine when
+ * max_q_len <= 512 and pages hold <= 64 keys), 3 = the same split batch with its one-row
+ * requests on the decode kernel, 1 = TMA + warp-MMA decode kernel (16-bit, head_dim 64/128,
+ * one query row per request, group <= 16, page size a divisor or multiple of 64 and >= 8),
+ * 0 = scalar kernel, negative = invalid arguments. */
 int rfx_paged_attention_kernel_kind(const RfxPagedAttentionArgs* a);
 int rfx_paged_attention_combine(const RfxPagedAttentionArgs* a);
 

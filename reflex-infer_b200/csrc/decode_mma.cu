@@ -41,6 +41,7 @@ struct StageMeta {
 
 struct DecodeParams {
     const void* q;
+    const int32_t* q_start;  // mixed batches: the kernel takes the requests with one query row, at row q_start[b]
     const int64_t* block_table;
     const void* rcos;
     const void* rsin;
@@ -216,11 +217,16 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 // one round trip: lane j holds the descriptor of item ib + j
                 const int my_id = ib + lane;
                 int4 my_desc = make_int4(0, 0, 0, 0);
-                int my_prow = 0, my_pos = -1;
+                int my_prow = 0, my_pos = -1, my_qrow = -1;
                 if (my_id < i_end) {
                     my_desc = P.items[my_id];
                     my_prow = P.item_prow[my_id];
                     if (P.rcos) my_pos = P.rpos[my_desc.x];
+                    my_qrow = my_desc.x;
+                    if (P.q_start) {
+                        const int r0 = P.q_start[my_desc.x];
+                        my_qrow = (P.q_start[my_desc.x + 1] - r0 == 1) ? r0 : -1;  // other requests: not this kernel's
+                    }
                 }
                 const int n_here = min(32, i_end - ib);
                 auto load_win = [&](const int64_t* bt, int w0, int ke) -> int64_t {
@@ -242,6 +248,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     const int kb = __shfl_sync(0xffffffffu, my_desc.z, j), ke = __shfl_sync(0xffffffffu, my_desc.w, j);
                     const int prow = __shfl_sync(0xffffffffu, my_prow, j);
                     const int pos = __shfl_sync(0xffffffffu, my_pos, j);
+                    const int qrow = __shfl_sync(0xffffffffu, my_qrow, j);
                     const bool rotate = P.rcos != nullptr && pos >= 0 && (int64_t)pos < P.table_rows;
                     const int64_t* bt = P.block_table + (int64_t)b * P.bt_sb;
                     int win0 = kb / P.block_size;
@@ -254,6 +261,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         nx_cur = load_win(bt1, kb1 / P.block_size, ke1);
                         nx_nxt = load_win(bt1, kb1 / P.block_size + 32, ke1);
                     }
+                    if (qrow < 0) continue;
                     const int n_tiles = (ke - kb + kTile - 1) / kTile;
                     for (int t = 0; t < n_tiles && alive; ++t) {
                         const int tok0 = kb + t * kTile;
@@ -315,7 +323,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             // the item's query rows (contiguous: heads hkv*G .. hkv*G+G-1 of row b) and table rows
                             unsigned char* qd = sQ + (size_t)stage * S::kQSlot;
                             const unsigned char* qsrc = (const unsigned char*)P.q +
-                                                        ((int64_t)b * P.Hq + (int64_t)hkv * P.G) * S::kRowBytes;
+                                                        ((int64_t)qrow * P.Hq + (int64_t)hkv * P.G) * S::kRowBytes;
                             ptx::bulk_load(qd, qsrc, q_bytes, &full[stage]);
                             if (rotate) {
                                 ptx::bulk_load(qd + S::kQBytes, (const unsigned char*)P.rcos + (int64_t)pos * S::kRowBytes,
@@ -657,11 +665,11 @@ static bool box_rows_ok(int64_t bs) {
     return bs >= 8 && 64 % bs == 0;
 }
 
-bool decode_mma_supported(const RfxPagedAttentionArgs* a) {
+// Everything but the shape of the batch: dtype, head sizes, pages, alignment.
+bool decode_mma_shape_ok(const RfxPagedAttentionArgs* a) {
     if (a->force_generic) return false;
     if (a->dtype != RFX_BF16 && a->dtype != RFX_F16) return false;
     if (a->head_dim != 128 && a->head_dim != 64) return false;
-    if (a->q_start != nullptr || a->max_q_len > 1) return false;  // one query row per request
     const int64_t G = a->num_q_heads / a->num_kv_heads;
     if (G > 16) return false;
     if ((G * a->head_dim * 2) % 16) return false;  // bulk copies move multiples of 16 bytes
@@ -670,6 +678,11 @@ bool decode_mma_supported(const RfxPagedAttentionArgs* a) {
     if (a->rope_cos && (((uintptr_t)a->rope_cos % 16) || ((uintptr_t)a->rope_sin % 16))) return false;
     if (a->num_blocks * a->num_kv_heads * a->block_size >= (1ll << 31)) return false;
     return true;
+}
+
+bool decode_mma_supported(const RfxPagedAttentionArgs* a) {
+    if (a->q_start != nullptr || a->max_q_len > 1) return false;  // one query row per request
+    return decode_mma_shape_ok(a);
 }
 
 int decode_mma_ctas(const RfxPagedAttentionArgs*) { return sm_count(); }
@@ -694,7 +707,7 @@ static int launch_decode_t(const RfxPagedAttentionArgs* a, const CUtensorMap& km
     return check_launch("rfx_paged_attention (decode MMA kernel)");
 }
 
-int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const PlanPtrs& Pp) {
+int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const PlanPtrs& Pp, bool single_row_requests_only) {
     const int HD = (int)a->head_dim;
     const int G = (int)(a->num_q_heads / a->num_kv_heads);
     const int R = (int)(a->block_size < 64 ? a->block_size : 64);
@@ -720,6 +733,7 @@ int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const P
 
     DecodeParams P;
     P.q = a->q; P.block_table = a->block_table;
+    P.q_start = single_row_requests_only ? a->q_start : nullptr;
     P.rcos = a->rope_cos; P.rsin = a->rope_sin; P.rpos = a->rope_positions;
     P.hdr = Pp.hdr; P.part_first = Pp.part_first; P.items = Pp.items; P.item_prow = Pp.item_prow;
     P.pm = Pp.m; P.pl = Pp.l; P.pacc = Pp.acc;

@@ -92,7 +92,12 @@ static int run_stages(const RfxPagedAttentionArgs* a, const char* name, int stag
             if (st != RFX_SUCCESS) return st;
         }
         if (stages & kStagePartials) {
-            st = launch_prefill_paged(a, P.hdr + HdrStatus, &L, &P);
+            const bool mixed = prefill_paged_mixed(a);
+            if (mixed) {
+                st = launch_decode_mma(a, L, P, true);
+                if (st != RFX_SUCCESS) return st;
+            }
+            st = launch_prefill_paged(a, P.hdr + HdrStatus, &L, &P, mixed);
             if (st != RFX_SUCCESS) return st;
         }
         if (stages & kStageCombine) return launch_paged_combine(a, L, P, gather);
@@ -124,7 +129,7 @@ extern "C" int rfx_paged_attention_partials(const RfxPagedAttentionArgs* a) {
 
 extern "C" int rfx_paged_attention_kernel_kind(const RfxPagedAttentionArgs* a) {
     if (rfx::validate(a, "rfx_paged_attention_kernel_kind") != RFX_SUCCESS) return -1;
-    if (rfx::prefill_paged_supported(a)) return 2;
+    if (rfx::prefill_paged_supported(a)) return rfx::prefill_paged_mixed(a) ? 3 : 2;
     return rfx::decode_mma_supported(a) ? 1 : 0;
 }
 

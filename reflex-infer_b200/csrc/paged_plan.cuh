@@ -96,7 +96,11 @@ int launch_paged_generic(const RfxPagedAttentionArgs* a, const PlanLayout& L, co
 int launch_paged_combine(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P,
                          const RfxHeadGatherArgs* gather = nullptr);
 bool decode_mma_supported(const RfxPagedAttentionArgs* a);
-int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P);
+bool decode_mma_shape_ok(const RfxPagedAttentionArgs* a);  // ... whatever the number of query rows per request
+// `single_row_requests_only`: a mixed batch (q_start given); requests with more than one query
+// row are left to the tcgen05 kernel.
+int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P,
+                      bool single_row_requests_only = false);
 int decode_mma_ctas(const RfxPagedAttentionArgs* a);
 // tcgen05 kernel for ragged query chunks (prefill_tc.cu).
 bool prefill_paged_supported(const RfxPagedAttentionArgs* a);
@@ -104,6 +108,8 @@ bool prefill_paged_split(const RfxPagedAttentionArgs* a);  // split-K over the p
 int prefill_paged_parts(const RfxPagedAttentionArgs* a);
 // `split` = nullptr: whole rows per CTA, output written directly; else partials for the combine.
 int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, const PlanLayout* L,
-                         const PlanPtrs* split);
+                         const PlanPtrs* split, bool skip_single_row_requests = false);
+// Mixed batches: decode rows on the TMA/MMA decode kernel, longer chunks on the tcgen05 kernel.
+bool prefill_paged_mixed(const RfxPagedAttentionArgs* a);
 
 }  // namespace rfx

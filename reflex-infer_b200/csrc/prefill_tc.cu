@@ -58,6 +58,7 @@ struct PrefillParams {
     float* pl;
     float* pacc;
     int items_cap;
+    int skip_single;                           // split-K mode: requests with one query row belong to the decode kernel
     int64_t bt_sb, max_blocks, num_blocks;
     int B, Hq, Hkv, G, T;                      // T = query tokens per tile = 128 / G
     int Sq, Sk;                                // dense sizes (paged: Sq = host bound on rows per request)
@@ -116,12 +117,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     const int n_q = P.q_start ? (P.q_start[b + 1] - q0) : P.Sq;
     const int ctx = P.ctx_lens ? max(0, P.ctx_lens[b]) : P.Sk;
     const int tok0 = qt * 2 * P.T;                  // tile a: tok0.., tile b: tok0 + T..
-    if (tok0 >= n_q) return;  // uniform over the CTA; nothing allocated yet
+    if (tok0 >= n_q || (P.skip_single && n_q == 1)) return;  // uniform over the CTA; nothing allocated yet
     const int off = ctx - n_q;                      // bottom-right: token t sees keys <= t + off
     const int last_tok = min(n_q, tok0 + 2 * P.T) - 1;
     // keys [kb, kv_end) are streamed: the item's range cut at the causal bound of the last row
     const int kv_end = min(ke_item, P.causal ? max(0, min(ctx, last_tok + off + 1)) : ctx);
     const int n_kv = kv_end > kb ? (kv_end - kb + kPfKeys - 1) / kPfKeys : 0;
+    const int n_tiles = (tok0 + P.T < n_q) ? 2 : 1;  // a short chunk leaves tile b without rows: it is not run
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < PfSmem::n_bars; ++i)
@@ -161,8 +163,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             ptx::prefetch_tensormap(&kmap);
             ptx::prefetch_tensormap(&vmap);
             // Q: two tiles x two 64-wide halves; rows beyond T*G stay stale and are never stored
-            ptx::mbar_arrive_expect_tx(&bars[PF_QFULL], 4u * (uint32_t)(P.T * P.G) * 128u);
-            for (int x = 0; x < 2; ++x)
+            ptx::mbar_arrive_expect_tx(&bars[PF_QFULL], 2u * (uint32_t)n_tiles * (uint32_t)(P.T * P.G) * 128u);
+            for (int x = 0; x < n_tiles; ++x)
                 for (int h = 0; h < 2; ++h) {
                     unsigned char* dst = sQ + x * kPfTileBytes + h * kPfHalfBytes;
                     if (P.head_major_rows)
@@ -184,7 +186,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                     ok = wait_phase(PF_KFULL + (i + 1) % kPfKvStages, (uint32_t)(((i + 1) / kPfKvStages) & 1)) ? 1 : 0;
                 if (ok) {
                     ptx::mbar_arrive(&bars[PF_PFULL + 0]);
-                    ptx::mbar_arrive(&bars[PF_PFULL + 1]);
+                    if (n_tiles == 2) ptx::mbar_arrive(&bars[PF_PFULL + 1]);
                 } else {
                     give_up();
                 }
@@ -264,7 +266,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                                  ptx::umma_desc_sw128(k_addr + o2, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
                 }
                 ptx::umma_commit(&bars[PF_SFULL + x]);
-                if (x == 1) ptx::umma_commit(&bars[PF_KEMPTY + jj % kPfKvStages]);
+                if (x == n_tiles - 1) ptx::umma_commit(&bars[PF_KEMPTY + jj % kPfKvStages]);
             }
         };
         if (!wait_bar(PF_QFULL, 0)) { if (lane == 0) give_up(); goto done; }
@@ -272,14 +274,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             if (!wait_bar(PF_KFULL + 0, 0)) { if (lane == 0) give_up(); goto done; }
             ptx::tc_fence_after_sync();
             issue_s(0, 0);
-            issue_s(1, 0);
+            if (n_tiles == 2) issue_s(1, 0);
         }
         for (int j = 0; j < n_kv; ++j) {
             const int st = j % kPfKvStages;
             // No waits for V_j and K_{j+1} here: the producer warp adds its vote to P_j ready only
             // when both have landed.
             const int valid = kv_end - (kb + j * kPfKeys);
-            for (int x = 0; x < 2; ++x) {
+            for (int x = 0; x < n_tiles; ++x) {
                 if (!wait_bar(PF_PFULL + x, (uint32_t)(j & 1))) { if (lane == 0) give_up(); goto done; }
                 if (x == 0 && valid < kPfKeys) {
                     // keys at or past kv_end carry probability zero but may hold NaN patterns: clear those V rows
@@ -301,7 +303,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                         ptx::umma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
                     }
                     ptx::umma_commit(&bars[PF_PVDONE + x]);
-                    if (x == 1) ptx::umma_commit(&bars[PF_VEMPTY + st]);
+                    if (x == n_tiles - 1) ptx::umma_commit(&bars[PF_VEMPTY + st]);
                 }
                 // next S for this tile right behind its P.V: the tensor pipe runs them in order,
                 // so the new scores land only after P has been read
@@ -320,6 +322,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         const int g = P.head_major_rows ? (r / P.T) : (r % P.G);
         const int tok = tok0 + x * P.T + t_loc;
         const bool row_live = r < rows_used && tok < n_q;
+        // A warp without a live row only keeps the barriers going; a tile without one is not run.
+        const bool warp_live = __any_sync(0xffffffffu, row_live);
+        if (x >= n_tiles) goto done;
         // keys 0..last_key are visible to this row; -1 for a dead row masks everything
         const int last_key = row_live ? min(kv_end - 1, P.causal ? min(ctx - 1, tok + off) : ctx - 1) : -1;
         float m_run = -INFINITY, l_run = 0.f;
@@ -331,8 +336,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 break;
             }
             ptx::tc_fence_after_sync();
+            if (!warp_live) {  // nothing to compute: P of these rows stays whatever S was, O rows are never read
+                ptx::tc_fence_before_sync();
+                ptx::mbar_arrive(&bars[PF_PFULL + x]);
+                continue;
+            }
             const int key0 = kb + j * kPfKeys;
-            const bool need_mask = key0 + kPfKeys - 1 > last_key;
+            // rows without a query (stale Q, results never stored) take no mask and trigger no rescale
+            const bool need_mask = row_live && key0 + kPfKeys - 1 > last_key;
             uint32_t v[128];
 #pragma unroll
             for (int c = 0; c < 4; ++c) ptx::tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
@@ -354,7 +365,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             float mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])),
                              fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
             mx *= P.scale_log2;  // scale > 0, so max and scale commute
-            const bool grow = mx > m_run + kPfRescaleTau;  // also true for the first finite maximum
+            const bool grow = row_live && mx > m_run + kPfRescaleTau;  // also true for the first finite maximum
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = fmaxf(m_run, mx);
                 const float alpha = (m_new == -INFINITY) ? 1.f : ptx::ex2(m_run - m_new);
@@ -577,8 +588,21 @@ bool prefill_paged_split(const RfxPagedAttentionArgs* a) {
 
 int prefill_paged_parts(const RfxPagedAttentionArgs* a) { (void)a; return 2 * sm_count(); }
 
+// A request with a single query row fills 1/18th or less of a 128-row tile and still pays the
+// tile's step time (about 64 KB of K/V per 4600 cycles and SM, a quarter of HBM speed). When most
+// requests of a split batch are such decode rows they go to the decode kernel, which streams K/V
+// at HBM speed, and both kernels leave partials for the one combine. With few decode rows the
+// hand-over does not pay: the decode kernel's CTAs take the plan's runs in a fixed order and
+// the decode rows are spread unevenly over them. The host sees only the totals, so the rule is
+// "at most four query rows per request on average"; REFLEX_B200_MIXED=0/1 overrides it.
+bool prefill_paged_mixed(const RfxPagedAttentionArgs* a) {
+    if (!prefill_paged_split(a) || !decode_mma_shape_ok(a)) return false;
+    if (const char* e = getenv("REFLEX_B200_MIXED")) return e[0] == '1';
+    return a->n_q <= 4 * a->batch;
+}
+
 int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, const PlanLayout* L,
-                         const PlanPtrs* split) {
+                         const PlanPtrs* split, bool skip_single_row_requests) {
     const int G = (int)(a->num_q_heads / a->num_kv_heads);
     const int T = 128 / G;
     const int R = (int)(a->block_size < 128 ? a->block_size : 128);
@@ -617,6 +641,7 @@ int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, c
         int64_t cap = a->batch * a->num_kv_heads + (a->target_chunk > 0 ? L->max_parts : prefill_paged_parts(a));
         if (cap > L->max_items) cap = L->max_items;
         P.items_cap = (int)cap;
+        P.skip_single = skip_single_row_requests ? 1 : 0;
         grid = (int64_t)P.n_qtiles * cap;
     }
     if (grid >= (1ll << 31)) return fail(RFX_INVALID_ARGUMENT, "prefill grid too large");

@@ -205,7 +205,7 @@ class PagedAttentionCall:
         buf = workspace.ensure(max(int(need), 256))
         a.workspace = buf.data_ptr()
         a.workspace_bytes = buf.numel()
-        self.kernel_kind = int(lib.rfx_paged_attention_kernel_kind(C.byref(a)))  # 1 TMA/MMA, 0 scalar
+        self.kernel_kind = int(lib.rfx_paged_attention_kernel_kind(C.byref(a)))  # 3/2 tcgen05 (3: one-row requests on the decode kernel), 1 TMA/MMA decode, 0 scalar
         self.out = out
         self.workspace = workspace
         self.device = dev

@@ -63,14 +63,14 @@ def test_cfg3_paged_prefill_small_and_kv_bit_exact(native):
     ws = PagedWorkspace(DEV)
     call = PagedAttentionCall(q_gpu, gpu.k_cache, gpu.v_cache, gpu.block_table, gpu.context_lens, q_start=gpu.q_start,
                               max_q_len=cpu.max_q_len, workspace=ws)
-    assert call.kernel_kind == 2
+    assert call.kernel_kind in (2, 3)  # 3: split over the keys, one-row requests on the decode kernel
     out = call.run()
     assert ws.status() == 0
     torch.testing.assert_close(out.cpu().float(), ref.float(), atol=2e-2, rtol=2e-2)
 
 
 @pytest.mark.parametrize("bs", [8, 16, 64, 128, 256])
-def test_chunked_prefill_mixed_batch_tensor_core(bs, native):
+def test_chunked_prefill_mixed_batch_tensor_core(bs, native, monkeypatch):
     """Configuration 5 in small on the tensor-core kernel: ragged chunks with decode rows among
     them, 28/4 heads (group of 7: 18 tokens x 7 heads per tile), existing contexts, several page
     sizes; cross-checked against the scalar kernel too."""
@@ -107,6 +107,37 @@ def test_chunked_prefill_mixed_batch_tensor_core(bs, native):
                                 target_chunk=chunk, **kw)
         assert ws.status() == 0 and torch.isfinite(out_c).all()
         torch.testing.assert_close(out_c.cpu().float(), ref.float(), atol=2e-2, rtol=2e-2)
+    # the one-row requests handed to the decode kernel (on by itself only for decode-heavy batches)
+    monkeypatch.setenv("REFLEX_B200_MIXED", "1")
+    call = PagedAttentionCall(q_rot.to(DEV), kc.to(DEV), vc.to(DEV), g.block_table, g.context_lens, **kw)
+    if bs <= 64:
+        assert call.kernel_kind == 3
+    out_m = call.run()
+    assert ws.status() == 0
+    torch.testing.assert_close(out_m.cpu().float(), ref.float(), atol=2e-2, rtol=2e-2)
+
+
+def test_decode_heavy_mixed_batch_hands_rows_to_decode_kernel(native):
+    """Twenty decode rows and two chunks in one batch: the decode rows run on the TMA/MMA decode
+    kernel, the chunks on the tensor-core kernel, one combine merges both kinds of partials."""
+    cos, sin = oracle.build_rope_tables(1200, 128, base=1e6, dtype=torch.bfloat16)
+    cpu = workloads.make_paged_batch("heavy", B=22, Hq=16, Hkv=2, D=128, block_size=16, ctx_range=(30, 1000),
+                                     new_range=(20, 21), decode_fraction=0.91, num_blocks=2048, seed=77, tables=(cos, sin))
+    assert cpu.n_tokens <= 4 * cpu.B
+    pos = cpu.positions.long()
+    q_rot = oracle.apply_rope(cpu.q_new.unsqueeze(0), cos[pos], sin[pos])[0]
+    k_rot = oracle.apply_rope(cpu.k_new.unsqueeze(0), cos[pos], sin[pos])[0]
+    kc, vc = cpu.k_cache.clone(), cpu.v_cache.clone()
+    oracle.kv_paged_append(k_rot, cpu.v_new, kc, vc, cpu.slot_mapping)
+    ref = oracle.paged_attention_composed(q_rot, kc, vc, cpu.block_table, cpu.context_lens, q_start=cpu.q_start.tolist())
+    g = cpu.to(DEV)
+    ws = PagedWorkspace(DEV)
+    call = PagedAttentionCall(q_rot.to(DEV), kc.to(DEV), vc.to(DEV), g.block_table, g.context_lens, q_start=g.q_start,
+                              max_q_len=cpu.max_q_len, workspace=ws)
+    assert call.kernel_kind == 3
+    out = call.run()
+    assert ws.status() == 0
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=2e-2, rtol=2e-2)
 
 
 def test_cfg3_full_request_properties(native):
