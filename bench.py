@@ -61,6 +61,9 @@ def parse_args():
                     help="--shard head: assemble the heads inside the combine kernel (peer stores) or with an "
                          "NCCL all-gather")
     ap.add_argument("--shard", default="replica", choices=["replica", "request", "head"])
+    ap.add_argument("--only", default=None, choices=["cfg3", "cfg5"],
+                    help="run just that secondary block on one GPU and print it (small profiling cases: "
+                         "--only cfg3 --requests 2)")
     ap.add_argument("--cpu-sample", type=int, default=0, help="requests in the CPU-baseline sample (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary configuration block")
@@ -448,7 +451,7 @@ def measure_prefill(args, device):
     the pool on the tcgen05 kernel. Tensor-pipe roofline on the attention kernel."""
     import workloads
     from kernels.attention import PagedAttentionCall, RopeAppendCall
-    b = workloads.cfg3(device=device)
+    b = workloads.cfg3(device=device, scale=(args.requests / 8.0 if args.requests else 1.0), seq=2048)
     q_rot = torch.empty_like(b.q_new)
     ra = RopeAppendCall(b.k_new, b.v_new, b.k_cache, b.v_cache, b.slot_mapping, b.positions, b.cos, b.sin,
                         q=b.q_new, q_out=q_rot)
@@ -473,8 +476,8 @@ def measure_prefill(args, device):
     except Exception:
         pass
     burst = float(peaks.get("bf16_tflops", 1590.0))
-    return {"config": "cfg3: bf16 causal paged prefill, 8 x 2048 new tokens on an empty cache, 32q/8kv heads, D=128, "
-                      "page 16, theta 1e6",
+    return {"config": f"cfg3: bf16 causal paged prefill, {b.B} x 2048 new tokens on an empty cache, 32q/8kv heads, "
+                      "D=128, page 16, theta 1e6",
             "value": b.n_tokens * args.steps / (total_ms * 1e-3), "unit": UNIT, "ms_per_step": total_ms / args.steps,
             "kernel": "prefill_tc_kernel" if attn.kernel_kind in (2, 3) else "scalar",
             "kernel_ms": km, "roofline": {"bound": "tensor", "achieved": flops / (km * 1e-3) / 1e12, "peak": burst,
@@ -680,9 +683,21 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_only(args):
+    from kernels import _native
+    _native.lib()
+    assert torch.cuda.is_available(), "bench.py needs a GPU"
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    block = measure_prefill(args, device) if args.only == "cfg3" else measure_mixed(args, device)
+    print(json.dumps({"only": args.only, "steps": args.steps, "warmup": args.warmup, **block}), flush=True)
+
+
 def main():
     args = parse_args()
-    if args.impl == "reference":
+    if args.only:
+        run_only(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

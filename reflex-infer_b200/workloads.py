@@ -224,8 +224,12 @@ def cfg3_shapes(scale: float = 1.0) -> dict:
                 theta=1e6, input_scale=0.5)
 
 
-def cfg3(device="cpu", seed=2, scale: float = 1.0, tables=None) -> PagedBatch:
+def cfg3(device="cpu", seed=2, scale: float = 1.0, tables=None, seq: Optional[int] = None) -> PagedBatch:
+    """`scale` shrinks batch and sequence together (tests); `seq` pins the sequence length, so
+    that `scale` then shrinks only the batch (small profiling cases of the full-length kernel)."""
     s = cfg3_shapes(scale)
+    if seq is not None:
+        s["S"] = int(seq)
     return make_paged_batch("cfg3", B=s["B"], Hq=s["Hq"], Hkv=s["Hkv"], D=s["D"], block_size=s["block_size"],
                             ctx_range=(0, 0), new_range=(s["S"], s["S"]), theta=s["theta"], device=device, seed=seed,
                             input_scale=s["input_scale"], fill_pool=False, tables=tables)
