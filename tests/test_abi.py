@@ -70,3 +70,30 @@ def test_workspace_size_query(native):
     assert n1 > 0 and n1 % 256 == 0
     p.batch = p.n_q = 64
     assert lib.rfx_paged_attention_workspace_bytes(C.byref(p)) > n1
+
+
+def test_cpp_header_compiles_and_links(native, tmp_path):
+    """The header-only C++ face (reference-style `Status`, args structs, `const Args&` calls)
+    compiles as C++17, links against the library and reports an argument error as a status."""
+    import shutil
+    import subprocess
+    from pathlib import Path
+    if shutil.which("g++") is None:
+        pytest.skip("no g++")
+    root = Path(__file__).resolve().parent.parent
+    lib = root / "reflex-infer_b200" / "lib"
+    src = tmp_path / "t.cpp"
+    src.write_text(
+        '#include "reflex_b200.hpp"\n'
+        "int main() {\n"
+        "    namespace rb = reflex::b200;\n"
+        "    rb::PagedAttentionDecodeArgs a;\n"
+        "    a.batch = 1; a.n_heads = 3; a.n_kv_heads = 2; a.head_dim = 64; a.num_blocks = 1; a.block_size = 16;\n"
+        "    if (rb::paged_decode_workspace_bytes(a) != 0) return 2;   // 3 heads over 2 kv heads: rejected\n"
+        "    if (rb::paged_flash_attention_decode(a) != rb::Status::InvalidArgument) return 3;\n"
+        "    return rb::kernel_support().paged_decode_attention ? 0 : 1;\n"
+        "}\n")
+    exe = tmp_path / "t"
+    subprocess.check_call(["g++", "-std=c++17", f"-I{root / 'include'}", str(src), f"-L{lib}", "-lreflex_b200",
+                           f"-Wl,-rpath,{lib}", "-o", str(exe)])
+    assert subprocess.call([str(exe)]) == 0
