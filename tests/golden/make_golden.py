@@ -3,7 +3,7 @@ path (``backend="torch"``, CPU tensors) on small deterministic inputs.
 
 Run where the reference checkout is available:
 
-    python tests/golden/make_golden.py [/path/to/reference]   (default /root/reference)
+    python tests/golden/make_golden.py /path/to/reference
 
 It imports ``kernels`` from the reference tree only (this repository's package of the same
 name is not on ``sys.path`` in this process). Inputs come from ``golden_io.pattern`` (pure
@@ -17,7 +17,9 @@ from __future__ import annotations
 import sys
 from pathlib import Path
 
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    raise SystemExit("usage: make_golden.py /path/to/reference")
+REF = Path(sys.argv[1])
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(REF))
 sys.path.insert(1, str(HERE.parent))
