@@ -61,7 +61,7 @@ def parse_args():
                     help="--shard head: assemble the heads inside the combine kernel (peer stores) or with an "
                          "NCCL all-gather")
     ap.add_argument("--shard", default="replica", choices=["replica", "request", "head"])
-    ap.add_argument("--only", default=None, choices=["cfg3", "cfg5"],
+    ap.add_argument("--only", default=None, choices=["cfg3", "cfg5", "linear_norm"],
                     help="run just that secondary block on one GPU and print it (small profiling cases: "
                          "--only cfg3 --requests 2)")
     ap.add_argument("--cpu-sample", type=int, default=0, help="requests in the CPU-baseline sample (0 = auto)")
@@ -554,6 +554,43 @@ def measure_mixed(args, device):
             "l2": "inputs larger than L2", "status": attn.workspace.status()}
 
 
+def measure_linear_norm(args, device):
+    """Fused linear + norm on the shapes of the reference's own benchmark
+    (benchmark/bench_fused_linear_norm.py:24-29): one call = GEMM with the row statistics in its
+    epilogue + the norm over the output. FLOPs counted as the reference does (2*M*K*N)."""
+    from kernels.fused_linear_norm import LinearNormWorkspace, fused_linear_layernorm, fused_linear_rmsnorm
+    peak = 1590.0
+    try:
+        peak = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text()).get("bf16_tflops", peak))
+    except Exception:
+        pass
+    shapes = [("llama8b_mlp_in", 1024, 4096, 14336, "rms", torch.bfloat16),
+              ("llama8b_attn_out", 1024, 4096, 4096, "rms", torch.bfloat16),
+              ("gpt2_mlp_in", 4096, 768, 3072, "layer", torch.float16),
+              ("decode_small", 1, 4096, 4096, "rms", torch.bfloat16)]
+    out = {}
+    g = torch.Generator(device=device).manual_seed(9)
+    for name, M, K, N, norm, dt in shapes:
+        x = torch.randn(M, K, device=device, generator=g).to(dt)
+        w = (torch.randn(N, K, device=device, generator=g) * K ** -0.5).to(dt)
+        bias = torch.randn(N, device=device, generator=g).to(dt)
+        gamma = torch.randn(N, device=device, generator=g).to(dt)
+        beta = torch.randn(N, device=device, generator=g).to(dt) if norm == "layer" else None
+        ws = LinearNormWorkspace(device)
+        if norm == "rms":
+            fn = lambda: fused_linear_rmsnorm(x, w, bias=bias, gamma=gamma, workspace=ws)  # noqa: E731
+        else:
+            fn = lambda: fused_linear_layernorm(x, w, bias=bias, gamma=gamma, beta=beta, workspace=ws)  # noqa: E731
+        total_ms, _ = timed_steps(fn, args.steps, args.warmup, None, None)
+        ms = total_ms / args.steps
+        flops = 2.0 * M * K * N
+        moved = (M * K + N * K + M * N) * x.element_size()
+        out[name] = {"M": M, "K": K, "N": N, "norm": norm, "dtype": str(dt).replace("torch.", ""), "ms": ms,
+                     "tflops": flops / (ms * 1e-3) / 1e12, "frac_of_bf16_peak": flops / (ms * 1e-3) / 1e12 / peak,
+                     "gbs_min_traffic": moved / (ms * 1e-3) / 1e9, "status": ws.status()}
+    return out
+
+
 def check_against_oracle(res, n_req=2):
     """Cheap sanity outside every timed region: first requests of the batch vs the CPU oracle."""
     import oracle
@@ -678,6 +715,8 @@ def run_ours(args):
         line["other_workloads"]["cfg3"] = measure_prefill(args, device)
         torch.cuda.empty_cache()
         line["other_workloads"]["cfg5"] = measure_mixed(args, device)
+        torch.cuda.empty_cache()
+        line["other_workloads"]["fused_linear_norm"] = measure_linear_norm(args, device)
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -689,7 +728,7 @@ def run_only(args):
     assert torch.cuda.is_available(), "bench.py needs a GPU"
     device = torch.device("cuda", 0)
     torch.cuda.set_device(0)
-    block = measure_prefill(args, device) if args.only == "cfg3" else measure_mixed(args, device)
+    block = {"cfg3": measure_prefill, "cfg5": measure_mixed, "linear_norm": measure_linear_norm}[args.only](args, device)
     print(json.dumps({"only": args.only, "steps": args.steps, "warmup": args.warmup, **block}), flush=True)
 
 

@@ -53,7 +53,7 @@ int rfx_abi_version(void);
 /* sizeof() of the args struct with the given index (0 RfxKvAppendArgs, 1 RfxKvLookupArgs,
  * 2 RfxRopeArgs, 3 RfxRopeTableArgs, 4 RfxRopeAppendArgs, 5 RfxSoftmaxArgs,
  * 6 RfxAttentionArgs, 7 RfxPagedAttentionArgs, 8 RfxCombineArgs, 9 RfxHeadGatherArgs,
- * 10 RfxPeerHandle; 0 for anything else), so
+ * 10 RfxPeerHandle, 11 RfxLinearNormArgs; 0 for anything else), so
  * a foreign-function binding can verify its struct mirrors before the first call. */
 size_t rfx_args_size(int which);
 const char* rfx_status_string(int status);
@@ -347,6 +347,39 @@ int rfx_peer_export(const void* device_ptr, RfxPeerHandle* out);
  * rfx_peer_close takes. Must be called by a process other than the exporter. */
 int rfx_peer_open(const RfxPeerHandle* h, void** mapped, void** mapped_base);
 int rfx_peer_close(void* mapped_base);
+
+/* ---- fused linear + norm (kernels/fused_linear_norm/__init__.py:27-73;
+ * torch_reference_fused_linear_norm, kernels/fused_linear_norm/triton_kernel.py:204-233) ------
+ *   y   = x @ weight^T + bias                       rounded to `dtype` (F.linear)
+ *   out = layer_norm(y) * gamma + beta              (norm_type 0; one rounding at the end)
+ *   out = round(y * rsqrt(mean(y^2) + eps)) * gamma (norm_type 1, RMSNorm; the product with gamma
+ *                                                    is a second rounding in `dtype`, as in the reference)
+ * x [M, K], weight [N, K], bias/gamma/beta [N] or NULL, out [M, N], all row-major and contiguous.
+ * 16-bit dtypes with K % 8 == 0 and N % 8 == 0 run a tcgen05 GEMM (128x256 tiles, TMA-fed, fp32
+ * accumulators in tensor memory) whose epilogue also leaves the row sums for the norm; the norm
+ * is applied by a second, bandwidth-bound kernel over `out` in place. Other cases (fp32, odd
+ * sizes) run a plain shared-memory GEMM. The workspace holds the row statistics:
+ * rfx_fused_linear_norm_workspace_bytes(args) bytes, 256-byte aligned. */
+typedef struct {
+    const void* x;
+    const void* weight;
+    const void* bias;            /* optional */
+    const void* gamma;           /* optional */
+    const void* beta;            /* optional, layer norm only */
+    void* out;
+    int64_t M, K, N;
+    float eps;
+    int norm_type;               /* 0 = LayerNorm, 1 = RMSNorm */
+    int dtype;
+    int force_generic;           /* 1 = the plain GEMM even where the tcgen05 one applies (testing) */
+    void* workspace;
+    size_t workspace_bytes;
+    rfx_stream stream;
+} RfxLinearNormArgs;
+size_t rfx_fused_linear_norm_workspace_bytes(const RfxLinearNormArgs* a);
+int rfx_fused_linear_norm(const RfxLinearNormArgs* a);
+/* 1 = tcgen05 GEMM, 0 = plain GEMM, negative = invalid arguments. */
+int rfx_fused_linear_norm_kernel_kind(const RfxLinearNormArgs* a);
 
 #ifdef __cplusplus
 }

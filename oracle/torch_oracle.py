@@ -14,7 +14,7 @@ import torch.nn.functional as F
 __all__ = [
     "kv_paged_append", "kv_paged_scatter", "kv_paged_lookup", "kv_paged_lookup_as_written",
     "build_rope_tables", "apply_rope", "online_softmax", "attention", "naive_attention_f64",
-    "paged_attention_composed", "bottom_right_mask", "merge_partials",
+    "paged_attention_composed", "bottom_right_mask", "merge_partials", "fused_linear_norm",
 ]
 
 
@@ -222,3 +222,19 @@ def merge_partials(m: torch.Tensor, l: torch.Tensor, acc: torch.Tensor) -> torch
         A = A * a + acc[s].double() * bta
         M = Mn
     return (A / L) if L > 0 else A
+
+
+def fused_linear_norm(x, weight, *, bias=None, gamma=None, beta=None, eps: float = 1e-5, norm_type: str = "layer"):
+    """torch_reference_fused_linear_norm, kernels/fused_linear_norm/triton_kernel.py:204-233:
+    ``F.linear`` in the activation dtype, then ``F.layer_norm`` (``:221-227``) or RMSNorm spelled
+    out (``:229-233``: statistics and scaling in fp32, one rounding, then ``* gamma`` in the
+    activation dtype)."""
+    y = F.linear(x, weight, bias)
+    n = weight.shape[0]
+    if norm_type.lower() == "layer":
+        return F.layer_norm(y, (n,), weight=gamma, bias=beta, eps=eps)
+    rms = y.float().pow(2).mean(dim=-1, keepdim=True).add(eps).rsqrt()
+    out = (y.float() * rms).to(y.dtype)
+    if gamma is not None:
+        out = out * gamma
+    return out

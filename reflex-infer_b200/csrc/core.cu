@@ -94,6 +94,7 @@ size_t rfx_args_size(int which) {
         case 8: return sizeof(RfxCombineArgs);
         case 9: return sizeof(RfxHeadGatherArgs);
         case 10: return sizeof(RfxPeerHandle);
+        case 11: return sizeof(RfxLinearNormArgs);
         default: return 0;
     }
 }

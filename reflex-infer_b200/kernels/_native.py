@@ -126,6 +126,15 @@ class CombineArgs(C.Structure):
     ]
 
 
+class LinearNormArgs(C.Structure):
+    _fields_ = [
+        ("x", vp), ("weight", vp), ("bias", vp), ("gamma", vp), ("beta", vp), ("out", vp),
+        ("M", i64), ("K", i64), ("N", i64),
+        ("eps", C.c_float), ("norm_type", C.c_int), ("dtype", C.c_int), ("force_generic", C.c_int),
+        ("workspace", vp), ("workspace_bytes", C.c_size_t), ("stream", vp),
+    ]
+
+
 RFX_MAX_PEERS = 16
 
 
@@ -171,12 +180,15 @@ EXPORTS = {
     "rfx_peer_export": (C.c_int, [vp, C.POINTER(PeerHandle)]),
     "rfx_peer_open": (C.c_int, [C.POINTER(PeerHandle), C.POINTER(vp), C.POINTER(vp)]),
     "rfx_peer_close": (C.c_int, [vp]),
+    "rfx_fused_linear_norm_workspace_bytes": (C.c_size_t, [C.POINTER(LinearNormArgs)]),
+    "rfx_fused_linear_norm": (C.c_int, [C.POINTER(LinearNormArgs)]),
+    "rfx_fused_linear_norm_kernel_kind": (C.c_int, [C.POINTER(LinearNormArgs)]),
 }
 
 
 # Index of each mirror in rfx_args_size().
 ARG_STRUCTS = [KvAppendArgs, KvLookupArgs, RopeArgs, RopeTableArgs, RopeAppendArgs, SoftmaxArgs,
-               AttentionArgs, PagedAttentionArgs, CombineArgs, HeadGatherArgs, PeerHandle]
+               AttentionArgs, PagedAttentionArgs, CombineArgs, HeadGatherArgs, PeerHandle, LinearNormArgs]
 
 
 def library_path() -> Path:

@@ -30,6 +30,7 @@ from kernels.attention import fused_attention  # noqa: E402  (reference)
 from kernels.kv_cache import kv_paged_append, kv_paged_lookup, kv_paged_scatter  # noqa: E402
 from kernels.rope import apply_rope, build_rope_tables  # noqa: E402
 from kernels.softmax import online_softmax  # noqa: E402
+from kernels.fused_linear_norm import fused_linear_layernorm, fused_linear_rmsnorm  # noqa: E402
 
 import golden_cases as gc  # noqa: E402
 import golden_io  # noqa: E402
@@ -98,6 +99,13 @@ def main():
             out[b] = ob.view(Hq, D)
         golden_io.save(name, dict(out=out, q_rot=q_rot, k_rot=k_rot),
                        {**META, "k_digest": golden_io.digest(kc), "v_digest": golden_io.digest(vc)}); n += 1
+    for name, c in gc.linear_norm_cases().items():
+        if c["norm"] == "rms":
+            y = fused_linear_rmsnorm(c["x"], c["weight"], bias=c["bias"], gamma=c["gamma"], eps=c["eps"], backend=BK)
+        else:
+            y = fused_linear_layernorm(c["x"], c["weight"], bias=c["bias"], gamma=c["gamma"], beta=c["beta"],
+                                       eps=c["eps"], backend=BK)
+        golden_io.save(name, dict(y=y), META); n += 1
     total = sum(p.stat().st_size for p in HERE.glob("*.npz"))
     print(f"wrote {n} fixtures, {total / 1e6:.2f} MB, torch {torch.__version__}")
 

@@ -147,3 +147,27 @@ def step_cases() -> dict:
         # configuration-5-like head ratio (28/4: group of 7), pages of 16
         "step_cfg5_small_bf16": _step(630, Hq=28, Hkv=4, D=128, bs=16, lens=[5, 100, 48], theta=1e6, dt=BF16),
     }
+
+
+def linear_norm_cases() -> dict:
+    """Small shapes of the reference's fused linear + norm (tests/test_fused_linear_norm.py and the
+    bench shapes of benchmark/bench_fused_linear_norm.py:24-29 scaled down): both norms, the three
+    dtypes, optional bias / gamma / beta, row counts off the 128-row tile and widths off the
+    256-column tile."""
+    cases = {}
+    spec = [("rms_bf16", BF16, 200, 256, 512, "rms", True, True),
+            ("rms_bf16_nobias", BF16, 64, 128, 264, "rms", False, True),
+            ("rms_f16_nogamma", F16, 130, 192, 256, "rms", True, False),
+            ("layer_f16", F16, 96, 256, 768, "layer", True, True),
+            ("layer_bf16_plain", BF16, 33, 64, 128, "layer", False, False),
+            ("rms_f32", F32, 40, 72, 100, "rms", True, True),
+            ("layer_f32", F32, 17, 50, 96, "layer", True, True),
+            ("rms_bf16_odd", BF16, 10, 60, 70, "rms", True, True)]
+    for i, (name, dt, M, K, N, norm, has_bias, has_gamma) in enumerate(spec):
+        c = dict(x=pattern((M, K), dt, 700 + 10 * i), weight=pattern((N, K), dt, 701 + 10 * i, scale=0.25),
+                 bias=pattern((N,), dt, 702 + 10 * i) if has_bias else None,
+                 gamma=(pattern((N,), dt, 703 + 10 * i) + 1.0).to(dt) if has_gamma else None,
+                 beta=pattern((N,), dt, 704 + 10 * i) if (norm == "layer" and has_gamma) else None,
+                 norm=norm, eps=1e-5)
+        cases[f"linear_norm_{name}"] = c
+    return cases

@@ -269,3 +269,28 @@ def test_decode_step_is_cuda_graph_capturable(native):
     torch.cuda.synchronize()
     assert torch.equal(replayed, att.out) and not torch.equal(replayed, eager)
     _clean(ws)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("force_generic", [False, True])
+def test_fused_decode_step_rope_variants(dtype, interleaved, force_generic, native):
+    """The fused step (RoPE + append, RoPE in the Q load) in both RoPE layouts and both 16-bit
+    types, on the TMA/MMA kernel and on the scalar one: pool bit-exact against the reference's
+    op-by-op rounding, outputs within the type's tolerance."""
+    cos, sin = oracle.build_rope_tables(700, 128, base=1e6, dtype=dtype, interleaved=interleaved)
+    cpu = workloads.make_paged_batch("variants", B=5, Hq=16, Hkv=4, D=128, block_size=16, ctx_range=(1, 600),
+                                     num_blocks=256, dtype=dtype, seed=41, tables=(cos, sin))
+    g = cpu.to(DEV)
+    ws = PagedWorkspace(DEV)
+    out = paged_decode_step(g.q_new, g.k_new, g.v_new, g.k_cache, g.v_cache, g.block_table, g.context_lens,
+                            g.slot_mapping, g.positions, g.cos, g.sin, interleaved=interleaved, workspace=ws,
+                            force_generic=force_generic)
+    assert ws.status() == 0
+    pos = cpu.positions.long()
+    q_rot = oracle.apply_rope(cpu.q_new.unsqueeze(0), cos[pos], sin[pos], interleaved=interleaved)[0]
+    k_rot = oracle.apply_rope(cpu.k_new.unsqueeze(0), cos[pos], sin[pos], interleaved=interleaved)[0]
+    oracle.kv_paged_append(k_rot, cpu.v_new, cpu.k_cache, cpu.v_cache, cpu.slot_mapping)
+    assert torch.equal(g.k_cache.cpu(), cpu.k_cache) and torch.equal(g.v_cache.cpu(), cpu.v_cache)
+    ref = oracle.paged_attention_composed(q_rot, cpu.k_cache, cpu.v_cache, cpu.block_table, cpu.context_lens)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=TOL[dtype], rtol=TOL[dtype])

@@ -162,3 +162,13 @@ def test_merge_partials_equals_unsplit():
         ms.append(m); ls.append(p.sum()); accs.append((p[:, None] * v[lo:hi]).sum(0))
     out = oracle.merge_partials(torch.stack(ms), torch.stack(ls), torch.stack(accs))
     torch.testing.assert_close(out, full, atol=1e-6, rtol=1e-6)
+
+
+@pytest.mark.parametrize("name", sorted(gc.linear_norm_cases()))
+def test_fused_linear_norm(name):
+    c = gc.linear_norm_cases()[name]
+    want, _ = golden_io.load(name)
+    got = oracle.fused_linear_norm(c["x"], c["weight"], bias=c["bias"], gamma=c["gamma"], beta=c["beta"], eps=c["eps"],
+                                   norm_type=c["norm"])
+    tol = {torch.float32: 1e-5, torch.bfloat16: 2e-2, torch.float16: 5e-3}[c["x"].dtype]
+    torch.testing.assert_close(got.float(), want["y"].float(), atol=tol, rtol=tol)
