@@ -357,8 +357,9 @@ int rfx_peer_close(void* mapped_base);
  * x [M, K], weight [N, K], bias/gamma/beta [N] or NULL, out [M, N], all row-major and contiguous.
  * 16-bit dtypes with K % 8 == 0 and N % 8 == 0 run a tcgen05 GEMM (128x256 tiles, TMA-fed, fp32
  * accumulators in tensor memory) whose epilogue also leaves the row sums for the norm; the norm
- * is applied by a second, bandwidth-bound kernel over `out` in place. Other cases (fp32, odd
- * sizes) run a plain shared-memory GEMM. The workspace holds the row statistics:
+ * is applied by a second, bandwidth-bound kernel over `out` in place. Up to 8 rows (decode) stream
+ * the weights once with one warp per output column. Other cases (fp32, odd sizes) run a plain
+ * shared-memory GEMM. The workspace holds the row statistics:
  * rfx_fused_linear_norm_workspace_bytes(args) bytes, 256-byte aligned. */
 typedef struct {
     const void* x;
@@ -378,7 +379,8 @@ typedef struct {
 } RfxLinearNormArgs;
 size_t rfx_fused_linear_norm_workspace_bytes(const RfxLinearNormArgs* a);
 int rfx_fused_linear_norm(const RfxLinearNormArgs* a);
-/* 1 = tcgen05 GEMM, 0 = plain GEMM, negative = invalid arguments. */
+/* 1 = tcgen05 GEMM, 2 = weight-streaming kernel for up to 8 rows (16-bit), 0 = plain GEMM,
+ * negative = invalid arguments. */
 int rfx_fused_linear_norm_kernel_kind(const RfxLinearNormArgs* a);
 
 #ifdef __cplusplus

@@ -23,12 +23,15 @@ constexpr int kLnTileM = 128, kLnTileN = 256, kLnTileK = 64, kLnStages = 4;
 constexpr int kLnABytes = kLnTileM * kLnTileK * 2;  // 16 KiB
 constexpr int kLnBBytes = kLnTileN * kLnTileK * 2;  // 32 KiB
 constexpr int kLnThreads = 192;                     // producer, issuer, four epilogue warps
+// Row statistics are spread over 16 slots per row (producer CTA index mod 16), so that the
+// atomics of the many CTAs of a narrow-M problem do not all hit one address.
+constexpr int kLnStatSlots = 16;
 constexpr size_t kLnSmem = (size_t)kLnStages * (kLnABytes + kLnBBytes) + 256 + 1024;
 
 struct LnGemmParams {
     const void* bias;
     void* out;
-    float* stats;      // [M][2]: sum, sum of squares of the rounded y
+    float* stats;      // [M][16 slots][2]: sum, sum of squares of the rounded y
     int32_t* status;   // bit 0: a bounded wait expired
     int M, N, K;
 };
@@ -145,8 +148,9 @@ linear_stats_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
                 }
             }
             if (live) {
-                atomicAdd(&P.stats[2 * (int64_t)row], sum);
-                atomicAdd(&P.stats[2 * (int64_t)row + 1], sumsq);
+                float* st = P.stats + ((int64_t)row * kLnStatSlots + (blockIdx.x % kLnStatSlots)) * 2;
+                atomicAdd(st, sum);
+                atomicAdd(st + 1, sumsq);
             }
         }
     }
@@ -186,8 +190,76 @@ linear_stats_generic_kernel(const T* __restrict__ x, const T* __restrict__ w, co
     }
     const float s = warp_sum(v), q = warp_sum(v * v);
     if (tx == 0 && row < M) {
-        atomicAdd(&stats[2 * (int64_t)row], s);
-        atomicAdd(&stats[2 * (int64_t)row + 1], q);
+        float* st = stats + ((int64_t)row * kLnStatSlots + (blockIdx.x % kLnStatSlots)) * 2;
+        atomicAdd(st, s);
+        atomicAdd(st + 1, q);
+    }
+}
+
+// Up to eight rows of x (decode): the weight matrix is streamed once at HBM speed, one warp per
+// output column, 16-byte loads along K, fp32 accumulate. 2*N*K*e bytes of weights dominate.
+constexpr int kLnSmallM = 8;
+template <typename T>
+__global__ void __launch_bounds__(256, 4)
+linear_stats_small_m_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ bias,
+                            T* __restrict__ out, float* __restrict__ stats, int M, int N, int K) {
+    constexpr int V = 16 / sizeof(T);
+    struct alignas(16) Vec { T v[V]; };
+    __shared__ float part[8][kLnSmallM];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + warp;
+    float acc[kLnSmallM];
+#pragma unroll
+    for (int m = 0; m < kLnSmallM; ++m) acc[m] = 0.f;
+    if (n < N) {
+        const Vec* wr = reinterpret_cast<const Vec*>(w + (int64_t)n * K);
+        const int nv = K / V;
+        // four 16-byte weight loads in flight per lane (2 KB of the row per warp), then the math;
+        // registers are kept to 64 so that four CTAs fit an SM
+        for (int kv0 = 0; kv0 < nv; kv0 += 4 * 32) {
+            Vec wv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int kv = kv0 + u * 32 + lane;
+                if (kv < nv) wv[u] = wr[kv];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int kv = kv0 + u * 32 + lane;
+                if (kv < nv) {
+#pragma unroll
+                    for (int m = 0; m < kLnSmallM; ++m) {
+                        if (m < M) {
+                            const Vec xv = reinterpret_cast<const Vec*>(x + (int64_t)m * K)[kv];
+#pragma unroll
+                            for (int j = 0; j < V; ++j)
+                                acc[m] = fmaf(Num<T>::to_f(xv.v[j]), Num<T>::to_f(wv[u].v[j]), acc[m]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < kLnSmallM; ++m) {
+        float v = warp_sum(acc[m]);
+        float y = 0.f;
+        if (n < N && m < M) {
+            if (bias) v += Num<T>::to_f(bias[n]);
+            const T r = Num<T>::from_f(v);
+            if (lane == 0) out[(int64_t)m * N + n] = r;
+            y = Num<T>::to_f(r);
+        }
+        if (lane == 0) part[warp][m] = y;
+    }
+    __syncthreads();
+    if (threadIdx.x < M) {
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < 8; ++wv) { const float y = part[wv][threadIdx.x]; s1 += y; s2 = fmaf(y, y, s2); }
+        float* st = stats + ((int64_t)threadIdx.x * kLnStatSlots + (blockIdx.x % kLnStatSlots)) * 2;
+        atomicAdd(st, s1);
+        atomicAdd(st + 1, s2);
     }
 }
 
@@ -198,10 +270,14 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 norm_rows_kernel(T* __restrict__ out, const float* __restrict__ stats, const T* __restrict__ gamma,
                  const T* __restrict__ beta, int64_t M, int N, float eps, int rms) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int V = 16 / sizeof(T);
-    for (int64_t row = (int64_t)blockIdx.x * 8 + warp; row < M; row += (int64_t)gridDim.x * 8) {
-        const float s = stats[2 * row], q = stats[2 * row + 1];
+    for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {  // one CTA per row
+        float s = 0.f, q = 0.f;
+#pragma unroll
+        for (int i = 0; i < kLnStatSlots; ++i) {
+            s += stats[(row * kLnStatSlots + i) * 2];
+            q += stats[(row * kLnStatSlots + i) * 2 + 1];
+        }
         const float mean = rms ? 0.f : s / (float)N;
         const float var = rms ? q / (float)N : fmaxf(q / (float)N - mean * mean, 0.f);
         const float rstd = rsqrtf(var + eps);
@@ -220,14 +296,14 @@ norm_rows_kernel(T* __restrict__ out, const float* __restrict__ stats, const T* 
         if (N % V == 0 && ((uintptr_t)r % 16) == 0) {
             struct alignas(16) Vec { T v[V]; };
             Vec* rv = reinterpret_cast<Vec*>(r);
-            for (int i = lane; i < N / V; i += 32) {
+            for (int i = threadIdx.x; i < N / V; i += blockDim.x) {
                 Vec p = rv[i];
 #pragma unroll
                 for (int j = 0; j < V; ++j) p.v[j] = one(p.v[j], i * V + j);
                 rv[i] = p;
             }
         } else {
-            for (int c = lane; c < N; c += 32) r[c] = one(r[c], c);
+            for (int c = threadIdx.x; c < N; c += blockDim.x) r[c] = one(r[c], c);
         }
     }
 }
@@ -265,7 +341,15 @@ static bool ln_tensor_ok(const RfxLinearNormArgs* a) {
     return true;
 }
 
-static size_t ln_ws_bytes(const RfxLinearNormArgs* a) { return round_up<size_t>((size_t)a->M * 8 + 256, 256); }
+static bool ln_small_m_ok(const RfxLinearNormArgs* a) {
+    if (a->force_generic || a->dtype == RFX_F32 || a->M > kLnSmallM) return false;
+    if (a->K % 8 || ((uintptr_t)a->x % 16) || ((uintptr_t)a->weight % 16)) return false;
+    return true;
+}
+
+static size_t ln_ws_bytes(const RfxLinearNormArgs* a) {
+    return round_up<size_t>((size_t)a->M * kLnStatSlots * 8 + 256, 256);
+}
 
 }  // namespace rfx
 
@@ -276,6 +360,7 @@ extern "C" size_t rfx_fused_linear_norm_workspace_bytes(const RfxLinearNormArgs*
 
 extern "C" int rfx_fused_linear_norm_kernel_kind(const RfxLinearNormArgs* a) {
     if (rfx::validate_ln(a, "rfx_fused_linear_norm_kernel_kind") != RFX_SUCCESS) return -1;
+    if (rfx::ln_small_m_ok(a)) return 2;
     return rfx::ln_tensor_ok(a) ? 1 : 0;
 }
 
@@ -300,7 +385,16 @@ extern "C" int rfx_fused_linear_norm(const RfxLinearNormArgs* a) {
 
     const int M = (int)a->M, N = (int)a->N, K = (int)a->K;
     bool done = false;
-    if (ln_tensor_ok(a)) {
+    if (ln_small_m_ok(a)) {
+        RFX_DISPATCH_DTYPE(a->dtype, T, {
+            linear_stats_small_m_kernel<T><<<(unsigned)ceil_div(N, 8), 256, 0, s>>>(
+                (const T*)a->x, (const T*)a->weight, (const T*)a->bias, (T*)a->out, stats, M, N, K);
+        });
+        st = check_launch(name);
+        if (st != RFX_SUCCESS) return st;
+        done = true;
+    }
+    if (!done && ln_tensor_ok(a)) {
         CUtensorMap xm, wm;
         const uint64_t xd[2] = {(uint64_t)K, (uint64_t)M}, wd[2] = {(uint64_t)K, (uint64_t)N};
         const uint64_t str[1] = {(uint64_t)K * 2};
@@ -325,8 +419,8 @@ extern "C" int rfx_fused_linear_norm(const RfxLinearNormArgs* a) {
         st = check_launch(name);
         if (st != RFX_SUCCESS) return st;
     }
-    int64_t blocks = ceil_div<int64_t>(a->M, 8);
-    const int64_t cap = (int64_t)sm_count() * 8;
+    int64_t blocks = a->M;
+    const int64_t cap = (int64_t)sm_count() * 16;
     if (blocks > cap) blocks = cap;
     RFX_DISPATCH_DTYPE(a->dtype, T, {
         norm_rows_kernel<T><<<(int)blocks, 256, 0, s>>>((T*)a->out, stats, (const T*)a->gamma, (const T*)a->beta, a->M, N,

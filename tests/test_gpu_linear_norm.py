@@ -36,16 +36,18 @@ def test_golden(name, force_generic, native):
 def test_tensor_core_gemm_is_selected(native):
     import ctypes as C
     from kernels import _native as N
-    def kind(dtype, K, Nn):
-        a = N.LinearNormArgs(x=256, weight=256, out=256, M=4, K=K, N=Nn, eps=1e-5, norm_type=1, dtype=N._DTYPE_CODE[dtype])
+    def kind(dtype, K, Nn, M=4):
+        a = N.LinearNormArgs(x=256, weight=256, out=256, M=M, K=K, N=Nn, eps=1e-5, norm_type=1, dtype=N._DTYPE_CODE[dtype])
         return N.lib().rfx_fused_linear_norm_kernel_kind(C.byref(a))
-    assert kind(torch.bfloat16, 4096, 4096) == 1
-    assert kind(torch.float16, 768, 3072) == 1
+    assert kind(torch.bfloat16, 4096, 4096) == 2      # 4 rows: the weight-streaming kernel
+    assert kind(torch.bfloat16, 4096, 4096, M=512) == 1
+    assert kind(torch.float16, 768, 3072, M=100) == 1
     assert kind(torch.float32, 4096, 4096) == 0
     assert kind(torch.bfloat16, 60, 70) == 0
 
 
-@pytest.mark.parametrize("M,K,N,norm", [(1, 4096, 4096, "rms"), (300, 1024, 1792, "rms"), (257, 768, 3072, "layer")])
+@pytest.mark.parametrize("M,K,N,norm", [(1, 4096, 4096, "rms"), (7, 512, 1000, "layer"), (300, 1024, 1792, "rms"),
+                                        (257, 768, 3072, "layer")])
 def test_larger_shapes_vs_oracle(M, K, N, norm, native):
     """Row counts off the tile, many K steps (the ring wraps), several N tiles per row (the row
     statistics come from more than one CTA), a 3-D input."""
