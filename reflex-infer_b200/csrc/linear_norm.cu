@@ -5,10 +5,10 @@
 //   1. y = x @ W^T + bias, rounded to the activation dtype, written to `out`; the epilogue also
 //      adds each row's sum and sum of squares of the ROUNDED values to the workspace (the norm
 //      of the reference sees the rounded y). 16-bit inputs run on the tensor cores:
-//      one CTA per 128x256 output tile, a TMA producer warp filling a four-stage ring of
+//      persistent CTAs over 128x256 output tiles, a TMA producer warp filling a four-stage ring of
 //      [128x64] x-tiles and [256x64] W-tiles (128-byte swizzle, both K-major), one thread issuing
-//      tcgen05.mma 128x256x16 into 256 columns of tensor memory, four epilogue warps reading
-//      the accumulator rows with tcgen05.ld. Tensor-pipe bound: 2*M*N*K FLOPs.
+//      tcgen05.mma 128x256x16 into one of two 256-column accumulators in tensor memory, four
+//      epilogue warps reading the other one's rows with tcgen05.ld under the next tile's main loop. Tensor-pipe bound: 2*M*N*K FLOPs.
 //      fp32 and sizes the tensor maps cannot express take a plain shared-memory GEMM.
 //   2. the norm over `out` in place, one warp per row: bandwidth-bound, 2*M*N*e bytes (the rows
 //      are still in L2 for the reference's sizes).
@@ -26,7 +26,7 @@ constexpr int kLnThreads = 192;                     // producer, issuer, four ep
 // Row statistics are spread over 16 slots per row (producer CTA index mod 16), so that the
 // atomics of the many CTAs of a narrow-M problem do not all hit one address.
 constexpr int kLnStatSlots = 16;
-constexpr size_t kLnSmem = (size_t)kLnStages * (kLnABytes + kLnBBytes) + 256 + 1024;
+constexpr size_t kLnSmem = (size_t)kLnStages * (kLnABytes + kLnBBytes) + 256 + 1024;  // ring, barriers, alignment slack
 
 struct LnGemmParams {
     const void* bias;
@@ -45,21 +45,29 @@ linear_stats_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
     unsigned char* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char* sA = smem;
     unsigned char* sB = smem + (size_t)kLnStages * kLnABytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + (size_t)kLnStages * kLnBBytes);  // full[4], empty[4], acc
-    uint32_t* misc = reinterpret_cast<uint32_t*>(bars + 2 * kLnStages + 1);
+    // barriers: full[4], empty[4] (smem ring), acc_full[2], acc_empty[2] (the two accumulators)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + (size_t)kLnStages * kLnBBytes);
+    uint32_t* misc = reinterpret_cast<uint32_t*>(bars + 2 * kLnStages + 4);
     uint64_t* full = bars;
     uint64_t* empty = bars + kLnStages;
-    uint64_t* acc_done = bars + 2 * kLnStages;
+    uint64_t* acc_full = bars + 2 * kLnStages;
+    uint64_t* acc_empty = acc_full + 2;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kLnTileN, m0 = blockIdx.y * kLnTileM;
     const int nk = (P.K + kLnTileK - 1) / kLnTileK;
+    // Persistent: CTA c takes tiles c, c + gridDim.x, ... (N-tile index fastest, so the CTAs of a
+    // wave share x rows); two accumulators in tensor memory, so the epilogue of one tile runs
+    // under the main loop of the next.
+    const int tiles_n = (P.N + kLnTileN - 1) / kLnTileN;
+    const int n_tiles = tiles_n * ((P.M + kLnTileM - 1) / kLnTileM);
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 2 * kLnStages + 1; ++i) ptx::mbar_init(&bars[i], 1);
+        for (int i = 0; i < 2 * kLnStages + 2; ++i) ptx::mbar_init(&bars[i], 1);
+        ptx::mbar_init(&acc_empty[0], 128);  // the four epilogue warps
+        ptx::mbar_init(&acc_empty[1], 128);
         ptx::fence_barrier_init();
     }
-    if (warp == 1) ptx::tmem_alloc(&misc[0], kLnTileN);
+    if (warp == 1) ptx::tmem_alloc(&misc[0], 2 * kLnTileN);
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
@@ -70,85 +78,109 @@ linear_stats_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
         if (lane == 0) {
             ptx::prefetch_tensormap(&xmap);
             ptx::prefetch_tensormap(&wmap);
-            for (int ks = 0; ks < nk; ++ks) {
-                const int st = ks % kLnStages;
-                if (!ptx::mbar_wait_bounded(&empty[st], (uint32_t)(((ks / kLnStages) & 1) ^ 1))) {
-                    atomicOr(P.status, 1);
-                    break;
+            int g = 0;  // K steps so far: step g uses stage g % 4, use g / 4 of that stage
+            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                const int n0 = (tile % tiles_n) * kLnTileN, m0 = (tile / tiles_n) * kLnTileM;
+                for (int ks = 0; ks < nk; ++ks, ++g) {
+                    const int st = g % kLnStages;
+                    if (!ptx::mbar_wait_bounded(&empty[st], (uint32_t)(((g / kLnStages) & 1) ^ 1))) {
+                        atomicOr(P.status, 1);
+                        tile = n_tiles;
+                        break;
+                    }
+                    ptx::mbar_arrive_expect_tx(&full[st], (uint32_t)(kLnABytes + kLnBBytes));
+                    ptx::tma_load_2d(sA + (size_t)st * kLnABytes, &xmap, &full[st], ks * kLnTileK, m0);
+                    ptx::tma_load_2d(sB + (size_t)st * kLnBBytes, &wmap, &full[st], ks * kLnTileK, n0);
                 }
-                ptx::mbar_arrive_expect_tx(&full[st], (uint32_t)(kLnABytes + kLnBBytes));
-                ptx::tma_load_2d(sA + (size_t)st * kLnABytes, &xmap, &full[st], ks * kLnTileK, m0);
-                ptx::tma_load_2d(sB + (size_t)st * kLnBBytes, &wmap, &full[st], ks * kLnTileK, n0);
             }
         }
     } else if (warp == 1) {
         // ---- MMA issuer
         constexpr uint32_t idesc = ptx::umma_idesc_f16(kLnTileM, kLnTileN, BF ? 1 : 0, 0, 0);  // x, W both K-major
         if (lane == 0) {
+            int g = 0, t = 0;  // t: tiles so far; tile t accumulates into buffer t & 1, use t / 2 of it
             bool ok = true;
-            for (int ks = 0; ks < nk && ok; ++ks) {
-                const int st = ks % kLnStages;
-                ok = ptx::mbar_wait_bounded(&full[st], (uint32_t)((ks / kLnStages) & 1));
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
+                const int buf = t & 1;
+                // the epilogue has drained this buffer's previous tile
+                ok = ptx::mbar_wait_bounded(&acc_empty[buf], (uint32_t)(((t >> 1) & 1) ^ 1));
                 if (!ok) { atomicOr(P.status, 1); break; }
                 ptx::tc_fence_after_sync();
-                const uint32_t a_addr = ptx::smem_u32(sA + (size_t)st * kLnABytes);
-                const uint32_t b_addr = ptx::smem_u32(sB + (size_t)st * kLnBBytes);
+                for (int ks = 0; ks < nk; ++ks, ++g) {
+                    const int st = g % kLnStages;
+                    ok = ptx::mbar_wait_bounded(&full[st], (uint32_t)((g / kLnStages) & 1));
+                    if (!ok) { atomicOr(P.status, 1); break; }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_addr = ptx::smem_u32(sA + (size_t)st * kLnABytes);
+                    const uint32_t b_addr = ptx::smem_u32(sB + (size_t)st * kLnBBytes);
 #pragma unroll
-                for (int k = 0; k < kLnTileK / 16; ++k)
-                    ptx::umma_ss(tmem, ptx::umma_desc_sw128(a_addr + k * 32, 16, 1024),
-                                 ptx::umma_desc_sw128(b_addr + k * 32, 16, 1024), idesc, (ks > 0 || k > 0) ? 1u : 0u);
-                ptx::umma_commit(&empty[st]);
+                    for (int k = 0; k < kLnTileK / 16; ++k)
+                        ptx::umma_ss(tmem + buf * kLnTileN, ptx::umma_desc_sw128(a_addr + k * 32, 16, 1024),
+                                     ptx::umma_desc_sw128(b_addr + k * 32, 16, 1024), idesc, (ks > 0 || k > 0) ? 1u : 0u);
+                    ptx::umma_commit(&empty[st]);
+                }
+                ptx::umma_commit(&acc_full[buf]);  // also after a failed wait: the epilogue must not hang
             }
-            ptx::umma_commit(acc_done);  // also reached after a failed wait: the epilogue must not hang
         }
         __syncwarp();
     } else {
         // ---- epilogue: thread = accumulator row (a warp reaches the TMEM lanes of its quadrant)
         const int quad = warp & 3;
-        const int row = m0 + quad * 32 + lane;
-        const bool live = row < P.M;
-        const bool ok = __all_sync(0xffffffffu, ptx::mbar_wait_bounded(acc_done, 0) ? 1 : 0) != 0;
-        ptx::tc_fence_after_sync();
-        if (!ok && lane == 0) atomicOr(P.status, 1);
-        float sum = 0.f, sumsq = 0.f;
         const T* bias = reinterpret_cast<const T*>(P.bias);
-        T* orow = reinterpret_cast<T*>(P.out) + (int64_t)row * P.N;
-        if (ok && nk > 0) {
+        int t = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
+            const int buf = t & 1;
+            const int n0 = (tile % tiles_n) * kLnTileN, m0 = (tile / tiles_n) * kLnTileM;
+            const int row = m0 + quad * 32 + lane;
+            const bool live = row < P.M;
+            const bool ok = __all_sync(0xffffffffu, ptx::mbar_wait_bounded(&acc_full[buf], (uint32_t)((t >> 1) & 1)) ? 1 : 0) != 0;
+            ptx::tc_fence_after_sync();
+            if (!ok) {
+                if (lane == 0) atomicOr(P.status, 1);
+                break;
+            }
+            float sum = 0.f, sumsq = 0.f;
+            T* orow = reinterpret_cast<T*>(P.out) + (int64_t)row * P.N;
+            if (nk > 0) {
 #pragma unroll 1
-            for (int c = 0; c < kLnTileN / 32; ++c) {
-                const int col0 = n0 + c * 32;
-                if (col0 >= P.N) break;  // uniform
-                uint32_t w[32];
-                ptx::tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + c * 32, w);
-                ptx::tmem_wait_ld();
-                uint32_t pk[16];
+                for (int c = 0; c < kLnTileN / 32; ++c) {
+                    const int col0 = n0 + c * 32;
+                    if (col0 >= P.N) break;  // uniform
+                    uint32_t w[32];
+                    ptx::tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + buf * kLnTileN + c * 32, w);
+                    ptx::tmem_wait_ld();
+                    uint32_t pk[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float a = __uint_as_float(w[i]), b2 = __uint_as_float(w[i + 1]);
-                    if (bias) {
-                        if (col0 + i < P.N) a += Num<T>::to_f(bias[col0 + i]);
-                        if (col0 + i + 1 < P.N) b2 += Num<T>::to_f(bias[col0 + i + 1]);
+                    for (int i = 0; i < 32; i += 2) {
+                        float a = __uint_as_float(w[i]), b2 = __uint_as_float(w[i + 1]);
+                        if (bias) {
+                            if (col0 + i < P.N) a += Num<T>::to_f(bias[col0 + i]);
+                            if (col0 + i + 1 < P.N) b2 += Num<T>::to_f(bias[col0 + i + 1]);
+                        }
+                        const T ra = Num<T>::from_f(a), rb = Num<T>::from_f(b2);
+                        const float fa = Num<T>::to_f(ra), fb = Num<T>::to_f(rb);
+                        if (col0 + i < P.N) { sum += fa; sumsq = fmaf(fa, fa, sumsq); }
+                        if (col0 + i + 1 < P.N) { sum += fb; sumsq = fmaf(fb, fb, sumsq); }
+                        pk[i >> 1] = (uint32_t)(*reinterpret_cast<const uint16_t*>(&ra)) |
+                                     ((uint32_t)(*reinterpret_cast<const uint16_t*>(&rb)) << 16);
                     }
-                    const T ra = Num<T>::from_f(a), rb = Num<T>::from_f(b2);
-                    const float fa = Num<T>::to_f(ra), fb = Num<T>::to_f(rb);
-                    if (col0 + i < P.N) { sum += fa; sumsq = fmaf(fa, fa, sumsq); }
-                    if (col0 + i + 1 < P.N) { sum += fb; sumsq = fmaf(fb, fb, sumsq); }
-                    pk[i >> 1] = (uint32_t)(*reinterpret_cast<const uint16_t*>(&ra)) |
-                                 ((uint32_t)(*reinterpret_cast<const uint16_t*>(&rb)) << 16);
-                }
-                if (live) {
-                    if (col0 + 32 <= P.N) {
-                        uint4* dst = reinterpret_cast<uint4*>(orow + col0);  // N % 8 == 0: 16-byte aligned
+                    if (live) {
+                        if (col0 + 32 <= P.N) {
+                            uint4* dst = reinterpret_cast<uint4*>(orow + col0);  // N % 8 == 0: 16-byte aligned
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
-                    } else {
-                        for (int i = 0; i < 32 && col0 + i < P.N; ++i)
-                            reinterpret_cast<uint16_t*>(orow)[col0 + i] = (uint16_t)(pk[i >> 1] >> ((i & 1) * 16));
+                            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                        } else {
+                            for (int i = 0; i < 32 && col0 + i < P.N; ++i)
+                                reinterpret_cast<uint16_t*>(orow)[col0 + i] = (uint16_t)(pk[i >> 1] >> ((i & 1) * 16));
+                        }
                     }
                 }
             }
-            if (live) {
-                float* st = P.stats + ((int64_t)row * kLnStatSlots + (blockIdx.x % kLnStatSlots)) * 2;
+            // the accumulator is in registers / stored: the issuer may reuse the buffer
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(&acc_empty[buf]);
+            if (live && nk > 0) {
+                float* st = P.stats + ((int64_t)row * kLnStatSlots + ((tile % tiles_n) % kLnStatSlots)) * 2;
                 atomicAdd(st, sum);
                 atomicAdd(st + 1, sumsq);
             }
@@ -158,7 +190,7 @@ linear_stats_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
     __syncthreads();
     if (warp == 1) {
         ptx::tc_fence_after_sync();
-        ptx::tmem_dealloc(tmem, kLnTileN);
+        ptx::tmem_dealloc(tmem, 2 * kLnTileN);
     }
 }
 
@@ -403,7 +435,8 @@ extern "C" int rfx_fused_linear_norm(const RfxLinearNormArgs* a) {
             LnGemmParams P;
             P.bias = a->bias; P.out = a->out; P.stats = stats; P.status = status;
             P.M = M; P.N = N; P.K = K;
-            const dim3 grid((unsigned)ceil_div(N, kLnTileN), (unsigned)ceil_div(M, kLnTileM));
+            const int tiles = ceil_div(N, kLnTileN) * ceil_div(M, kLnTileM);
+            const dim3 grid((unsigned)(tiles < sm_count() ? tiles : sm_count()));
             st = a->dtype == RFX_BF16 ? launch_ln_tc<__nv_bfloat16>(xm, wm, P, grid, s)
                                       : launch_ln_tc<__half>(xm, wm, P, grid, s);
             if (st != RFX_SUCCESS) return st;
