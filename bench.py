@@ -61,7 +61,7 @@ def parse_args():
                     help="--shard head: assemble the heads inside the combine kernel (peer stores) or with an "
                          "NCCL all-gather")
     ap.add_argument("--shard", default="replica", choices=["replica", "request", "head"])
-    ap.add_argument("--only", default=None, choices=["cfg3", "cfg5", "linear_norm"],
+    ap.add_argument("--only", default=None, choices=["cfg3", "cfg5", "linear_norm", "small_ops"],
                     help="run just that secondary block on one GPU and print it (small profiling cases: "
                          "--only cfg3 --requests 2)")
     ap.add_argument("--cpu-sample", type=int, default=0, help="requests in the CPU-baseline sample (0 = auto)")
@@ -601,6 +601,61 @@ def measure_linear_norm(args, device):
     return out
 
 
+def measure_small_ops(args, device):
+    """The bandwidth-bound ops of the path on the reference's own benchmark shapes
+    (benchmark/bench_kv_cache.py, bench_rope.py, bench_softmax.py): each call replayed from a CUDA
+    graph (they run for tens of microseconds, less than the Python call path), L2 flushed between
+    replays; bytes as the reference counts them."""
+    from kernels.kv_cache import kv_paged_append, kv_paged_lookup
+    from kernels.rope import apply_rope_, build_rope_tables
+    from kernels.softmax import online_softmax
+    peak, _ = measured_peak()
+    flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=device)
+    bf = torch.bfloat16
+    out = {}
+
+    def timed(fn):
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            fn()
+            torch.cuda.synchronize()
+            cg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cg, stream=side):
+                fn()
+        torch.cuda.synchronize()
+        total_ms, _ = timed_steps(cg.replay, args.steps, args.warmup, lambda: flush_buf.zero_(), None)
+        return total_ms / args.steps
+
+    def put(name, ms, nbytes):
+        out[name] = {"us": ms * 1e3, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / peak}
+
+    g = torch.Generator(device=device).manual_seed(11)
+    N, H, D, bs = 131072, 8, 128, 16
+    k = torch.randn(N, H, D, device=device, generator=g).to(bf)
+    v = torch.randn(N, H, D, device=device, generator=g).to(bf)
+    kc = torch.zeros(N // bs + 8, H, bs, D, dtype=bf, device=device)
+    vc = torch.zeros_like(kc)
+    slots = torch.randperm(kc.shape[0] * bs, device=device, generator=g)[:N]
+    put("kv_paged_append 131072 tokens x 8 heads bf16", timed(lambda: kv_paged_append(k, v, kc, vc, slots)),
+        2 * 2 * N * H * D * 2 + 8 * N)
+    del k, v, kc, vc
+    B, ctx, H = 8, 8192, 32
+    kc = torch.randn(B * ctx // bs, H, bs, D, device=device, generator=g).to(bf)
+    vc = torch.randn(B * ctx // bs, H, bs, D, device=device, generator=g).to(bf)
+    bt = torch.randperm(kc.shape[0], device=device, generator=g).view(B, -1)
+    lens = torch.full((B,), ctx, dtype=torch.int32, device=device)
+    put("kv_paged_lookup 8 x 8192 x 32 heads bf16", timed(lambda: kv_paged_lookup(kc, vc, bt, lens, ctx)),
+        2 * 2 * B * H * ctx * D * 2)
+    del kc, vc
+    x = torch.randn(8, 2048, 32, D, device=device, generator=g).to(bf)
+    cos, sin = build_rope_tables(2048, D, base=1e6, device=device, dtype=bf)
+    put("apply_rope_ 8 x 2048 x 32 x 128 bf16", timed(lambda: apply_rope_(x, cos, sin)), 2 * x.numel() * 2)
+    for M, Nn, dt in ((4096, 4096, bf), (512, 50257, bf), (32768, 1024, bf), (8192, 8192, torch.float32)):
+        x = torch.randn(M, Nn, device=device, generator=g).to(dt)
+        put(f"online_softmax {M} x {Nn} {str(dt)[6:]}", timed(lambda: online_softmax(x)), 2 * x.numel() * x.element_size())
+    return out
+
+
 def check_against_oracle(res, n_req=2):
     """Cheap sanity outside every timed region: first requests of the batch vs the CPU oracle."""
     import oracle
@@ -727,6 +782,8 @@ def run_ours(args):
         line["other_workloads"]["cfg5"] = measure_mixed(args, device)
         torch.cuda.empty_cache()
         line["other_workloads"]["fused_linear_norm"] = measure_linear_norm(args, device)
+        torch.cuda.empty_cache()
+        line["other_workloads"]["small_ops"] = measure_small_ops(args, device)
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -738,7 +795,8 @@ def run_only(args):
     assert torch.cuda.is_available(), "bench.py needs a GPU"
     device = torch.device("cuda", 0)
     torch.cuda.set_device(0)
-    block = {"cfg3": measure_prefill, "cfg5": measure_mixed, "linear_norm": measure_linear_norm}[args.only](args, device)
+    block = {"cfg3": measure_prefill, "cfg5": measure_mixed, "linear_norm": measure_linear_norm,
+             "small_ops": measure_small_ops}[args.only](args, device)
     print(json.dumps({"only": args.only, "steps": args.steps, "warmup": args.warmup, **block}), flush=True)
 
 

@@ -1,17 +1,19 @@
 // Row softmax / log-softmax (the public online_softmax op). Bandwidth-bound: 2*numel*e
 // bytes (benchmark/bench_softmax.py:34), every element read once and written once.
-//   * rows whose 16-byte vectors divide evenly (and up to 16 K elements): one CTA of 256
-//     threads per row, the row lives in registers as fp32 (up to 8 vectors per thread),
-//     two block reductions (max, sum), vector stores;
-//   * other rows up to 51 200 elements: one CTA per row, the row staged in shared memory as
-//     fp32; loads and stores are 16-byte vectors over the aligned body of the row with scalar
-//     head and tail, so odd lengths (50 257) and unaligned rows still move full sectors;
+//   * rows whose 16-byte vectors divide evenly (and up to 16 K elements): the row lives in
+//     registers as fp32, 1/2/4/8 vectors per thread (templated, so short rows keep their
+//     occupancy); a warp per row with shuffles only (eight rows per CTA) or a CTA of 256 threads
+//     per row with two block reductions; vector stores;
+//   * other rows up to 200 KB: one CTA per row, the row staged in shared memory in its own type
+//     (a 16-bit row of 50 257 elements is 100 KB: two CTAs per SM); loads and stores are 16-byte
+//     vectors over the aligned body of the row with scalar head and tail, so odd lengths and
+//     unaligned rows still move full sectors;
 //   * longer rows: three passes over global memory.
 #include "common.cuh"
 
 namespace rfx {
 
-constexpr int kSoftmaxMaxSmemFloats = 51200;  // 200 KiB
+constexpr int kSoftmaxMaxSmemBytes = 200 * 1024;  // staged rows: up to 51 200 fp32 or 102 400 16-bit elements
 constexpr int kVecThreads = 256;
 constexpr int kVecItems = 8;                  // vectors per thread in the register kernel
 
@@ -31,7 +33,9 @@ template <typename T> struct alignas(16) Vec16 { T v[16 / sizeof(T)]; };
 // Register kernel: n % V == 0, rows 16-byte aligned, n <= TPR * kVecItems * V. TPR threads
 // share a row: a whole CTA (two block reductions) or one warp (shuffles only, eight rows
 // per CTA). exp through ex2 of the pre-scaled difference, one reciprocal per row.
-template <typename T, int TPR>
+// ITEMS = vectors per thread (1, 2, 4 or 8): the row is held in ITEMS * V registers, so short rows
+// do not pay the register footprint (and the occupancy) of the longest one.
+template <typename T, int TPR, int ITEMS>
 __global__ void __launch_bounds__(kVecThreads)
 softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n, int causal, int is_log) {
     constexpr int V = 16 / sizeof(T);
@@ -48,10 +52,10 @@ softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows
         const Vec16<T>* xr = reinterpret_cast<const Vec16<T>*>(x + row * (int64_t)n);
         Vec16<T>* yr = reinterpret_cast<Vec16<T>*>(y + row * (int64_t)n);
         const int valid = causal ? (int)(row % n) + 1 : n;  // columns [0, valid) take part
-        float f[kVecItems][V];
+        float f[ITEMS][V];
         float m = -INFINITY;
 #pragma unroll
-        for (int it = 0; it < kVecItems; ++it) {
+        for (int it = 0; it < ITEMS; ++it) {
             const int vi = it * TPR + tr;
             if (live && vi < nvec) {
                 const Vec16<T> p = xr[vi];
@@ -68,7 +72,7 @@ softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows
         const float mb = m * kLog2e;
         float l = 0.f;
 #pragma unroll
-        for (int it = 0; it < kVecItems; ++it) {
+        for (int it = 0; it < ITEMS; ++it) {
             const int vi = it * TPR + tr;
             if (live && vi < nvec) {
 #pragma unroll
@@ -83,7 +87,7 @@ softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows
         const float logl = logf(l);
         const float inv = 1.0f / l;
 #pragma unroll
-        for (int it = 0; it < kVecItems; ++it) {
+        for (int it = 0; it < ITEMS; ++it) {
             const int vi = it * TPR + tr;
             if (live && vi < nvec) {
                 Vec16<T> o;
@@ -134,39 +138,59 @@ __device__ inline void for_each_store(T* row, int count, F val) {
     for (int i = head + nbody * V + threadIdx.x; i < count; i += blockDim.x) row[i] = Num<T>::from_f(val(i));
 }
 
+// STAGED: the row is kept in shared memory in its own type (a 16-bit row of 50 257 elements is
+// 100 KB, so two CTAs share an SM), read from global memory once and written once; the
+// exponentials are evaluated twice (sum, output) rather than kept as fp32.
 template <typename T, bool STAGED>
 __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n,
                                     int causal, int is_log) {
-    extern __shared__ float srow[];
+    extern __shared__ __align__(16) unsigned char srow_raw[];
+    T* srow = reinterpret_cast<T*>(srow_raw);
     __shared__ float red[32];
+    constexpr float kLog2e = 1.4426950408889634f;
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const T* xr = x + row * (int64_t)n;
         T* yr = y + row * (int64_t)n;
         const int valid = causal ? (int)(row % n) + 1 : n;  // columns [0, valid) take part
         float m = -INFINITY;
-        for_each_load<T>(xr, valid, [&](int i, float v) {
-            if (STAGED) srow[i] = v;
-            m = fmaxf(m, v);
-        });
-        m = block_reduce(m, true, red);  // also orders the smem writes before the reads below
-        float l = 0.f;
         if (STAGED) {
-            for (int i = threadIdx.x; i < valid; i += blockDim.x) {
-                const float e = expf(srow[i] - m);
-                if (!is_log) srow[i] = e;
-                l += e;
+            // raw copy with 16-byte vectors over the aligned body of the row
+            constexpr int V = 16 / sizeof(T);
+            const int mis = (int)(((uintptr_t)xr % 16) / sizeof(T));
+            const int head = min(valid, mis ? V - mis : 0);
+            // the staged row keeps the global row's misalignment so that vector k of the body lands
+            // on a 16-byte boundary of shared memory too
+            T* sr = srow + mis;
+            for (int i = threadIdx.x; i < head; i += blockDim.x) { const T v = xr[i]; sr[i] = v; m = fmaxf(m, Num<T>::to_f(v)); }
+            const int nbody = (valid - head) / V;
+            struct alignas(16) Vec { T v[V]; };
+            const Vec* gb = reinterpret_cast<const Vec*>(xr + head);
+            Vec* sb = reinterpret_cast<Vec*>(sr + head);
+            for (int vi = threadIdx.x; vi < nbody; vi += blockDim.x) {
+                const Vec p = gb[vi];
+                sb[vi] = p;
+#pragma unroll
+                for (int j = 0; j < V; ++j) m = fmaxf(m, Num<T>::to_f(p.v[j]));
             }
-        } else {
-            for_each_load<T>(xr, valid, [&](int, float v) { l += expf(v - m); });
-        }
-        l = block_reduce(l, false, red);
-        const float logl = logf(l);
-        if (STAGED) {
+            for (int i = head + nbody * V + threadIdx.x; i < valid; i += blockDim.x) { const T v = xr[i]; sr[i] = v; m = fmaxf(m, Num<T>::to_f(v)); }
+            m = block_reduce(m, true, red);  // also orders the smem writes before the reads below
+            const float mb = m * kLog2e;
+            float l = 0.f;
+            for (int i = threadIdx.x; i < valid; i += blockDim.x) l += exp2f(fmaf(Num<T>::to_f(sr[i]), kLog2e, -mb));
+            l = block_reduce(l, false, red);
+            const float logl = logf(l), inv = 1.0f / l;
             for_each_store<T>(yr, n, [&](int i) -> float {
                 if (i >= valid) return is_log ? -INFINITY : 0.f;
-                return is_log ? (srow[i] - m) - logl : srow[i] / l;
+                const float v = Num<T>::to_f(sr[i]);
+                return is_log ? (v - m) - logl : exp2f(fmaf(v, kLog2e, -mb)) * inv;
             });
         } else {
+            for_each_load<T>(xr, valid, [&](int, float v) { m = fmaxf(m, v); });
+            m = block_reduce(m, true, red);
+            float l = 0.f;
+            for_each_load<T>(xr, valid, [&](int, float v) { l += expf(v - m); });
+            l = block_reduce(l, false, red);
+            const float logl = logf(l);
             for (int i = threadIdx.x; i < n; i += blockDim.x) {
                 float o;
                 if (i >= valid) o = is_log ? -INFINITY : 0.f;
@@ -210,19 +234,28 @@ extern "C" int rfx_online_softmax(const RfxSoftmaxArgs* a) {
         const bool warp_rows = n <= 32 * kVecItems * V;  // a warp per row, eight rows per CTA
         int64_t g2 = warp_rows ? (a->rows + 7) / 8 : a->rows;
         if (g2 > cap) g2 = cap;
+        const int tpr = warp_rows ? 32 : kVecThreads;
+        const int need = ((n / V) + tpr - 1) / tpr;  // vectors per thread
+#define RFX_SOFTMAX_REG(T, TPR, ITEMS)                                                                      \
+    softmax_rows_reg_kernel<T, TPR, ITEMS><<<(int)g2, kVecThreads, 0, s>>>((const T*)a->x, (T*)a->y, a->rows, n, \
+                                                                           a->is_causal, a->log)
+#define RFX_SOFTMAX_ITEMS(T, TPR)                    \
+    if (need <= 1) RFX_SOFTMAX_REG(T, TPR, 1);       \
+    else if (need <= 2) RFX_SOFTMAX_REG(T, TPR, 2);  \
+    else if (need <= 4) RFX_SOFTMAX_REG(T, TPR, 4);  \
+    else RFX_SOFTMAX_REG(T, TPR, 8)
         RFX_DISPATCH_DTYPE(a->dtype, T, {
-            if (warp_rows)
-                softmax_rows_reg_kernel<T, 32><<<(int)g2, kVecThreads, 0, s>>>((const T*)a->x, (T*)a->y, a->rows, n,
-                                                                               a->is_causal, a->log);
-            else
-                softmax_rows_reg_kernel<T, kVecThreads><<<(int)g2, kVecThreads, 0, s>>>(
-                    (const T*)a->x, (T*)a->y, a->rows, n, a->is_causal, a->log);
+            if (warp_rows) { RFX_SOFTMAX_ITEMS(T, 32); }
+            else { RFX_SOFTMAX_ITEMS(T, kVecThreads); }
         });
+#undef RFX_SOFTMAX_ITEMS
+#undef RFX_SOFTMAX_REG
         return check_launch(name);
     }
     const int threads = n <= 512 ? 64 : n <= 4096 ? 128 : n <= 16384 ? 256 : 1024;
-    const bool staged = n <= kSoftmaxMaxSmemFloats;
-    const size_t smem = staged ? (size_t)n * sizeof(float) : 0;
+    const size_t smem_need = (size_t)n * e + 32;  // the row in its own type + room for its misalignment
+    const bool staged = smem_need <= (size_t)kSoftmaxMaxSmemBytes;
+    const size_t smem = staged ? smem_need : 0;
     RFX_DISPATCH_DTYPE(a->dtype, T, {
         if (staged) {
             auto kern = softmax_rows_kernel<T, true>;
