@@ -58,13 +58,18 @@ softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows
         for (int it = 0; it < ITEMS; ++it) {
             const int vi = it * TPR + tr;
             if (live && vi < nvec) {
-                const Vec16<T> p = xr[vi];
+                if (vi * V < valid) {
+                    const Vec16<T> p = xr[vi];
 #pragma unroll
-                for (int j = 0; j < V; ++j) {
-                    float v = Num<T>::to_f(p.v[j]);
-                    if (vi * V + j >= valid) v = -INFINITY;
-                    f[it][j] = v;
-                    m = fmaxf(m, v);
+                    for (int j = 0; j < V; ++j) {
+                        float v = Num<T>::to_f(p.v[j]);
+                        if (vi * V + j >= valid) v = -INFINITY;
+                        f[it][j] = v;
+                        m = fmaxf(m, v);
+                    }
+                } else {  // wholly masked (causal): not read
+#pragma unroll
+                    for (int j = 0; j < V; ++j) f[it][j] = -INFINITY;
                 }
             }
         }
