@@ -46,6 +46,28 @@ softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows
     const int tr = threadIdx.x % TPR;
     const int sub = threadIdx.x / TPR;
     const int64_t row_groups = (rows + RPC - 1) / RPC;
+    // Long fp32 rows on a whole CTA (PIPE): only two or three such CTAs fit an SM and their
+    // block-wide reductions leave the memory system idle, so the grid is one wave of resident CTAs,
+    // every CTA walks several rows, and the raw vectors of its next row are requested before the
+    // current row's reductions and stores (fp32 8192 x 8192: 152 -> 91 us, 4096 x 4096: 39 -> 29 us).
+    // Measured slower with it, and so left as they were: 16-bit rows (twice the arithmetic per
+    // byte; 8192 x 8192 bf16 72 -> 90 us), short rows, and a warp per row.
+    constexpr bool PIPE = TPR != 32 && sizeof(T) == 4 && ITEMS >= 4;
+    Vec16<T> nxt[PIPE ? ITEMS : 1];
+    auto fetch = [&](int64_t grp) {
+        const int64_t row = grp * RPC + sub;
+        if (grp >= row_groups || row >= rows) return;
+        const Vec16<T>* xr = reinterpret_cast<const Vec16<T>*>(x + row * (int64_t)n);
+        const int valid = causal ? (int)(row % n) + 1 : n;
+        if constexpr (PIPE) {
+#pragma unroll
+            for (int it = 0; it < ITEMS; ++it) {
+                const int vi = it * TPR + tr;
+                if (vi < nvec && vi * V < valid) nxt[it] = xr[vi];  // wholly masked vectors (causal) are not read
+            }
+        }
+    };
+    if (PIPE) fetch(blockIdx.x);
     for (int64_t grp = blockIdx.x; grp < row_groups; grp += gridDim.x) {
         const int64_t row = grp * RPC + sub;
         const bool live = row < rows;
@@ -59,7 +81,7 @@ softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows
             const int vi = it * TPR + tr;
             if (live && vi < nvec) {
                 if (vi * V < valid) {
-                    const Vec16<T> p = xr[vi];
+                    const Vec16<T> p = PIPE ? nxt[PIPE ? it : 0] : xr[vi];
 #pragma unroll
                     for (int j = 0; j < V; ++j) {
                         float v = Num<T>::to_f(p.v[j]);
@@ -67,12 +89,13 @@ softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows
                         f[it][j] = v;
                         m = fmaxf(m, v);
                     }
-                } else {  // wholly masked (causal): not read
+                } else {
 #pragma unroll
                     for (int j = 0; j < V; ++j) f[it][j] = -INFINITY;
                 }
             }
         }
+        if (PIPE) fetch(grp + gridDim.x);
         m = (TPR == 32) ? warp_max(m) : block_reduce(m, true, red);
         const float mb = m * kLog2e;
         float l = 0.f;
@@ -180,15 +203,42 @@ __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, 
             for (int i = head + nbody * V + threadIdx.x; i < valid; i += blockDim.x) { const T v = xr[i]; sr[i] = v; m = fmaxf(m, Num<T>::to_f(v)); }
             m = block_reduce(m, true, red);  // also orders the smem writes before the reads below
             const float mb = m * kLog2e;
+            // The two passes over the staged row read it as 16-byte vectors too: with one element per
+            // load the kernel was bound by its instruction count, not by memory.
             float l = 0.f;
-            for (int i = threadIdx.x; i < valid; i += blockDim.x) l += exp2f(fmaf(Num<T>::to_f(sr[i]), kLog2e, -mb));
+            const int tail0 = head + nbody * V;
+            for (int i = threadIdx.x; i < head; i += blockDim.x) l += exp2f(fmaf(Num<T>::to_f(sr[i]), kLog2e, -mb));
+            for (int vi = threadIdx.x; vi < nbody; vi += blockDim.x) {
+                const Vec p = sb[vi];
+#pragma unroll
+                for (int j = 0; j < V; ++j) l += exp2f(fmaf(Num<T>::to_f(p.v[j]), kLog2e, -mb));
+            }
+            for (int i = tail0 + threadIdx.x; i < valid; i += blockDim.x) l += exp2f(fmaf(Num<T>::to_f(sr[i]), kLog2e, -mb));
             l = block_reduce(l, false, red);
             const float logl = logf(l), inv = 1.0f / l;
-            for_each_store<T>(yr, n, [&](int i) -> float {
+            auto out_of = [&](int i, float v) -> float {
                 if (i >= valid) return is_log ? -INFINITY : 0.f;
-                const float v = Num<T>::to_f(sr[i]);
                 return is_log ? (v - m) - logl : exp2f(fmaf(v, kLog2e, -mb)) * inv;
-            });
+            };
+            if ((int)(((uintptr_t)yr % 16) / sizeof(T)) == mis) {
+                // output row aligned like the input row: vector k of the staged body is vector k of the output
+                const int head_y = min(n, mis ? V - mis : 0);
+                const int nbody_y = (n - head_y) / V;
+                for (int i = threadIdx.x; i < head_y; i += blockDim.x) yr[i] = Num<T>::from_f(out_of(i, Num<T>::to_f(sr[i])));
+                Vec* yb = reinterpret_cast<Vec*>(yr + head_y);
+                const Vec* sby = reinterpret_cast<const Vec*>(sr + head_y);
+                for (int vi = threadIdx.x; vi < nbody_y; vi += blockDim.x) {
+                    const Vec p = sby[vi];  // columns past `valid` were never staged: whatever is read there is not used
+                    Vec o;
+#pragma unroll
+                    for (int j = 0; j < V; ++j) o.v[j] = Num<T>::from_f(out_of(head_y + vi * V + j, Num<T>::to_f(p.v[j])));
+                    yb[vi] = o;
+                }
+                for (int i = head_y + nbody_y * V + threadIdx.x; i < n; i += blockDim.x)
+                    yr[i] = Num<T>::from_f(out_of(i, Num<T>::to_f(sr[i])));
+            } else {
+                for_each_store<T>(yr, n, [&](int i) -> float { return out_of(i, i < valid ? Num<T>::to_f(sr[i]) : 0.f); });
+            }
         } else {
             for_each_load<T>(xr, valid, [&](int, float v) { m = fmaxf(m, v); });
             m = block_reduce(m, true, red);
@@ -237,13 +287,22 @@ extern "C" int rfx_online_softmax(const RfxSoftmaxArgs* a) {
                         ((uintptr_t)a->y % 16) == 0;
     if (reg_ok) {
         const bool warp_rows = n <= 32 * kVecItems * V;  // a warp per row, eight rows per CTA
-        int64_t g2 = warp_rows ? (a->rows + 7) / 8 : a->rows;
-        if (g2 > cap) g2 = cap;
+        const int64_t groups = warp_rows ? (a->rows + 7) / 8 : a->rows;
         const int tpr = warp_rows ? 32 : kVecThreads;
         const int need = ((n / V) + tpr - 1) / tpr;  // vectors per thread
-#define RFX_SOFTMAX_REG(T, TPR, ITEMS)                                                                      \
-    softmax_rows_reg_kernel<T, TPR, ITEMS><<<(int)g2, kVecThreads, 0, s>>>((const T*)a->x, (T*)a->y, a->rows, n, \
-                                                                           a->is_causal, a->log)
+        // the grid is one wave of resident CTAs (what the occupancy query says fits), each walking several rows
+#define RFX_SOFTMAX_REG(T, TPR, ITEMS)                                                                          \
+    do {                                                                                                        \
+        static int per_sm = 0;                                                                                  \
+        if (!per_sm &&                                                                                          \
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, softmax_rows_reg_kernel<T, TPR, ITEMS>,      \
+                                                          kVecThreads, 0) != cudaSuccess)                       \
+            per_sm = 1;                                                                                         \
+        const int64_t wave = (TPR == 32 || sizeof(T) != 4 || ITEMS < 4) ? cap : (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);  \
+        const int64_t g2 = groups < wave ? groups : wave;                                                       \
+        softmax_rows_reg_kernel<T, TPR, ITEMS><<<(int)g2, kVecThreads, 0, s>>>((const T*)a->x, (T*)a->y,        \
+                                                                               a->rows, n, a->is_causal, a->log); \
+    } while (0)
 #define RFX_SOFTMAX_ITEMS(T, TPR)                    \
     if (need <= 1) RFX_SOFTMAX_REG(T, TPR, 1);       \
     else if (need <= 2) RFX_SOFTMAX_REG(T, TPR, 2);  \
