@@ -29,6 +29,22 @@ def test_golden(name, native):
     assert y.dtype == c["x"].dtype and y.shape == c["x"].shape
 
 
+@pytest.mark.parametrize("n", [4096, 8192])
+def test_long_fp32_rows_many_per_cta(native, n):
+    """fp32 rows of four or eight vectors per thread: the grid is one wave of CTAs, each walking
+    several rows with the next row's loads already in flight; plain and causal (ragged lengths)."""
+    x = torch.randn(1500, n, device=DEV, generator=torch.Generator(device=DEV).manual_seed(n))
+    torch.testing.assert_close(online_softmax(x).cpu(), oracle.online_softmax(x.cpu()), atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(online_softmax(x, log=True).cpu(), oracle.online_softmax(x.cpu(), log=True), atol=1e-4, rtol=1e-5)
+    sq = torch.randn(1, 1, n, n, device=DEV, generator=torch.Generator(device=DEV).manual_seed(n + 1))
+    y = online_softmax(sq, is_causal=True)
+    rows = torch.tensor([0, 1, 7, 8, 1023, 1024, n // 2, n - 2, n - 1])
+    ref = oracle.online_softmax(sq.cpu(), is_causal=True)
+    torch.testing.assert_close(y.cpu()[0, 0, rows], ref[0, 0, rows], atol=1e-5, rtol=1e-5)
+    assert not torch.triu(y[0, 0], diagonal=1).any()
+    torch.testing.assert_close(y[0, 0].sum(-1), torch.ones(n, device=DEV), atol=1e-4, rtol=0)
+
+
 @pytest.mark.parametrize("n", [1, 33, 4096, 50257, 60000])
 def test_rows_sum_to_one(native, n):  # reference tests/test_softmax.py:17-33; 60000 takes the unstaged path
     x = torch.randn(6, n, device=DEV, generator=torch.Generator(device=DEV).manual_seed(n))
