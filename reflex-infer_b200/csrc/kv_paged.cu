@@ -18,15 +18,28 @@ kv_append_kernel(const VEC* __restrict__ k_in, const VEC* __restrict__ v_in,
                  int64_t in_sn, int64_t in_sh,              // strides in VEC units
                  int64_t c_sblk, int64_t c_sh, int64_t c_spos) {
     const int64_t total = n_tokens * heads * vec_per_row;
+    // a 64-bit division costs about a hundred instructions, several per piece more than the copy
+    // itself: below 2^31 pieces (and slots) the indices are taken apart in 32 bits
+    const bool small = total < (1ll << 31) && num_slots < (1ll << 31);
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
-        const int c = (int)(i % vec_per_row);
-        const int64_t row = i / vec_per_row;
-        const int h = (int)(row % heads);
-        const int64_t n = row / heads;
+        int c, h;
+        int64_t n;
+        if (small) {
+            uint32_t r = (uint32_t)i;
+            c = (int)(r % (uint32_t)vec_per_row);
+            r /= (uint32_t)vec_per_row;
+            h = (int)(r % (uint32_t)heads);
+            n = (int64_t)(r / (uint32_t)heads);
+        } else {
+            c = (int)(i % vec_per_row);
+            const int64_t row = i / vec_per_row;
+            h = (int)(row % heads);
+            n = row / heads;
+        }
         const int64_t slot = slots[n];
         if (slot < 0 || slot >= num_slots) continue;
-        const int64_t page = slot / block_size;
+        const int64_t page = small ? (int64_t)((uint32_t)slot / (uint32_t)block_size) : slot / block_size;
         const int pos = (int)(slot - page * block_size);
         const int64_t src = n * in_sn + h * in_sh + c;
         const int64_t dst = page * c_sblk + h * c_sh + pos * c_spos + c;
@@ -45,18 +58,33 @@ kv_lookup_kernel(const VEC* __restrict__ k_cache, const VEC* __restrict__ v_cach
                  int64_t num_blocks, int block_size, int64_t max_blocks, int64_t bt_sb,
                  int64_t c_sblk, int64_t c_sh, int64_t c_spos) {
     const int64_t total = batch * heads * max_ctx * vec_per_row;
+    const bool small = total < (1ll << 31);  // then the index is taken apart in 32 bits (see kv_append_kernel)
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
-        const int c = (int)(i % vec_per_row);
-        int64_t r = i / vec_per_row;
-        const int64_t t = r % max_ctx;
-        r /= max_ctx;
-        const int h = (int)(r % heads);
-        const int64_t b = r / heads;
+        int c, h;
+        int64_t t, b, j;
+        if (small) {
+            uint32_t r = (uint32_t)i;
+            c = (int)(r % (uint32_t)vec_per_row);
+            r /= (uint32_t)vec_per_row;
+            const uint32_t t32 = r % (uint32_t)max_ctx;
+            r /= (uint32_t)max_ctx;
+            h = (int)(r % (uint32_t)heads);
+            b = (int64_t)(r / (uint32_t)heads);
+            t = (int64_t)t32;
+            j = (int64_t)(t32 / (uint32_t)block_size);
+        } else {
+            c = (int)(i % vec_per_row);
+            int64_t r = i / vec_per_row;
+            t = r % max_ctx;
+            r /= max_ctx;
+            h = (int)(r % heads);
+            b = r / heads;
+            j = t / block_size;
+        }
         VEC kv, vv;
         memset(&kv, 0, sizeof(VEC));
         memset(&vv, 0, sizeof(VEC));
-        const int64_t j = t / block_size;
         if (t < (int64_t)ctx_lens[b] && j < max_blocks) {
             const int64_t page = block_table[b * bt_sb + j];
             if (page >= 0 && page < num_blocks) {

@@ -64,14 +64,29 @@ rope_apply_kernel(const T* x, T* y, const T* __restrict__ cosb, const T* __restr
                   int64_t xsb, int64_t xss, int64_t xsh, int64_t ysb, int64_t yss, int64_t ysh,
                   int64_t tss) {
     const int64_t total = B * S * H * pieces;
+    // 64-bit divisions cost a few hundred instructions per piece, more than the rotation itself:
+    // below 2^31 pieces the index is taken apart in 32 bits
+    const bool small = total < (1ll << 31);
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
-        const int p = (int)(i % pieces);
-        int64_t r = i / pieces;
-        const int h = (int)(r % H);
-        r /= H;
-        const int64_t s = r % S;
-        const int64_t b = r / S;
+        int p, h;
+        int64_t s, b;
+        if (small) {
+            uint32_t r = (uint32_t)i;
+            p = (int)(r % (uint32_t)pieces);
+            r /= (uint32_t)pieces;
+            h = (int)(r % (uint32_t)H);
+            r /= (uint32_t)H;
+            s = (int64_t)(r % (uint32_t)S);
+            b = (int64_t)(r / (uint32_t)S);
+        } else {
+            p = (int)(i % pieces);
+            int64_t r = i / pieces;
+            h = (int)(r % H);
+            r /= H;
+            s = r % S;
+            b = r / S;
+        }
         rope_piece<T, V, INTER>(x + b * xsb + s * xss + h * xsh, y + b * ysb + s * yss + h * ysh,
                                 cosb + s * tss, sinb + s * tss, D, p);
     }
@@ -89,12 +104,23 @@ rope_append_kernel(const T* __restrict__ k_in, const T* __restrict__ v_in, const
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the split-K plan may start alongside
     const int rows_per_tok = 2 * Hkv + Hq;
     const int64_t total = N * rows_per_tok * pieces;
+    const bool small = total < (1ll << 31);  // then the index is taken apart in 32 bits (see rope_apply_kernel)
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
-        const int p = (int)(i % pieces);
-        int64_t r = i / pieces;
-        const int row = (int)(r % rows_per_tok);
-        const int64_t n = r / rows_per_tok;
+        int p, row;
+        int64_t n;
+        if (small) {
+            uint32_t r = (uint32_t)i;
+            p = (int)(r % (uint32_t)pieces);
+            r /= (uint32_t)pieces;
+            row = (int)(r % (uint32_t)rows_per_tok);
+            n = (int64_t)(r / (uint32_t)rows_per_tok);
+        } else {
+            p = (int)(i % pieces);
+            const int64_t r = i / pieces;
+            row = (int)(r % rows_per_tok);
+            n = r / rows_per_tok;
+        }
         int64_t pos = positions[n];
         if (pos < 0 || pos >= table_rows) continue;  // no table row: leave the token untouched
         const T* cr = cosb + pos * D;
