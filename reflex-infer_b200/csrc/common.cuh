@@ -61,6 +61,27 @@ template <typename T> __device__ inline T add_r(T a, T b) {
     return Num<T>::from_f(__fadd_rn(Num<T>::to_f(a), Num<T>::to_f(b)));
 }
 
+// Two 16-bit values side by side. The product of two bf16 (or fp16) numbers is exact in fp32, so
+// "widen, multiply in fp32, round to T" is one rounding of the exact product, which is what the
+// packed multiply does for both lanes in one instruction (results below the fp32 normal range, where
+// the fp32 product itself would already have rounded, are the one place the two could differ).
+// Sums are not exact in fp32, so add_r / sub_r keep the widened form.
+template <typename T> struct Pair16;
+template <> struct Pair16<__nv_bfloat16> {
+    using P = __nv_bfloat162;
+    __device__ static P mul(P a, P b) { return __hmul2(a, b); }
+    __device__ static float2 widen(P a) { return __bfloat1622float2(a); }
+    __device__ static P round(float a, float b) { return __floats2bfloat162_rn(a, b); }
+    __device__ static P both_low(P a) { return __low2bfloat162(a); }
+};
+template <> struct Pair16<__half> {
+    using P = __half2;
+    __device__ static P mul(P a, P b) { return __hmul2(a, b); }
+    __device__ static float2 widen(P a) { return __half22float2(a); }
+    __device__ static P round(float a, float b) { return __floats2half2_rn(a, b); }
+    __device__ static P both_low(P a) { return __low2half2(a); }
+};
+
 // The RoPE pair rotation of kernels/rope/triton_rope.py:230-240 in torch-eager rounding:
 //   y1 = x1*c - x2*s ; y2 = x1*s + x2*c, each op rounded to T.
 template <typename T>

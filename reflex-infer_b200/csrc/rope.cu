@@ -15,10 +15,65 @@ template <typename T, int V> struct alignas(sizeof(T) * V) Pack { T v[V]; };
 // [p*V, p*V+V) of the first half and their partners half further on; both table factors
 // come from the first half of the table row (triton_rope.py:226-227). Interleaved:
 // piece p covers [p*V, p*V+V), pairs (2i, 2i+1), factors from the even entries (:218-219).
+// 16-bit rows, two elements per instruction: same values as rope_pair (see Pair16). The kernels
+// were bound by their instruction count (widen, multiply, round, widen again: ~14 per element).
+template <typename T, int V, bool INTER>
+__device__ inline void rope_piece_packed(const T* x, T* y, const T* __restrict__ cosr,
+                                         const T* __restrict__ sinr, int D, int p) {
+    using P = Pack<T, V>;
+    using A = Pair16<T>;
+    using W = typename A::P;
+    const int o = p * V;
+    if (INTER) {
+        P xv = *reinterpret_cast<const P*>(x + o);
+        P cv = *reinterpret_cast<const P*>(cosr + o);
+        P sv = *reinterpret_cast<const P*>(sinr + o);
+        P out;
+        const W* xw = reinterpret_cast<const W*>(&xv);
+        const W* cw = reinterpret_cast<const W*>(&cv);
+        const W* sw = reinterpret_cast<const W*>(&sv);
+        W* ow = reinterpret_cast<W*>(&out);
+#pragma unroll
+        for (int j = 0; j < V / 2; ++j) {
+            // pair (x0, x1), factors from the even entry: y0 = x0 c - x1 s, y1 = x0 s + x1 c
+            const float2 pc = A::widen(A::mul(xw[j], A::both_low(cw[j])));
+            const float2 ps = A::widen(A::mul(xw[j], A::both_low(sw[j])));
+            ow[j] = A::round(__fsub_rn(pc.x, ps.y), __fadd_rn(ps.x, pc.y));
+        }
+        *reinterpret_cast<P*>(y + o) = out;
+    } else {
+        const int half = D >> 1;
+        P x1 = *reinterpret_cast<const P*>(x + o);
+        P x2 = *reinterpret_cast<const P*>(x + half + o);
+        P cv = *reinterpret_cast<const P*>(cosr + o);
+        P sv = *reinterpret_cast<const P*>(sinr + o);
+        P y1, y2;
+        const W* x1w = reinterpret_cast<const W*>(&x1);
+        const W* x2w = reinterpret_cast<const W*>(&x2);
+        const W* cw = reinterpret_cast<const W*>(&cv);
+        const W* sw = reinterpret_cast<const W*>(&sv);
+        W* y1w = reinterpret_cast<W*>(&y1);
+        W* y2w = reinterpret_cast<W*>(&y2);
+#pragma unroll
+        for (int j = 0; j < V / 2; ++j) {
+            const float2 a = A::widen(A::mul(x1w[j], cw[j])), bb = A::widen(A::mul(x2w[j], sw[j]));
+            const float2 c = A::widen(A::mul(x1w[j], sw[j])), d = A::widen(A::mul(x2w[j], cw[j]));
+            y1w[j] = A::round(__fsub_rn(a.x, bb.x), __fsub_rn(a.y, bb.y));
+            y2w[j] = A::round(__fadd_rn(c.x, d.x), __fadd_rn(c.y, d.y));
+        }
+        *reinterpret_cast<P*>(y + o) = y1;
+        *reinterpret_cast<P*>(y + half + o) = y2;
+    }
+}
+
 template <typename T, int V, bool INTER>
 __device__ inline void rope_piece(const T* x, T* y, const T* __restrict__ cosr,
                                   const T* __restrict__ sinr, int D, int p) {
     using P = Pack<T, V>;
+    if constexpr (sizeof(T) == 2 && V >= 2) {
+        rope_piece_packed<T, V, INTER>(x, y, cosr, sinr, D, p);
+        return;
+    }
     if (INTER) {
         const int o = p * V;
         P xv = *reinterpret_cast<const P*>(x + o);
