@@ -30,6 +30,27 @@ __device__ inline float block_reduce(float v, bool is_max, float* red) {
 
 template <typename T> struct alignas(16) Vec16 { T v[16 / sizeof(T)]; };
 
+// 2^x by the hardware approximation (2 ulp, results below the normal range flush to zero): the
+// library exp2f spends four more instructions per element on that range, and the register
+// kernels are bound by their instruction count.
+__device__ __forceinline__ float ex2_fast(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+// Two results rounded to T and stored side by side: one packed conversion for the 16-bit types.
+template <typename T> __device__ __forceinline__ void put2(T* dst, float a, float b) {
+    dst[0] = Num<T>::from_f(a);
+    dst[1] = Num<T>::from_f(b);
+}
+template <> __device__ __forceinline__ void put2<__nv_bfloat16>(__nv_bfloat16* dst, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(a, b);
+}
+template <> __device__ __forceinline__ void put2<__half>(__half* dst, float a, float b) {
+    *reinterpret_cast<__half2*>(dst) = __floats2half2_rn(a, b);
+}
+
 // Register kernel: n % V == 0, rows 16-byte aligned, n <= TPR * kVecItems * V. TPR threads
 // share a row: a whole CTA (two block reductions) or one warp (shuffles only, eight rows
 // per CTA). exp through ex2 of the pre-scaled difference, one reciprocal per row.
@@ -82,12 +103,20 @@ softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows
             if (live && vi < nvec) {
                 if (vi * V < valid) {
                     const Vec16<T> p = PIPE ? nxt[PIPE ? it : 0] : xr[vi];
+                    if (vi * V + V <= valid) {  // the usual case: no column of this vector is masked
 #pragma unroll
-                    for (int j = 0; j < V; ++j) {
-                        float v = Num<T>::to_f(p.v[j]);
-                        if (vi * V + j >= valid) v = -INFINITY;
-                        f[it][j] = v;
-                        m = fmaxf(m, v);
+                        for (int j = 0; j < V; ++j) {
+                            f[it][j] = Num<T>::to_f(p.v[j]);
+                            m = fmaxf(m, f[it][j]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < V; ++j) {
+                            float v = Num<T>::to_f(p.v[j]);
+                            if (vi * V + j >= valid) v = -INFINITY;
+                            f[it][j] = v;
+                            m = fmaxf(m, v);
+                        }
                     }
                 } else {
 #pragma unroll
@@ -103,11 +132,15 @@ softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows
         for (int it = 0; it < ITEMS; ++it) {
             const int vi = it * TPR + tr;
             if (live && vi < nvec) {
+                if (is_log) {
 #pragma unroll
-                for (int j = 0; j < V; ++j) {
-                    const float e = exp2f(fmaf(f[it][j], kLog2e, -mb));  // 0 for masked columns
-                    l += e;
-                    if (!is_log) f[it][j] = e;
+                    for (int j = 0; j < V; ++j) l += ex2_fast(fmaf(f[it][j], kLog2e, -mb));  // 0 for masked columns
+                } else {
+#pragma unroll
+                    for (int j = 0; j < V; ++j) {
+                        f[it][j] = ex2_fast(fmaf(f[it][j], kLog2e, -mb));
+                        l += f[it][j];
+                    }
                 }
             }
         }
@@ -119,10 +152,12 @@ softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows
             const int vi = it * TPR + tr;
             if (live && vi < nvec) {
                 Vec16<T> o;
+                if (is_log) {
 #pragma unroll
-                for (int j = 0; j < V; ++j) {
-                    const float r = is_log ? (f[it][j] - m) - logl : f[it][j] * inv;
-                    o.v[j] = Num<T>::from_f(r);
+                    for (int j = 0; j < V; j += 2) put2<T>(&o.v[j], (f[it][j] - m) - logl, (f[it][j + 1] - m) - logl);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < V; j += 2) put2<T>(&o.v[j], f[it][j] * inv, f[it][j + 1] * inv);
                 }
                 yr[vi] = o;
             }
@@ -207,18 +242,18 @@ __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, 
             // load the kernel was bound by its instruction count, not by memory.
             float l = 0.f;
             const int tail0 = head + nbody * V;
-            for (int i = threadIdx.x; i < head; i += blockDim.x) l += exp2f(fmaf(Num<T>::to_f(sr[i]), kLog2e, -mb));
+            for (int i = threadIdx.x; i < head; i += blockDim.x) l += ex2_fast(fmaf(Num<T>::to_f(sr[i]), kLog2e, -mb));
             for (int vi = threadIdx.x; vi < nbody; vi += blockDim.x) {
                 const Vec p = sb[vi];
 #pragma unroll
-                for (int j = 0; j < V; ++j) l += exp2f(fmaf(Num<T>::to_f(p.v[j]), kLog2e, -mb));
+                for (int j = 0; j < V; ++j) l += ex2_fast(fmaf(Num<T>::to_f(p.v[j]), kLog2e, -mb));
             }
-            for (int i = tail0 + threadIdx.x; i < valid; i += blockDim.x) l += exp2f(fmaf(Num<T>::to_f(sr[i]), kLog2e, -mb));
+            for (int i = tail0 + threadIdx.x; i < valid; i += blockDim.x) l += ex2_fast(fmaf(Num<T>::to_f(sr[i]), kLog2e, -mb));
             l = block_reduce(l, false, red);
             const float logl = logf(l), inv = 1.0f / l;
             auto out_of = [&](int i, float v) -> float {
                 if (i >= valid) return is_log ? -INFINITY : 0.f;
-                return is_log ? (v - m) - logl : exp2f(fmaf(v, kLog2e, -mb)) * inv;
+                return is_log ? (v - m) - logl : ex2_fast(fmaf(v, kLog2e, -mb)) * inv;
             };
             if ((int)(((uintptr_t)yr % 16) / sizeof(T)) == mis) {
                 // output row aligned like the input row: vector k of the staged body is vector k of the output
@@ -230,8 +265,16 @@ __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, 
                 for (int vi = threadIdx.x; vi < nbody_y; vi += blockDim.x) {
                     const Vec p = sby[vi];  // columns past `valid` were never staged: whatever is read there is not used
                     Vec o;
+                    const int c0 = head_y + vi * V;
+                    if (c0 + V <= valid && !is_log) {  // the usual case, two results per conversion
 #pragma unroll
-                    for (int j = 0; j < V; ++j) o.v[j] = Num<T>::from_f(out_of(head_y + vi * V + j, Num<T>::to_f(p.v[j])));
+                        for (int j = 0; j < V; j += 2)
+                            put2<T>(&o.v[j], ex2_fast(fmaf(Num<T>::to_f(p.v[j]), kLog2e, -mb)) * inv,
+                                    ex2_fast(fmaf(Num<T>::to_f(p.v[j + 1]), kLog2e, -mb)) * inv);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < V; ++j) o.v[j] = Num<T>::from_f(out_of(c0 + j, Num<T>::to_f(p.v[j])));
+                    }
                     yb[vi] = o;
                 }
                 for (int i = head_y + nbody_y * V + threadIdx.x; i < n; i += blockDim.x)
