@@ -229,6 +229,7 @@ __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, 
             struct alignas(16) Vec { T v[V]; };
             const Vec* gb = reinterpret_cast<const Vec*>(xr + head);
             Vec* sb = reinterpret_cast<Vec*>(sr + head);
+#pragma unroll 4
             for (int vi = threadIdx.x; vi < nbody; vi += blockDim.x) {
                 const Vec p = gb[vi];
                 sb[vi] = p;
