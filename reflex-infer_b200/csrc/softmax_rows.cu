@@ -57,8 +57,8 @@ template <> __device__ __forceinline__ void put2<__half>(__half* dst, float a, f
 // ITEMS = vectors per thread (1, 2, 4 or 8): the row is held in ITEMS * V registers, so short rows
 // do not pay the register footprint (and the occupancy) of the longest one.
 template <typename T, int TPR, int ITEMS>
-__global__ void __launch_bounds__(kVecThreads)
-softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n, int causal, int is_log) {
+__device__ __forceinline__ void
+softmax_rows_reg_body(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n, int causal, int is_log) {
     constexpr int V = 16 / sizeof(T);
     constexpr int RPC = kVecThreads / TPR;  // rows per CTA
     constexpr float kLog2e = 1.4426950408889634f;
@@ -163,6 +163,22 @@ softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows
             }
         }
     }
+}
+
+// Two entry points over the same body. Rows of one or two vectors per thread are bound by the warps
+// in flight (ncu: 40 of 64 warps at 48 registers): eight CTAs per SM asked for, which fits them
+// into 32 registers without spills (4096 x 4096 bf16 24.6 -> 22.5 us). Longer rows keep the plain
+// bound: any minimum-blocks hint made them slower (32768 x 1024 bf16 41 -> 61 us at the same
+// register count).
+template <typename T, int TPR, int ITEMS>
+__global__ void __launch_bounds__(kVecThreads)
+softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n, int causal, int is_log) {
+    softmax_rows_reg_body<T, TPR, ITEMS>(x, y, rows, n, causal, is_log);
+}
+template <typename T, int TPR, int ITEMS>
+__global__ void __launch_bounds__(kVecThreads, 8)
+softmax_rows_reg_small_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n, int causal, int is_log) {
+    softmax_rows_reg_body<T, TPR, ITEMS>(x, y, rows, n, causal, is_log);
 }
 
 // Visits elements [0, count) of a row: scalar head up to the first 16-byte boundary, vector
@@ -337,15 +353,13 @@ extern "C" int rfx_online_softmax(const RfxSoftmaxArgs* a) {
         // the grid is one wave of resident CTAs (what the occupancy query says fits), each walking several rows
 #define RFX_SOFTMAX_REG(T, TPR, ITEMS)                                                                          \
     do {                                                                                                        \
+        auto kern = (ITEMS <= 2) ? softmax_rows_reg_small_kernel<T, TPR, ITEMS> : softmax_rows_reg_kernel<T, TPR, ITEMS>; \
         static int per_sm = 0;                                                                                  \
-        if (!per_sm &&                                                                                          \
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, softmax_rows_reg_kernel<T, TPR, ITEMS>,      \
-                                                          kVecThreads, 0) != cudaSuccess)                       \
+        if (!per_sm && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kVecThreads, 0) != cudaSuccess) \
             per_sm = 1;                                                                                         \
         const int64_t wave = (TPR == 32 || sizeof(T) != 4 || ITEMS < 4) ? cap : (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);  \
         const int64_t g2 = groups < wave ? groups : wave;                                                       \
-        softmax_rows_reg_kernel<T, TPR, ITEMS><<<(int)g2, kVecThreads, 0, s>>>((const T*)a->x, (T*)a->y,        \
-                                                                               a->rows, n, a->is_causal, a->log); \
+        kern<<<(int)g2, kVecThreads, 0, s>>>((const T*)a->x, (T*)a->y, a->rows, n, a->is_causal, a->log);       \
     } while (0)
 #define RFX_SOFTMAX_ITEMS(T, TPR)                    \
     if (need <= 1) RFX_SOFTMAX_REG(T, TPR, 1);       \
