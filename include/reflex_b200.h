@@ -205,6 +205,10 @@ typedef struct {
 } RfxAttentionArgs;
 size_t rfx_fused_attention_workspace_bytes(const RfxAttentionArgs* a);
 int rfx_fused_attention(const RfxAttentionArgs* a);
+/* Which kernel the arguments select: 1 = tcgen05 kernel (16-bit, head_dim 128, at least 32 query
+ * rows per kv head, causal only with seq_q == seq_k, additive mask allowed, 16-byte aligned
+ * tensors), 0 = scalar kernel, negative = invalid arguments. */
+int rfx_fused_attention_kernel_kind(const RfxAttentionArgs* a);
 
 /* Paged attention over ragged query chunks: the fused form of the composition
  * kv_paged_lookup -> repeat_interleave -> fused_attention evaluated per request with

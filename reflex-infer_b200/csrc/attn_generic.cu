@@ -231,6 +231,12 @@ namespace rfx {
 // Implemented in prefill_mma.cu: tensor-core path for bf16/fp16 dense attention. Returns
 // RFX_NOT_IMPLEMENTED when the shape is outside its coverage.
 int launch_dense_tensor(const RfxAttentionArgs* a);
+bool dense_tensor_ok(const RfxAttentionArgs* a);
+}
+
+extern "C" int rfx_fused_attention_kernel_kind(const RfxAttentionArgs* a) {
+    if (!a || a->num_kv_heads <= 0 || a->num_q_heads <= 0) return -1;
+    return rfx::dense_tensor_ok(a) ? 1 : 0;
 }
 
 extern "C" int rfx_fused_attention(const RfxAttentionArgs* a) {

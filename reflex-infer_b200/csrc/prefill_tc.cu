@@ -67,6 +67,9 @@ struct PrefillParams {
     int head_major_rows;                       // 0: row = t*G + g (paged Q [N,Hq,D]); 1: row = g*T + t (dense [B,H,S,D])
     int causal;
     float scale_log2;
+    // dense only: additive mask [B, Hq, Sq, Sk] in the tensors' type (nullptr: none); 1 / sm_scale
+    const void* mask;
+    float inv_scale;
 };
 
 struct PfSmem {
@@ -83,7 +86,7 @@ struct PfSmem {
 enum PfBar { PF_QFULL = 0, PF_KFULL = 1, PF_KEMPTY = 3, PF_VFULL = 5, PF_VEMPTY = 7, PF_SFULL = 9, PF_PFULL = 11,
              PF_PVDONE = 13 };
 
-template <typename T>
+template <typename T, bool MASK>
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                   const __grid_constant__ CUtensorMap vmap, const PrefillParams P) {
@@ -348,6 +351,29 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 #pragma unroll
             for (int c = 0; c < 4; ++c) ptx::tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
             ptx::tmem_wait_ld();
+            if (MASK) {
+                // score * scale + mask = (score + mask / scale) * scale: the mask joins the raw scores, so
+                // the rest of the tile's softmax is the unmasked code. One row of the mask per thread.
+                if (row_live) {
+                    const T* mrow = static_cast<const T*>(P.mask) +
+                                    (((int64_t)b * P.Hq + hkv * P.G + g) * P.Sq + tok) * (int64_t)P.Sk + key0;
+                    const int nk = min(kPfKeys, P.Sk - key0);
+                    if (nk == kPfKeys && (reinterpret_cast<uintptr_t>(mrow) & 15) == 0) {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            const uint4 w = reinterpret_cast<const uint4*>(mrow)[c];
+                            const T* e = reinterpret_cast<const T*>(&w);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                v[c * 8 + i] = __float_as_uint(fmaf(Num<T>::to_f(e[i]), P.inv_scale, __uint_as_float(v[c * 8 + i])));
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 128; ++i)  // fully unrolled: v[] has to stay in registers
+                            if (i < nk) v[i] = __float_as_uint(fmaf(Num<T>::to_f(mrow[i]), P.inv_scale, __uint_as_float(v[i])));
+                    }
+                }
+            }
             if (need_mask) {
 #pragma unroll
                 for (int i = 0; i < 128; ++i)
@@ -501,10 +527,10 @@ done:
 // ---- host side -------------------------------------------------------------------------
 namespace rfx {
 
-template <typename T>
+template <typename T, bool MASK = false>
 static int launch_prefill_t(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm,
                             const PrefillParams& P, int grid, cudaStream_t stream) {
-    auto kern = prefill_tc_kernel<T>;
+    auto kern = prefill_tc_kernel<T, MASK>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -521,18 +547,25 @@ static bool kv_box_ok(int64_t bs) { return bs >= 8 && ((bs <= 128 && 128 % bs ==
 
 // Dense fused_attention on tensor cores: q [B,H,Sq,D], k/v [B,Hkv,Sk,D]. Returns
 // RFX_NOT_IMPLEMENTED for shapes the kernel does not cover (the caller then runs the scalar kernel).
-int launch_dense_tensor(const RfxAttentionArgs* a) {
-    if (getenv("REFLEX_B200_NO_TC")) return RFX_NOT_IMPLEMENTED;
-    if (a->dtype != RFX_BF16 && a->dtype != RFX_F16) return RFX_NOT_IMPLEMENTED;
-    if (a->head_dim != kPfHD || a->attn_mask) return RFX_NOT_IMPLEMENTED;
+bool dense_tensor_ok(const RfxAttentionArgs* a) {
+    if (getenv("REFLEX_B200_NO_TC")) return false;
+    if (a->dtype != RFX_BF16 && a->dtype != RFX_F16) return false;
+    if (a->head_dim != kPfHD) return false;
+    if (a->attn_mask && !(a->sm_scale > 0.f)) return false;  // the mask is folded in as mask / scale
     const int G = (int)(a->num_q_heads / a->num_kv_heads);
-    if (G > 128 || a->seq_k == 0) return RFX_NOT_IMPLEMENTED;
-    if (a->seq_q * G < 32) return RFX_NOT_IMPLEMENTED;                 // decode-like: not worth a 128-row tile
-    if (a->is_causal && a->seq_q != a->seq_k) return RFX_NOT_IMPLEMENTED;  // top-left causal on non-square
+    if (G > 128 || a->seq_k == 0) return false;
+    if (a->seq_q * G < 32) return false;                 // decode-like: not worth a 128-row tile
+    if (a->is_causal && a->seq_q != a->seq_k) return false;  // top-left causal on non-square
     if (((uintptr_t)a->q % 16) || ((uintptr_t)a->k % 16) || ((uintptr_t)a->v % 16) || ((uintptr_t)a->out % 16))
-        return RFX_NOT_IMPLEMENTED;
+        return false;
     if (a->batch * a->num_kv_heads * a->seq_k >= (1ll << 31) || a->batch * a->num_q_heads >= (1ll << 31))
-        return RFX_NOT_IMPLEMENTED;
+        return false;
+    return true;
+}
+
+int launch_dense_tensor(const RfxAttentionArgs* a) {
+    if (!dense_tensor_ok(a)) return RFX_NOT_IMPLEMENTED;
+    const int G = (int)(a->num_q_heads / a->num_kv_heads);
     const int T = 128 / G;
     CUtensorMap qm, km, vm;
     {
@@ -560,6 +593,13 @@ int launch_dense_tensor(const RfxAttentionArgs* a) {
     P.scale_log2 = a->sm_scale * 1.4426950408889634f;
     const int64_t grid = (int64_t)P.n_qtiles * P.B * P.Hkv;
     if (grid >= (1ll << 31)) return RFX_NOT_IMPLEMENTED;
+    if (a->attn_mask) {
+        P.mask = a->attn_mask;
+        P.inv_scale = 1.0f / a->sm_scale;
+        if (a->dtype == RFX_BF16)
+            return launch_prefill_t<__nv_bfloat16, true>(qm, km, vm, P, (int)grid, as_stream(a->stream));
+        return launch_prefill_t<__half, true>(qm, km, vm, P, (int)grid, as_stream(a->stream));
+    }
     if (a->dtype == RFX_BF16) return launch_prefill_t<__nv_bfloat16>(qm, km, vm, P, (int)grid, as_stream(a->stream));
     return launch_prefill_t<__half>(qm, km, vm, P, (int)grid, as_stream(a->stream));
 }

@@ -171,6 +171,7 @@ EXPORTS = {
     "rfx_paged_attention_partials": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_paged_attention_combine": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_paged_attention_kernel_kind": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
+    "rfx_fused_attention_kernel_kind": (C.c_int, [C.POINTER(AttentionArgs)]),
     "rfx_paged_attention_static_capacity": (C.c_size_t, []),
     "rfx_paged_attention_static": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_splitk_combine": (C.c_int, [C.POINTER(CombineArgs)]),

@@ -16,6 +16,7 @@ Paged (additive; none of them changes the functions above):
 """
 from __future__ import annotations
 
+import ctypes as C
 import math
 from typing import Optional
 
@@ -87,8 +88,14 @@ def fused_attention(
         sm_scale=float(sm_scale), is_causal=int(bool(is_causal)), dtype=N.dtype_code(q),
         workspace=None, workspace_bytes=0, stream=N.stream_handle(dev),
     )
+    global last_dense_kernel_kind
+    last_dense_kernel_kind = int(N.lib().rfx_fused_attention_kernel_kind(C.byref(a)))
     N.call("rfx_fused_attention", a, dev)
     return out
+
+
+#: Which kernel the last ``fused_attention`` call selected: 1 = tcgen05 kernel, 0 = scalar kernel.
+last_dense_kernel_kind = -1
 
 
 # ---------------------------------------------------------------------------- paged ----

@@ -7,6 +7,7 @@ import pytest
 import torch
 
 import golden_io
+import kernels.attention
 import oracle
 import workloads
 from kernels.attention import PagedAttentionCall, PagedWorkspace, fused_attention, paged_attention, rope_append
@@ -32,6 +33,39 @@ def test_dense_prefill_vs_naive(B, H, Hkv, S, causal, dtype, native):
     torch.testing.assert_close(o.cpu().double(), ref, atol=tol, rtol=tol)
     # and against the reference's own path (SDPA after GQA expansion) at its tolerance
     torch.testing.assert_close(o.cpu().float(), oracle.attention(q, k, v, is_causal=causal).float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("B,H,Hkv,Sq,Sk,causal,dtype", [
+    (2, 8, 2, 256, 256, False, torch.bfloat16),   # aligned rows of the mask: 16-byte loads
+    (1, 8, 2, 300, 300, True, torch.bfloat16),    # ragged last tile, mask and causal together
+    (1, 4, 4, 128, 517, False, torch.float16),    # odd key count: element loads
+    (1, 32, 8, 70, 200, False, torch.bfloat16)])
+def test_dense_additive_mask_on_tensor_core_kernel(B, H, Hkv, Sq, Sk, causal, dtype, native, monkeypatch):
+    """`attn_mask` [B, H, S_q, S_k] added to the scaled scores (reference triton_fused_attention.py:190-202)
+    on the tcgen05 kernel: a smooth bias, a band of -inf entries, and a boolean mask; cross-checked
+    against the scalar kernel."""
+    q = golden_io.pattern((B, H, Sq, 128), dtype, 11, scale=0.5)
+    k = golden_io.pattern((B, Hkv, Sk, 128), dtype, 12, scale=0.5)
+    v = golden_io.pattern((B, Hkv, Sk, 128), dtype, 13)
+    bias = golden_io.pattern((B, H, Sq, Sk), dtype, 14, scale=2.0)
+    far = (torch.arange(Sk).view(1, -1) - torch.arange(Sq).view(-1, 1)).abs() > 96   # keep a band around the diagonal
+    far[:, 0] = False                                                                 # every row keeps a key
+    bias = bias.masked_fill(far.view(1, 1, Sq, Sk), float("-inf"))
+    tol = 2e-2 if dtype == torch.bfloat16 else 5e-3
+    full = bias.double() + (_causal(Sq) if causal else 0.0)
+    ref = oracle.naive_attention_f64(q, k, v, mask=full)
+    o = fused_attention(q.to(DEV), k.to(DEV), v.to(DEV), attn_mask=bias.to(DEV), is_causal=causal)
+    assert kernels.attention.last_dense_kernel_kind == 1
+    torch.testing.assert_close(o.cpu().double(), ref, atol=tol, rtol=tol)
+    keep = ~far.view(1, 1, Sq, Sk).expand(B, H, Sq, Sk)
+    ob = fused_attention(q.to(DEV), k.to(DEV), v.to(DEV), attn_mask=keep.to(DEV), is_causal=causal)
+    refb = oracle.naive_attention_f64(q, k, v, mask=torch.zeros(Sq, Sk).masked_fill(far, float("-inf")).double()
+                                      + (_causal(Sq) if causal else 0.0))
+    torch.testing.assert_close(ob.cpu().double(), refb, atol=tol, rtol=tol)
+    monkeypatch.setenv("REFLEX_B200_NO_TC", "1")
+    os_ = fused_attention(q.to(DEV), k.to(DEV), v.to(DEV), attn_mask=bias.to(DEV), is_causal=causal)
+    assert kernels.attention.last_dense_kernel_kind == 0
+    torch.testing.assert_close(o.float(), os_.float(), atol=tol, rtol=tol)
 
 
 def test_dense_prefill_matches_scalar_kernel(native, monkeypatch):
