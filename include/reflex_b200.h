@@ -239,7 +239,9 @@ typedef struct {
     const int32_t* rope_positions; /* [N_q] */
     int64_t n_q, batch, num_q_heads, num_kv_heads, head_dim;
     int64_t num_blocks, block_size, max_blocks, bt_stride_b, table_rows;
-    int64_t max_q_len;           /* host upper bound of any request's query rows (1 for decode) */
+    int64_t max_q_len;           /* host upper bound of any request's query rows (1 for decode); sizes the
+                                  * workspace and the grid. The device checks q_start against it and
+                                  * against n_q: on a mismatch nothing is computed and status bit 2 is set */
     float sm_scale;
     int is_causal;               /* bottom-right; irrelevant when every request has one row */
     int rope_interleaved;
@@ -306,8 +308,10 @@ typedef struct {
 int rfx_splitk_combine(const RfxCombineArgs* a);
 
 /* Reads the device status word a paged-attention launch leaves in its workspace
- * (0 = ok; bit 0 = a bounded wait expired; bit 1 = a page index outside the pool was
- * skipped). Synchronises the stream; meant for tests and debugging. */
+ * (0 = ok; bit 0 = a bounded wait expired; bit 1 = a page index outside the pool: its keys
+ * were left out; bit 2 = q_start disagrees with max_q_len or n_q: nothing was computed).
+ * `workspace` NULL reads the word of rfx_paged_attention_static's built-in array on the
+ * current device. Synchronises the stream; poll it after a step whose inputs are not trusted. */
 int rfx_paged_attention_status(const void* workspace, rfx_stream stream, int* status_word_host);
 
 /* ---- head-sharded output gather fused into the combine (no counterpart in the reference,

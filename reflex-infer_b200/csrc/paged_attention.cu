@@ -1,5 +1,7 @@
 // Entry points of paged attention: argument checks, workspace layout, and the three
 // launches of a step (plan, split-K partials, combine).
+#include <atomic>
+
 #include "paged_plan.cuh"
 
 namespace rfx {
@@ -155,8 +157,26 @@ extern "C" int rfx_paged_attention_gather(const RfxPagedAttentionArgs* a, const 
 namespace rfx {
 constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
-// Device address of the array per device ordinal, resolved on the first call on that device.
-static void* g_static_scratch_ptr[64] = {};
+// Device address of the array per device ordinal, resolved on the first call on that device. Two
+// host threads may both resolve it; they store the same value.
+static std::atomic<void*> g_static_scratch_ptr[64];
+
+// In host code the array's name is only a handle; a kernel needs its device address.
+static int static_scratch(const char* name, void** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "%s: cudaGetDevice: %s", name, cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) return fail(RFX_UNSUPPORTED_DEVICE, "%s: device ordinal %d out of range", name, dev);
+    void* p = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (!p) {
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p)
+            return fail(RFX_CUDA_ERROR, "%s: cudaGetSymbolAddress: %s", name, cudaGetErrorString(e));
+        g_static_scratch_ptr[dev].store(p, std::memory_order_release);
+    }
+    *out = p;
+    return RFX_SUCCESS;
+}
 }  // namespace rfx
 
 extern "C" size_t rfx_paged_attention_static_capacity(void) { return rfx::kStaticScratchBytes; }
@@ -174,20 +194,11 @@ extern "C" int rfx_paged_attention_static(const RfxPagedAttentionArgs* a) {
                     "%s: this problem needs %zu B of scratch, the built-in array holds %zu B; use "
                     "rfx_paged_attention with a caller workspace",
                     name, L.total, kStaticScratchBytes);
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "%s: cudaGetDevice: %s", name, cudaGetErrorString(e));
-    if (dev < 0 || dev >= 64) return fail(RFX_UNSUPPORTED_DEVICE, "%s: device ordinal %d out of range", name, dev);
-    if (!g_static_scratch_ptr[dev]) {
-        // In host code the array's name is only a handle; a kernel needs its device address.
-        void* p = nullptr;
-        e = cudaGetSymbolAddress(&p, g_static_scratch);
-        if (e != cudaSuccess || !p)
-            return fail(RFX_CUDA_ERROR, "%s: cudaGetSymbolAddress: %s", name, cudaGetErrorString(e));
-        g_static_scratch_ptr[dev] = p;
-    }
+    void* scratch = nullptr;
+    st = static_scratch(name, &scratch);
+    if (st != RFX_SUCCESS) return st;
     RfxPagedAttentionArgs b = *a;
-    b.workspace = g_static_scratch_ptr[dev];
+    b.workspace = scratch;
     b.workspace_bytes = kStaticScratchBytes;
     b.reuse_plan = 0;  // the array is shared by every caller: always plan afresh
     return run_stages(&b, name, kStagePlan | kStagePartials | kStageCombine);
@@ -195,7 +206,13 @@ extern "C" int rfx_paged_attention_static(const RfxPagedAttentionArgs* a) {
 
 extern "C" int rfx_paged_attention_status(const void* workspace, rfx_stream stream, int* status_word_host) {
     using namespace rfx;
-    if (!workspace || !status_word_host) return fail(RFX_INVALID_ARGUMENT, "rfx_paged_attention_status: null pointer");
+    if (!status_word_host) return fail(RFX_INVALID_ARGUMENT, "rfx_paged_attention_status: null pointer");
+    if (!workspace) {  // the built-in array of rfx_paged_attention_static on the current device
+        void* p = nullptr;
+        int st = static_scratch("rfx_paged_attention_status", &p);
+        if (st != RFX_SUCCESS) return st;
+        workspace = p;
+    }
     int32_t w = 0;
     cudaError_t e = cudaMemcpyAsync(&w, (const int32_t*)workspace + HdrStatus, sizeof(w), cudaMemcpyDeviceToHost,
                                     as_stream(stream));

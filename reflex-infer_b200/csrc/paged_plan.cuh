@@ -34,6 +34,7 @@ enum : int {
 
 constexpr int kStatusWaitExpired = 1;
 constexpr int kStatusBadPage = 2;
+constexpr int kStatusCapacity = 4;   // the device-side row counts exceed what the host sized the workspace for
 constexpr int kPlanTile = 64;  // keys per tile of the stream
 
 struct PlanLayout {

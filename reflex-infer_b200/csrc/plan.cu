@@ -36,7 +36,8 @@ __device__ inline void block_exscan2(long long& a, long long& b, long long (*red
 
 __global__ void __launch_bounds__(kPlanThreads)
 plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_start, int B, int Hkv,
-            int G, long long max_parts, long long target_chunk, int parts_hint, int32_t* hdr,
+            int G, long long max_parts, long long target_chunk, int parts_hint, long long max_items,
+            long long cap_rows, long long max_q_len, long long n_q, int32_t* hdr,
             int32_t* pair_item_begin, int32_t* part_first, int4* items, int32_t* item_prow) {
     __shared__ long long red[kPlanThreads / 32][2];
     ptx::pdl_trigger();  // the partial kernel may set itself up while the plan is computed
@@ -86,6 +87,31 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
     }
     block_exscan2(item_pre, row_pre, red, n_items, n_rows);
 
+    // The workspace was sized on the host from max_q_len and n_q; the row counts used here come
+    // from q_start on the device. If they do not agree (a request with more rows than max_q_len,
+    // q_start[B] - q_start[0] != n_q, more partial rows or items than the workspace holds), nothing
+    // may be written past the capacity: the plan is left empty -- no items, no runs, every pair
+    // without splits, so the partial kernels do nothing and the combine writes zeros -- and
+    // kStatusCapacity is raised in the status word.
+    int over = 0;
+    for (int b = b0; b < b1; ++b) over |= nq_of(b) > max_q_len ? 1 : 0;
+    if (tid == 0 && q_start) over |= ((long long)q_start[B] - q_start[0] != n_q) ? 1 : 0;
+    over |= (n_items > max_items || n_rows > cap_rows) ? 1 : 0;
+    if (__syncthreads_or(over)) {
+        for (long long i = tid; i <= (long long)B * Hkv; i += kPlanThreads) pair_item_begin[i] = 0;
+        if (tid == 0) {
+            part_first[0] = 0;
+            item_prow[0] = 0;
+            hdr[HdrNumItems] = 0;
+            hdr[HdrTilesPerPart] = 1;
+            hdr[HdrNumParts] = 0;
+            hdr[HdrStatus] = kStatusCapacity;
+            hdr[HdrTotalRows] = 0;
+        }
+        ptx::pdl_wait();
+        return;
+    }
+
     long long pre = tile_pre, it = item_pre, rw = row_pre;
     for (int b = b0; b < b1; ++b) {
         const int c = ctx_of(b);
@@ -126,8 +152,9 @@ int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanP
     const int G = (int)(a->num_q_heads / a->num_kv_heads);
     cudaError_t e = launch_pdl(plan_kernel, dim3(1), dim3(kPlanThreads), 0, as_stream(a->stream), a->context_lens,
                                a->q_start, (int)a->batch, (int)a->num_kv_heads, G, (long long)L.max_parts,
-                               (long long)a->target_chunk, parts_hint, P.hdr, P.pair_item_begin, P.part_first, P.items,
-                               P.item_prow);
+                               (long long)a->target_chunk, parts_hint, (long long)L.max_items, (long long)L.cap_rows,
+                               (long long)(a->max_q_len < 1 ? 1 : a->max_q_len), (long long)a->n_q, P.hdr,
+                               P.pair_item_begin, P.part_first, P.items, P.item_prow);
     if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "rfx_paged_attention_plan: %s", cudaGetErrorString(e));
     return check_launch("rfx_paged_attention_plan");
 }

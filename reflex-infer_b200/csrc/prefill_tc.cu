@@ -9,8 +9,9 @@
 //              (no shuffles), writes P as bf16 back into the TMEM columns S occupied, and
 //              rescales O in TMEM only when a row maximum grew by more than 2^8 (a stale
 //              maximum is exact as long as the final 1/l uses the same reference).
-//   warp 8     TMA producer: both Q tiles once, then K and V tiles of 128 keys, one box per
-//              page (or one per tile for dense K/V), two stages each, 128-byte swizzle.
+//   warp 8     TMA producer: both Q tiles once, then K and V tiles of 128 keys, two stages each,
+//              128-byte swizzle; one box per page, holding both 64-wide halves (one per tile for
+//              dense K/V and for pages of 128 keys or more).
 //   warp 9     MMA issuer: S_x = Q_x.K_j^T (8 x tcgen05.mma 128x128x16 from shared-memory
 //              descriptors), O_x += P_x.V_j with P read from TMEM and V as an MN-major
 //              shared-memory operand, in the fixed order [P_a.V, S_a'] [P_b.V, S_b'] ...: the two
@@ -22,6 +23,12 @@
 //              K_{j+1} have landed.
 //              Completion through tcgen05.commit on mbarriers.
 // TMEM: columns [0,128) S_a/P_a, [128,256) S_b/P_b, [256,384) O_a, [384,512) O_b (fp32).
+//
+// Shared-memory form of a K/V tile. Paged: [group of 8 keys][64-wide half][8 keys][128 B], i.e.
+// 2 KiB per 8 keys, which is what one TMA box {64 elems, 8 keys, 2 halves, page/8 groups} of a
+// 4-D view of the pool writes; the MMA descriptors walk it with 2 KiB between 8-key groups and
+// 1 KiB between the halves. Dense: [half][128 keys][128 B] (1 KiB between groups, 16 KiB between
+// halves). Both are 128-byte swizzled in 1 KiB atoms.
 //
 // Causal masking is bottom-right aligned: token t of n sees keys 0..ctx-n+t; K tiles wholly
 // above the diagonal are never loaded. Tensor-pipe bound: 4*rows*keys*D FLOPs per tile pair.
@@ -62,7 +69,9 @@ struct PrefillParams {
     int64_t bt_sb, max_blocks, num_blocks;
     int B, Hq, Hkv, G, T;                      // T = query tokens per tile = 128 / G
     int Sq, Sk;                                // dense sizes (paged: Sq = host bound on rows per request)
-    int block_size, box_rows, boxes_per_tile;  // K/V boxes: rows per TMA box, boxes per 128-key tile
+    int block_size;
+    int box_keys, box_shift, boxes_per_tile;   // keys per TMA box (a power of two), boxes per 128-key tile
+    uint32_t kv_sbo, kv_half;                  // bytes between 8-key groups / between the 64-wide halves of a tile
     int n_qtiles;                              // CTAs per (request, kv head) = ceil(Sq / 2T)
     int head_major_rows;                       // 0: row = t*G + g (paged Q [N,Hq,D]); 1: row = g*T + t (dense [B,H,S,D])
     int causal;
@@ -80,7 +89,7 @@ struct PfSmem {
     // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2]
     static constexpr int n_bars = 1 + 4 * kPfKvStages + 6;
     static constexpr size_t off_misc = off_bars + 8 * n_bars;
-    static constexpr size_t total = off_misc + 64 + 1024;
+    static constexpr size_t total = off_misc + 64 + 1024;  // misc: TMEM base, abort flag, 4 bad-box masks
 };
 
 enum PfBar { PF_QFULL = 0, PF_KFULL = 1, PF_KEMPTY = 3, PF_VFULL = 5, PF_VEMPTY = 7, PF_SFULL = 9, PF_PFULL = 11,
@@ -98,6 +107,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     unsigned char* sV = smem + PfSmem::off_v;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PfSmem::off_bars);
     uint32_t* misc = reinterpret_cast<uint32_t*>(smem + PfSmem::off_misc);  // [0] TMEM base, [1] abort flag
+    volatile uint32_t* sbad = misc + 4;  // [4] boxes of K tile j (slot j % 4) that could not be loaded: bad page index
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -120,6 +130,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     const int n_q = P.q_start ? (P.q_start[b + 1] - q0) : P.Sq;
     const int ctx = P.ctx_lens ? max(0, P.ctx_lens[b]) : P.Sk;
     const int tok0 = qt * 2 * P.T;                  // tile a: tok0.., tile b: tok0 + T..
+    // Whole rows per CTA: the grid was sized from the host's bound on the rows of a request; rows
+    // beyond it would silently keep stale output, so say so in the status word. (Split batches are
+    // checked by the plan kernel.)
+    if (!P.items && threadIdx.x == 0 && P.status && qt == P.n_qtiles - 1 && n_q > P.n_qtiles * 2 * P.T)
+        atomicOr(P.status, kStatusCapacity);
     if (tok0 >= n_q || (P.skip_single && n_q == 1)) return;  // uniform over the CTA; nothing allocated yet
     const int off = ctx - n_q;                      // bottom-right: token t sees keys <= t + off
     const int last_tok = min(n_q, tok0 + 2 * P.T) - 1;
@@ -159,6 +174,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         return false;
     };
 
+    // byte offset of key row r (0..127), 16-byte chunk c (0..15) inside a K/V tile (before swizzling,
+    // which only permutes the eight chunks of one 128-byte line)
+    auto kv_row_off = [&](int r, int c) -> uint32_t {
+        return (uint32_t)(r >> 3) * P.kv_sbo + (uint32_t)(c >> 3) * P.kv_half + (uint32_t)(r & 7) * 128u +
+               (uint32_t)(c & 7) * 16u;
+    };
+
     if (warp == 8) {
         // ------------------------------------------------------------------ TMA producer --
         if (lane == 0) {
@@ -176,62 +198,87 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                         ptx::tma_load_3d(dst, &qmap, &bars[PF_QFULL], h * 64, hkv * P.G, q0 + tok0 + x * P.T);
                 }
         }
-        const int R = P.box_rows;
+        const int R = P.box_keys;
         // The producer's vote on P_i ready (both tiles): V_i and K_{i+1} have landed. A barrier
         // poll costs a few hundred cycles while the tensor core streams operands from shared
         // memory, so it is kept out of the issuer's and the softmax warps' loops; this warp has
-        // the time.
+        // the time. Keys at or past kv_end carry probability zero but their V rows may hold NaN
+        // patterns: cleared here, before the vote.
         auto landed = [&](int i) -> bool {
             int ok = 1;
             if (lane == 0) {
                 ok = wait_phase(PF_VFULL + i % kPfKvStages, (uint32_t)((i / kPfKvStages) & 1)) ? 1 : 0;
                 if (ok && i + 1 < n_kv)
                     ok = wait_phase(PF_KFULL + (i + 1) % kPfKvStages, (uint32_t)(((i + 1) / kPfKvStages) & 1)) ? 1 : 0;
-                if (ok) {
-                    ptx::mbar_arrive(&bars[PF_PFULL + 0]);
-                    if (n_tiles == 2) ptx::mbar_arrive(&bars[PF_PFULL + 1]);
-                } else {
-                    give_up();
-                }
+                if (!ok) give_up();
             }
-            return __shfl_sync(0xffffffffu, ok, 0) != 0;
+            if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
+            const int valid = kv_end - (kb + i * kPfKeys);
+            if (valid < kPfKeys) {
+                unsigned char* vt = sV + (size_t)(i % kPfKvStages) * kPfTileBytes;
+                for (int i2 = lane; i2 < (kPfKeys - valid) * 16; i2 += 32)
+                    *reinterpret_cast<uint4*>(vt + kv_row_off(valid + (i2 >> 4), i2 & 15)) = make_uint4(0, 0, 0, 0);
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+            }
+            if (lane == 0) {
+                ptx::mbar_arrive(&bars[PF_PFULL + 0]);
+                if (n_tiles == 2) ptx::mbar_arrive(&bars[PF_PFULL + 1]);
+            }
+            return true;
         };
         for (int j = 0; j < n_kv; ++j) {
             const int st = j % kPfKvStages;
             const uint32_t par = (uint32_t)((j / kPfKvStages) & 1);
             const int key0 = kb + j * kPfKeys;
-            // rows of this tile's boxes: lane i owns box i
-            int row = -1;
+            // lane i owns box i of the tile: its coordinates in the 4-D view
+            int c1 = 0, c3 = -1;
+            bool bad = false;
             if (lane < P.boxes_per_tile) {
                 const int key = key0 + lane * R;
                 if (key < kv_end) {
                     if (P.block_table) {
                         const int64_t lb = key / P.block_size;
-                        int64_t page = lb < P.max_blocks ? P.block_table[(int64_t)b * P.bt_sb + lb] : -1;
+                        const int64_t page = lb < P.max_blocks ? P.block_table[(int64_t)b * P.bt_sb + lb] : -1;
                         if (page >= 0 && page < P.num_blocks)
-                            row = (int)((page * P.Hkv + hkv) * P.block_size + (key - lb * P.block_size));
-                        else if (P.status) atomicOr(P.status, 2);
+                            c3 = (int)(((page * P.Hkv + hkv) * P.block_size + (key - lb * P.block_size)) >> 3);
+                        else
+                            bad = true;
                     } else {
-                        row = (b * P.Hkv + hkv) * P.Sk + key;
+                        c1 = key;
+                        c3 = b * P.Hkv + hkv;
                     }
                 }
             }
-            const unsigned have = __ballot_sync(0xffffffffu, row >= 0);
-            const uint32_t tx = (uint32_t)__popc(have) * (uint32_t)R * 128u * 2u;
+            const unsigned have = __ballot_sync(0xffffffffu, c3 >= 0);
+            const unsigned badm = __ballot_sync(0xffffffffu, bad);
+            const uint32_t tx = (uint32_t)__popc(have) * (uint32_t)R * 256u;
+            if (badm && lane == 0 && P.status) atomicOr(P.status, kStatusBadPage);
             for (int which = 0; which < 2; ++which) {  // 0: K, 1: V
                 uint64_t* fullb = &bars[(which ? PF_VFULL : PF_KFULL) + st];
+                unsigned char* tile = (which ? sV : sK) + (size_t)st * kPfTileBytes;
                 int ok = 1;
                 if (lane == 0) ok = wait_phase((which ? PF_VEMPTY : PF_KEMPTY) + st, par ^ 1u) ? 1 : 0;
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) { if (lane == 0) give_up(); goto done; }
-                if (lane == 0) ptx::mbar_arrive_expect_tx(fullb, tx);
-                __syncwarp();
-                if (row >= 0) {
-                    unsigned char* dst = (which ? sV : sK) + (size_t)st * kPfTileBytes + (size_t)lane * R * 128;
-                    const CUtensorMap* m = which ? &vmap : &kmap;
-                    ptx::tma_load_2d(dst, m, fullb, 0, row);
-                    ptx::tma_load_2d(dst + kPfHalfBytes, m, fullb, 64, row);
+                if (badm) {
+                    // a page index outside the pool: its keys are masked by the softmax warps (sbad) and
+                    // its rows are cleared here, so that they count as absent, as in the scalar kernel
+                    for (int i2 = lane; i2 < kPfKeys * 16; i2 += 32) {
+                        const int r = i2 >> 4;
+                        if ((badm >> (r >> P.box_shift)) & 1u)
+                            *reinterpret_cast<uint4*>(tile + kv_row_off(r, i2 & 15)) = make_uint4(0, 0, 0, 0);
+                    }
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
                 }
+                if (lane == 0) {
+                    if (!which) sbad[j & 3] = badm;  // a slot is reused only after the softmax of tile j + 1
+                    ptx::mbar_arrive_expect_tx(fullb, tx);
+                }
+                __syncwarp();
+                if (c3 >= 0)
+                    ptx::tma_load_4d(tile + (size_t)lane * R * 256, which ? &vmap : &kmap, fullb, 0, c1, 0, c3);
             }
             if (j > 0 && !landed(j - 1)) goto done;
         }
@@ -259,15 +306,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             if (lane == 0) ok = wait_phase(bar, parity) ? 1 : 0;
             return __shfl_sync(0xffffffffu, ok, 0) != 0;
         };
+        // descriptor halves: a byte offset inside a tile is a 32-bit add on the low word
+        const uint32_t hi_q = ptx::umma_desc_hi(1024), hi_kv = ptx::umma_desc_hi(P.kv_sbo);
+        const uint32_t q_lo0 = ptx::umma_desc_lo(q_addr, 16);
+        const uint32_t k_lo0 = ptx::umma_desc_lo(ptx::smem_u32(sK), 16);
+        const uint32_t v_lo0 = ptx::umma_desc_lo(ptx::smem_u32(sV), P.kv_half);
+        const uint32_t half16 = P.kv_half >> 4, vstep = P.kv_sbo >> 3;  // 16 keys of V = two 8-key groups
         auto issue_s = [&](int x, int jj) {  // S_x = Q_x . K_jj^T
             if (lane == 0) {
-                const uint32_t k_addr = ptx::smem_u32(sK + (size_t)(jj % kPfKvStages) * kPfTileBytes);
+                const uint32_t qlo = q_lo0 + (uint32_t)x * (kPfTileBytes >> 4);
+                const uint32_t klo = k_lo0 + (uint32_t)(jj % kPfKvStages) * (kPfTileBytes >> 4);
+                const uint32_t klo1 = klo + half16;
 #pragma unroll
-                for (int ks = 0; ks < kPfHD / 16; ++ks) {
-                    const uint32_t o2 = (uint32_t)(ks >> 2) * kPfHalfBytes + (uint32_t)(ks & 3) * 32u;
-                    ptx::umma_ss(tmem + x * 128, ptx::umma_desc_sw128(q_addr + x * kPfTileBytes + o2, 16, 1024),
-                                 ptx::umma_desc_sw128(k_addr + o2, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
-                }
+                for (int ks = 0; ks < kPfHD / 16; ++ks)
+                    ptx::umma_ss_lh(tmem + x * 128, qlo + (uint32_t)((ks >> 2) * (kPfHalfBytes >> 4) + (ks & 3) * 2), hi_q,
+                                    ((ks >> 2) ? klo1 : klo) + (uint32_t)((ks & 3) * 2), hi_kv, idesc_s, ks > 0 ? 1u : 0u);
                 ptx::umma_commit(&bars[PF_SFULL + x]);
                 if (x == n_tiles - 1) ptx::umma_commit(&bars[PF_KEMPTY + jj % kPfKvStages]);
             }
@@ -283,28 +336,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             const int st = j % kPfKvStages;
             // No waits for V_j and K_{j+1} here: the producer warp adds its vote to P_j ready only
             // when both have landed.
-            const int valid = kv_end - (kb + j * kPfKeys);
             for (int x = 0; x < n_tiles; ++x) {
                 if (!wait_bar(PF_PFULL + x, (uint32_t)(j & 1))) { if (lane == 0) give_up(); goto done; }
-                if (x == 0 && valid < kPfKeys) {
-                    // keys at or past kv_end carry probability zero but may hold NaN patterns: clear those V rows
-                    unsigned char* vt = sV + (size_t)st * kPfTileBytes;
-                    for (int i = lane; i < (kPfKeys - valid) * 16; i += 32) {
-                        const int r = valid + i / 16, c = i % 16;
-                        *reinterpret_cast<uint4*>(vt + (size_t)(c >> 3) * kPfHalfBytes + (size_t)r * 128 +
-                                                  (size_t)(c & 7) * 16) = make_uint4(0, 0, 0, 0);
-                    }
-                    ptx::fence_proxy_async_smem();
-                    __syncwarp();
-                }
                 ptx::tc_fence_after_sync();
                 if (lane == 0) {
-                    const uint32_t v_addr = ptx::smem_u32(sV + (size_t)st * kPfTileBytes);
+                    const uint32_t vlo = v_lo0 + (uint32_t)st * (kPfTileBytes >> 4);
+                    const uint32_t pa = tmem + x * 128, od = tmem + 256 + x * 128;
 #pragma unroll
-                    for (int ks = 0; ks < kPfKeys / 16; ++ks) {
-                        const uint64_t bd = ptx::umma_desc_sw128(v_addr + ks * 2048, kPfHalfBytes, 1024);
-                        ptx::umma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-                    }
+                    for (int ks = 0; ks < kPfKeys / 16; ++ks)
+                        ptx::umma_ts_lh(od, pa + ks * 8, vlo + (uint32_t)ks * vstep, hi_kv, idesc_o,
+                                        (j > 0 || ks > 0) ? 1u : 0u);
                     ptx::umma_commit(&bars[PF_PVDONE + x]);
                     if (x == n_tiles - 1) ptx::umma_commit(&bars[PF_VEMPTY + st]);
                 }
@@ -350,6 +391,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             uint32_t v[128];
 #pragma unroll
             for (int c = 0; c < 4; ++c) ptx::tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+            const uint32_t badk = sbad[j & 3];  // almost always 0
             ptx::tmem_wait_ld();
             if (MASK) {
                 // score * scale + mask = (score + mask / scale) * scale: the mask joins the raw scores, so
@@ -379,17 +421,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 for (int i = 0; i < 128; ++i)
                     if (key0 + i > last_key) v[i] = 0xff800000u;  // -inf
             }
-            // row maximum over eight independent chains (a single chain is 128 dependent steps)
-            float m8[8];
+            if (badk) {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) m8[k] = __uint_as_float(v[k]);
+                for (int i = 0; i < 128; ++i)
+                    if ((badk >> (i >> P.box_shift)) & 1u) v[i] = 0xff800000u;
+            }
+            // row maximum over four independent chains of three-input maxima
+            float m4[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) m4[k] = fmaxf(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1]));
 #pragma unroll
             for (int i = 8; i < 128; i += 8) {
 #pragma unroll
-                for (int k = 0; k < 8; ++k) m8[k] = fmaxf(m8[k], __uint_as_float(v[i + k]));
+                for (int k = 0; k < 4; ++k)
+                    m4[k] = ptx::max3(m4[k], __uint_as_float(v[i + 2 * k]), __uint_as_float(v[i + 2 * k + 1]));
             }
-            float mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])),
-                             fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+            float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
             mx *= P.scale_log2;  // scale > 0, so max and scale commute
             const bool grow = row_live && mx > m_run + kPfRescaleTau;  // also true for the first finite maximum
             if (__any_sync(0xffffffffu, grow)) {
@@ -543,7 +590,15 @@ static int launch_prefill_t(const CUtensorMap& qm, const CUtensorMap& km, const 
     return check_launch("prefill_tc_kernel");
 }
 
-static bool kv_box_ok(int64_t bs) { return bs >= 8 && ((bs <= 128 && 128 % bs == 0) || bs % 128 == 0); }
+// Pages the K/V boxes can be cut from: whole groups of 8 keys, and either several pages per 128-key
+// tile or several tiles per page.
+static bool kv_box_ok(int64_t bs) { return bs >= 8 && ((bs <= kPfKeys && kPfKeys % bs == 0) || bs % kPfKeys == 0); }
+
+static int log2_of(int v) {
+    int s = 0;
+    while ((1 << s) < v) ++s;
+    return s;
+}
 
 // Dense fused_attention on tensor cores: q [B,H,Sq,D], k/v [B,Hkv,Sk,D]. Returns
 // RFX_NOT_IMPLEMENTED for shapes the kernel does not cover (the caller then runs the scalar kernel).
@@ -558,8 +613,7 @@ bool dense_tensor_ok(const RfxAttentionArgs* a) {
     if (a->is_causal && a->seq_q != a->seq_k) return false;  // top-left causal on non-square
     if (((uintptr_t)a->q % 16) || ((uintptr_t)a->k % 16) || ((uintptr_t)a->v % 16) || ((uintptr_t)a->out % 16))
         return false;
-    if (a->batch * a->num_kv_heads * a->seq_k >= (1ll << 31) || a->batch * a->num_q_heads >= (1ll << 31))
-        return false;
+    if (a->seq_k >= (1ll << 31) || a->seq_q >= (1ll << 31) || a->batch * a->num_q_heads >= (1ll << 31)) return false;
     return true;
 }
 
@@ -575,11 +629,13 @@ int launch_dense_tensor(const RfxAttentionArgs* a) {
         if (encode_tiled_16bit(&qm, a->q, 3, dims, str, box)) return RFX_NOT_IMPLEMENTED;
     }
     {
-        const uint64_t dims[2] = {(uint64_t)kPfHD, (uint64_t)(a->batch * a->num_kv_heads * a->seq_k)};
-        const uint64_t str[1] = {(uint64_t)kPfHD * 2};
-        const uint32_t box[2] = {64, 128};
-        if (encode_tiled_16bit(&km, a->k, 2, dims, str, box)) return RFX_NOT_IMPLEMENTED;
-        if (encode_tiled_16bit(&vm, a->v, 2, dims, str, box)) return RFX_NOT_IMPLEMENTED;
+        // [half][key][64 elems] per (batch, kv head): one box lands a whole 128-key tile, keys past
+        // seq_k arrive as zeros
+        const uint64_t dims[4] = {64, (uint64_t)a->seq_k, 2, (uint64_t)(a->batch * a->num_kv_heads)};
+        const uint64_t str[3] = {(uint64_t)kPfHD * 2, 128, (uint64_t)a->seq_k * kPfHD * 2};
+        const uint32_t box[4] = {64, (uint32_t)kPfKeys, 2, 1};
+        if (encode_tiled_16bit(&km, a->k, 4, dims, str, box)) return RFX_NOT_IMPLEMENTED;
+        if (encode_tiled_16bit(&vm, a->v, 4, dims, str, box)) return RFX_NOT_IMPLEMENTED;
     }
     PrefillParams P = {};
     P.out = a->out; P.out_tok_stride = kPfHD; P.out_head_stride = a->seq_q * kPfHD;
@@ -587,7 +643,8 @@ int launch_dense_tensor(const RfxAttentionArgs* a) {
     P.status = (a->workspace && a->workspace_bytes >= 4) ? (int32_t*)a->workspace : nullptr;
     P.B = (int)a->batch; P.Hq = (int)a->num_q_heads; P.Hkv = (int)a->num_kv_heads; P.G = G; P.T = T;
     P.Sq = (int)a->seq_q; P.Sk = (int)a->seq_k;
-    P.block_size = (int)a->seq_k; P.box_rows = 128; P.boxes_per_tile = 1;
+    P.block_size = (int)a->seq_k; P.box_keys = kPfKeys; P.box_shift = 7; P.boxes_per_tile = 1;
+    P.kv_sbo = 1024; P.kv_half = kPfKeys * 128;
     P.n_qtiles = (int)((a->seq_q + 2 * T - 1) / (2 * T));
     P.head_major_rows = 1; P.causal = a->is_causal;
     P.scale_log2 = a->sm_scale * 1.4426950408889634f;
@@ -614,7 +671,7 @@ bool prefill_paged_supported(const RfxPagedAttentionArgs* a) {
     if (G > 128 || !kv_box_ok(a->block_size)) return false;
     if (((uintptr_t)a->q % 16) || ((uintptr_t)a->k_cache % 16) || ((uintptr_t)a->v_cache % 16) || ((uintptr_t)a->out % 16))
         return false;
-    if (a->num_blocks * a->num_kv_heads * a->block_size >= (1ll << 31)) return false;
+    if (a->num_blocks * a->num_kv_heads * a->block_size >= (1ll << 34)) return false;  // box coordinate = row / 8
     return true;
 }
 
@@ -647,7 +704,7 @@ int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, c
                          const PlanPtrs* split, bool skip_single_row_requests) {
     const int G = (int)(a->num_q_heads / a->num_kv_heads);
     const int T = 128 / G;
-    const int R = (int)(a->block_size < 128 ? a->block_size : 128);
+    const int R = (int)(a->block_size < kPfKeys ? a->block_size : kPfKeys);  // keys per box
     CUtensorMap qm, km, vm;
     {
         const uint64_t dims[3] = {(uint64_t)kPfHD, (uint64_t)a->num_q_heads, (uint64_t)a->n_q};
@@ -657,11 +714,15 @@ int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, c
         if (r) return fail(RFX_CUDA_ERROR, "cuTensorMapEncodeTiled(q) failed (%d)", r);
     }
     {
-        const uint64_t dims[2] = {(uint64_t)kPfHD, (uint64_t)(a->num_blocks * a->num_kv_heads * a->block_size)};
-        const uint64_t str[1] = {(uint64_t)kPfHD * 2};
-        const uint32_t box[2] = {64, (uint32_t)R};
-        int r1 = encode_tiled_16bit(&km, a->k_cache, 2, dims, str, box);
-        int r2 = encode_tiled_16bit(&vm, a->v_cache, 2, dims, str, box);
+        // The pool's rows (page, kv head, position) in groups of 8: [group][half][row in group][64 elems],
+        // so one box {64, 8, 2, R/8} brings both halves of up to 128 keys of a page and lands them as
+        // 2 KiB per group, halves 1 KiB apart.
+        const uint64_t rows = (uint64_t)(a->num_blocks * a->num_kv_heads * a->block_size);
+        const uint64_t dims[4] = {64, 8, 2, rows / 8};
+        const uint64_t str[3] = {(uint64_t)kPfHD * 2, 128, 8ull * kPfHD * 2};
+        const uint32_t box[4] = {64, 8, 2, (uint32_t)(R / 8)};
+        int r1 = encode_tiled_16bit(&km, a->k_cache, 4, dims, str, box);
+        int r2 = encode_tiled_16bit(&vm, a->v_cache, 4, dims, str, box);
         if (r1 || r2) return fail(RFX_CUDA_ERROR, "cuTensorMapEncodeTiled(kv) failed (%d, %d)", r1, r2);
     }
     PrefillParams P = {};
@@ -671,7 +732,8 @@ int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, c
     P.bt_sb = a->bt_stride_b; P.max_blocks = a->max_blocks; P.num_blocks = a->num_blocks;
     P.B = (int)a->batch; P.Hq = (int)a->num_q_heads; P.Hkv = (int)a->num_kv_heads; P.G = G; P.T = T;
     P.Sq = (int)a->max_q_len; P.Sk = 0;
-    P.block_size = (int)a->block_size; P.box_rows = R; P.boxes_per_tile = 128 / R;
+    P.block_size = (int)a->block_size; P.box_keys = R; P.box_shift = log2_of(R); P.boxes_per_tile = kPfKeys / R;
+    P.kv_sbo = 2048; P.kv_half = 1024;
     P.n_qtiles = (int)((a->max_q_len + 2 * T - 1) / (2 * T));
     P.head_major_rows = 0; P.causal = a->is_causal;
     P.scale_log2 = a->sm_scale * 1.4426950408889634f;

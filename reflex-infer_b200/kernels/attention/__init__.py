@@ -138,7 +138,7 @@ class PagedAttentionCall:
     wants. The tensors are referenced, not copied: refill them in place between calls.
     """
 
-    def __init__(self, q, k_cache, v_cache, block_table, context_lens, *, q_start=None, max_q_len=1,
+    def __init__(self, q, k_cache, v_cache, block_table, context_lens, *, q_start=None, max_q_len=None,
                  is_causal=True, sm_scale=None, rope_cos=None, rope_sin=None, rope_positions=None,
                  rope_interleaved=False, workspace=None, out=None, force_generic=False, target_chunk=0):
         import ctypes as C
@@ -185,6 +185,11 @@ class PagedAttentionCall:
             rope_sin = rope_sin.to(q.dtype).contiguous()
             if rope_cos.dim() != 2 or rope_cos.shape[1] != D or rope_sin.shape != rope_cos.shape:
                 raise ValueError(f"{name}: rope tables must be [rows, {D}]")
+        if max_q_len is None:
+            # No request can own more rows than there are: a safe bound that needs no device read.
+            max_q_len = max(1, n_q) if q_start is not None else 1
+        if int(max_q_len) < 1:
+            raise ValueError(f"{name}: max_q_len must be >= 1, got {max_q_len}")
         if sm_scale is None:
             sm_scale = 1.0 / math.sqrt(D)
         if out is None:
@@ -283,7 +288,7 @@ def paged_attention(
     context_lens: torch.Tensor,
     *,
     q_start: Optional[torch.Tensor] = None,
-    max_q_len: int = 1,
+    max_q_len: Optional[int] = None,
     is_causal: bool = True,
     sm_scale: Optional[float] = None,
     rope_cos: Optional[torch.Tensor] = None,
@@ -304,7 +309,10 @@ def paged_attention(
     ``0..context_lens[b]-n_b+i`` (bottom-right aligned). Equals, per request,
     ``fused_attention(q_b, *kv_paged_lookup(..., max_ctx=context_lens[b]))`` with GQA
     expansion. ``max_q_len`` is a host-side upper bound of any request's row count (sizes
-    the workspace). Pass ``rope_cos/rope_sin/rope_positions`` to rotate Q on load.
+    the workspace and the grid; default: ``N_q`` when ``q_start`` is given, else 1). If a
+    request turns out to own more rows than that, or ``q_start[B] - q_start[0] != N_q``, nothing is
+    computed, the output rows are zero or left as they were, and bit 2 of the workspace status
+    word is set. Pass ``rope_cos/rope_sin/rope_positions`` to rotate Q on load.
     """
     call = PagedAttentionCall(q, k_cache, v_cache, block_table, context_lens, q_start=q_start, max_q_len=max_q_len,
                               is_causal=is_causal, sm_scale=sm_scale, rope_cos=rope_cos, rope_sin=rope_sin,
