@@ -17,14 +17,21 @@ attention partials (the HBM-bound kernel), combine. Rank 0 prints ONE JSON line.
   cpu_baseline  the CPU oracle (a port of the reference's torch path) timed on this box's
              host cores on a bounded sample of the same workload (rank 0, N=1 only).
 
-``--impl reference`` times that CPU port alone, on the same configuration, and prints the
-same line with ``"impl": "reference"``.
+``--impl reference`` times the reference's own torch path on CPU (its ``kernels`` package from
+``baseline/_ref`` when that copy exists, else the oracle port of it), on the same configuration,
+and prints the same line with ``"impl": "reference"``.
 
-Multi-GPU: one process per GPU (torchrun). ``--shard replica`` (default, weak scaling):
-every rank decodes its own batch of the configuration, no collective. ``--shard request``
-(strong): the one batch is split by request across ranks with a greedy balance on context
-length, no collective. ``--shard head`` (strong): ranks own kv-head slices of the pool and
-one NCCL all-gather assembles the output heads.
+Multi-GPU: one process per GPU (torchrun). ``--shard request`` (default, strong scaling): the ONE
+batch of the configuration is split by request across the ranks with a greedy balance on context
+length, no collective. ``--shard head`` (strong): ranks own kv-head slices of the pool and the
+output heads are assembled inside the combine kernel (peer stores) or by one NCCL all-gather.
+``--shard replica`` (weak): every rank decodes its own batch of the configuration. Without
+``--shard`` a multi-GPU run measures the request split for the headline and then the other three
+modes, reported under ``other_shards``.
+
+The secondary blocks (the other decode configuration, prefill, the mixed batch, fused linear + norm,
+the small ops) are printed as their own JSON lines BEFORE the result line, which is the last line
+of stdout and repeats their headline figures under ``secondary``.
 """
 from __future__ import annotations
 
@@ -39,9 +46,29 @@ import time
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
-for p in (ROOT / "reflex-infer_b200", ROOT):
-    if str(p) not in sys.path:
-        sys.path.insert(0, str(p))
+PKG = ROOT / "reflex-infer_b200"
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def use_package():
+    """Puts this repository's package (kernels, workloads, sharding) on the import path. Not done in
+    the reference arm, where ``kernels`` must be the reference's own package."""
+    if str(PKG) not in sys.path:
+        sys.path.insert(0, str(PKG))
+
+
+def load_workloads():
+    """The synthetic workload generators, loaded by file so that the reference arm need not put this
+    repository's ``kernels`` package on the path."""
+    if "workloads" in sys.modules:
+        return sys.modules["workloads"]
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("workloads", PKG / "workloads.py")
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["workloads"] = mod
+    spec.loader.exec_module(mod)
+    return mod
 
 import torch  # noqa: E402
 
@@ -60,11 +87,15 @@ def parse_args():
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="--shard head: assemble the heads inside the combine kernel (peer stores) or with an "
                          "NCCL all-gather")
-    ap.add_argument("--shard", default="replica", choices=["replica", "request", "head"])
+    ap.add_argument("--shard", default=None, choices=["replica", "request", "head"],
+                    help="default: request (strong scaling); a multi-GPU run without this flag also measures "
+                         "the other modes and reports them under other_shards")
     ap.add_argument("--only", default=None, choices=["cfg3", "cfg5", "linear_norm", "small_ops"],
                     help="run just that secondary block on one GPU and print it (small profiling cases: "
                          "--only cfg3 --requests 2)")
     ap.add_argument("--cpu-sample", type=int, default=0, help="requests in the CPU-baseline sample (0 = auto)")
+    ap.add_argument("--cpu-budget", type=float, default=120.0,
+                    help="--impl reference: seconds of CPU work the warm-up and timed steps may take in total")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary configuration block")
     ap.add_argument("--chunk", type=int, default=0, help="keys per split (0 = planner's choice)")
@@ -73,6 +104,20 @@ def parse_args():
     ap.add_argument("--requests", type=int, default=0,
                     help="profiling aid: shrink the batch to this many requests (0 = the configuration's own)")
     return ap.parse_args()
+
+
+REFERENCE_SAMPLE_NOTE = ("the reference arm (--impl reference) times a bounded sample of the requests per step "
+                         "on the host cores and is normalised per token")
+
+
+def line_config(workload: str, shard: str, extra: dict = None) -> dict:
+    """The `config` object of the result line; the same for both arms of a run."""
+    kv_small = workload == "cfg2"
+    return {**workload_desc(workload), "shard": shard,
+            "l2": ("512 MiB memset between timed steps flushes L2 (outside the timed events)" if kv_small else
+                   "K+V read per step exceeds L2 (126 MB) many times over; no flush"),
+            "timing": "CUDA events per step on the launch stream, max over ranks",
+            "reference_arm_sample": REFERENCE_SAMPLE_NOTE, **(extra or {})}
 
 
 def workload_desc(name: str) -> dict:
@@ -159,26 +204,66 @@ class ClockSampler:
                 "samples": len(sm), "samples_inside_timed_regions": len(inside), "reasons": sorted(reasons)}
 
 
-# ---- CPU legs (oracle: the only place besides tests that may import it) -------------------
+# ---- CPU legs (the reference arm; the only place besides tests that may import the oracle) --------
 
-def cpu_decode_time(batch, as_written: bool = False) -> float:
-    """One decode step of `batch` (CPU tensors) through the oracle; seconds."""
-    import oracle
-    t0 = time.perf_counter()
-    pos = batch.positions.long()
-    q_rot = oracle.apply_rope(batch.q_new.unsqueeze(0), batch.cos[pos], batch.sin[pos])[0]
-    k_rot = oracle.apply_rope(batch.k_new.unsqueeze(0), batch.cos[pos], batch.sin[pos])[0]
-    oracle.kv_paged_append(k_rot, batch.v_new, batch.k_cache, batch.v_cache, batch.slot_mapping)
-    out = oracle.paged_attention_composed(q_rot, batch.k_cache, batch.v_cache, batch.block_table, batch.context_lens,
-                                          as_written=as_written)
-    dt = time.perf_counter() - t0
-    cpu_decode_time.last_out = out
-    return dt
+class ReferenceOps:
+    """The four ops of the path as the reference arm calls them: the reference's own ``kernels``
+    package (torch backend, CPU tensors) when a copy sits under baseline/_ref, else the oracle's
+    restatement of that path. `kind` says which ("reference" / "port")."""
+
+    def __init__(self):
+        root = ROOT / "baseline" / "_ref"
+        self.kind = "port"
+        if (root / "kernels" / "attention" / "__init__.py").exists() and "kernels" not in sys.modules:
+            sys.path.insert(0, str(root))
+            try:
+                from kernels.attention import fused_attention
+                from kernels.kv_cache import kv_paged_append, kv_paged_lookup
+                from kernels.rope import apply_rope
+                assert Path(sys.modules["kernels"].__file__).resolve().is_relative_to(root.resolve())
+                bk = dict(backend="torch")
+                self.apply_rope = lambda x, c, s_: apply_rope(x, c, s_, **bk)
+                self.append = lambda k, v, kc, vc, sl: kv_paged_append(k, v, kc, vc, sl, **bk)
+                self.lookup = lambda kc, vc, bt, cl, mx: kv_paged_lookup(kc, vc, bt, cl, mx, **bk)
+                self.attention = lambda q, k, v: fused_attention(q, k, v, **bk)
+                self.kind = "reference"
+            except Exception as e:  # an unusable copy: say so and fall back to the port
+                print(f"bench.py: baseline/_ref is not importable ({e}); using the oracle port", file=sys.stderr)
+                sys.path.remove(str(root))
+        import oracle
+        self.oracle = oracle
+        if self.kind == "port":
+            self.apply_rope = oracle.apply_rope
+            self.append = oracle.kv_paged_append
+            self.lookup = oracle.kv_paged_lookup_as_written
+            self.attention = lambda q, k, v: oracle.attention(q, k, v)
+
+    def decode_step(self, batch, vectorised: bool = False) -> float:
+        """One decode step of `batch` (CPU tensors) the way the reference composes it: tables rows ->
+        apply_rope -> kv_paged_append -> per request kv_paged_lookup, GQA expansion, fused_attention.
+        `vectorised` swaps the per-token Python loop of the reference's lookup for one gather (same
+        result), so that the baseline is not a Python loop alone. Seconds."""
+        t0 = time.perf_counter()
+        pos = batch.positions.long()
+        q_rot = self.apply_rope(batch.q_new.unsqueeze(0), batch.cos[pos], batch.sin[pos])[0]
+        k_rot = self.apply_rope(batch.k_new.unsqueeze(0), batch.cos[pos], batch.sin[pos])[0]
+        self.append(k_rot, batch.v_new, batch.k_cache, batch.v_cache, batch.slot_mapping)
+        lookup = self.oracle.kv_paged_lookup if vectorised else self.lookup
+        g = batch.Hq // batch.Hkv
+        out = torch.zeros_like(q_rot)
+        for r in range(batch.B):
+            ctx = int(batch.context_lens[r])
+            kd, vd = lookup(batch.k_cache, batch.v_cache, batch.block_table[r:r + 1], batch.context_lens[r:r + 1], ctx)
+            qb = q_rot[r:r + 1].transpose(0, 1).unsqueeze(0)  # [1, H, 1, D]
+            ob = self.attention(qb, kd.repeat_interleave(g, dim=1), vd.repeat_interleave(g, dim=1))
+            out[r] = ob[0, :, 0]
+        self.last_out = out
+        return time.perf_counter() - t0
 
 
 def make_cpu_batch(workload: str, n_req: int, seed: int):
     import oracle
-    import workloads
+    workloads = load_workloads()
     if workload == "cfg4":
         cos, sin = oracle.build_rope_tables(32770, 128, base=1e6, dtype=torch.bfloat16)
         return workloads.cfg4(device="cpu", seed=seed, B=n_req, tables=(cos, sin))
@@ -189,25 +274,16 @@ def make_cpu_batch(workload: str, n_req: int, seed: int):
 
 
 def cpu_baseline(workload: str, sample: int, budget_s: float = 20.0) -> dict:
-    torch.set_num_threads(os.cpu_count() or 1)
-    cores = torch.get_num_threads()
-    n = sample or 2
-    batch = make_cpu_batch(workload, n, seed=100)
-    t = cpu_decode_time(batch)  # warm-up, also sizes the sample
-    if not sample:
-        n = max(2, min(64, int(budget_s / max(t / n, 1e-3) / 3)))
-        batch = make_cpu_batch(workload, n, seed=101)
-        cpu_decode_time(batch)
-    times = [cpu_decode_time(batch) for _ in range(2)]
-    best = min(times)
-    small = make_cpu_batch(workload, 2, seed=102)
-    t_written = cpu_decode_time(small, as_written=True)
-    return {"value": n / best, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": f"{n} requests of {workload} drawn from the same generator, one decode step, best of 2 after "
-                      f"warm-up; oracle composition (vectorised page gather + torch CPU SDPA)",
-            "as_written_value": 2 / t_written,
-            "as_written_note": "same composition with the reference's per-token Python lookup loop, 2 requests",
-            "torch": torch.__version__}
+    """The reference arm run as its own process (its `kernels` package cannot share a process with
+    this repository's package of the same name) on a bounded sample; its `cpu_baseline` object."""
+    cmd = [sys.executable, str(Path(__file__).resolve()), "--impl", "reference", "--workload", workload, "--steps", "2",
+           "--warmup", "1", "--cpu-budget", str(budget_s)] + (["--cpu-sample", str(sample)] if sample else [])
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        line = json.loads(r.stdout.strip().splitlines()[-1])
+        return line["cpu_baseline"]
+    except Exception as e:
+        return {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "port", "sample": f"failed: {e}"}
 
 
 def run_reference(args):
@@ -216,27 +292,38 @@ def run_reference(args):
         return
     torch.set_num_threads(os.cpu_count() or 1)
     cores = torch.get_num_threads()
+    ops = ReferenceOps()
     n = args.cpu_sample or 2
     batch = make_cpu_batch(args.workload, n, seed=100)
-    t = cpu_decode_time(batch)
+    t = ops.decode_step(batch)
     if not args.cpu_sample:
-        # size the per-step sample so that steps+warmup end within about two minutes
+        # size the per-step sample so that warm-up + steps end within the budget (about two minutes
+        # for the driver's run, 20 s for the in-line baseline of the GPU arm)
         per_req = t / n
-        n = max(1, min(64, int(120.0 / max(args.steps + args.warmup, 1) / max(per_req, 1e-3))))
+        n = max(1, min(64, workload_desc(args.workload)["batch"],
+                       int(args.cpu_budget / max(args.steps + args.warmup, 1) / max(per_req, 1e-3))))
         batch = make_cpu_batch(args.workload, n, seed=101)
     for _ in range(args.warmup):
-        cpu_decode_time(batch)
-    times = [cpu_decode_time(batch) for _ in range(args.steps)]
+        ops.decode_step(batch)
+    times = [ops.decode_step(batch) for _ in range(args.steps)]
     total = sum(times)
     value = n * args.steps / total
-    sample = (f"{n} requests of {args.workload} per step (same generator and distributions), CPU oracle port of the "
-              f"reference torch path: rope -> append -> per-request gather -> GQA expansion -> SDPA")
+    t_vec = min(ops.decode_step(batch, vectorised=True) for _ in range(2))
+    what = ("the reference's own kernels package (baseline/_ref), backend='torch', CPU tensors" if ops.kind == "reference"
+            else "CPU oracle port of the reference's torch path")
+    sample = (f"{n} of {workload_desc(args.workload)['batch']} requests of {args.workload} per step (same generator and "
+              f"distributions), {what}: apply_rope -> kv_paged_append -> per request kv_paged_lookup, GQA expansion, "
+              f"fused_attention")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_desc(args.workload),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+        "higher_is_better": True, "scaling": "weak" if args.shard == "replica" else "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": line_config(args.workload, args.shard or "request"),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": ops.kind, "sample": sample,
+                         "vectorised_gather_value": n / t_vec,
+                         "vectorised_gather_note": "same composition with the lookup's per-token Python loop replaced "
+                                                   "by one gather (identical result), best of 2",
                          "torch": torch.__version__},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -358,7 +445,7 @@ def timed_steps(fn, steps, warmup, flush=None, dist=None, with_kernel_events=Fal
 
 
 def build_batch(workload, device, seed, shard, rank, world, requests=0):
-    import workloads
+    workloads = load_workloads()
     if workload == "cfg4":
         b = workloads.cfg4(device=device, seed=seed, B=requests or None)
     elif requests:
@@ -375,11 +462,11 @@ def build_batch(workload, device, seed, shard, rank, world, requests=0):
     return b
 
 
-def measure(workload, args, device, rank, world, dist, want_e2e=True, sampler=None):
+def measure(workload, args, device, rank, world, dist, want_e2e=True, sampler=None, shard="request", gather_kind="fused"):
     seed_base = {"cfg4": 3, "cfg2": 1}[workload]
     # replica: every rank draws its own batch; request/head: all ranks draw the same one, then cut it
-    seed = seed_base + (1000 * rank if args.shard == "replica" else 0)
-    batch = build_batch(workload, device, seed, args.shard, rank, world, args.requests if workload == args.workload else 0)
+    seed = seed_base + (1000 * rank if shard == "replica" else 0)
+    batch = build_batch(workload, device, seed, shard, rank, world, args.requests if workload == args.workload else 0)
     packed, batch = pack_step_inputs(batch)
     step = DecodeStep(batch, chunk=args.chunk)
     kv_bytes = batch.kv_bytes()
@@ -393,10 +480,10 @@ def measure(workload, args, device, rank, world, dist, want_e2e=True, sampler=No
 
     gather = None
     gather_check = None
-    if world > 1 and args.shard == "head":
+    if world > 1 and shard == "head":
         from sharding import FusedHeadGather, HeadGather
         gather = HeadGather(step.out, dist)
-        if args.gather == "fused":
+        if gather_kind == "fused":
             # same step twice: NCCL all-gather of the local heads, then the gathering combine
             want = gather.run(step.run()).clone()
             step.gather = FusedHeadGather(step.out.shape[0], batch.Hq, batch.D, batch.dtype, device, dist)
@@ -434,7 +521,7 @@ def measure(workload, args, device, rank, world, dist, want_e2e=True, sampler=No
            "kernel_ms_min": min(kern_ms), "status": status, "flush": flush_note, "kernel_kind": step.attn.kernel_kind,
            "launches": step.kernel_launches * args.steps, "gather_check": gather_check}
     if want_e2e:
-        head_mode = world > 1 and args.shard == "head"
+        head_mode = world > 1 and shard == "head"
         host = HostDrivenStep(step, packed, post=gather, read_back=(rank == 0 or not head_mode))
         e2e_ms, _ = timed_steps(host.run, args.steps, args.warmup, flush, dist)
         res.update(e2e_ms=e2e_ms, h2d=host.h2d, d2h=host.d2h)
@@ -445,11 +532,35 @@ def measure(workload, args, device, rank, world, dist, want_e2e=True, sampler=No
     return res
 
 
+def whole_job(res, dist, device, shard, world):
+    """Whole-job figures of one measurement: the tokens of all ranks over the slowest rank's time.
+    Returns (total_ms, e2e_ms, kernel_ms, tokens, kv_bytes), the times as max over ranks."""
+    t = torch.tensor([res["total_ms"], res.get("e2e_ms", 0.0), res["kernel_ms"]], dtype=torch.float64, device=device)
+    toks = torch.tensor([float(res["tokens"]), float(res["kv_bytes"])], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(toks, op=dist.ReduceOp.SUM)
+    total_ms, e2e_ms, kernel_ms = t.tolist()
+    all_tokens, all_bytes = toks.tolist()
+    if shard == "head" and world > 1:
+        all_tokens = float(res["tokens"])  # every rank works on all requests; count them once
+    return total_ms, e2e_ms, kernel_ms, all_tokens, all_bytes
+
+
+def release(res):
+    """Frees what a measurement holds on the device (peer mappings first)."""
+    g = getattr(res.get("step"), "gather", None)
+    if g is not None:
+        g.close()
+    res.clear()
+    torch.cuda.empty_cache()
+
+
 def measure_prefill(args, device):
     """Configuration 3 (causal paged prefill, 8 x 2048 new tokens, 32q/8kv heads, D=128, page 16):
     one step = fused RoPE + append of every new token (Q rotated too) + causal attention from
     the pool on the tcgen05 kernel. Tensor-pipe roofline on the attention kernel."""
-    import workloads
+    workloads = load_workloads()
     from kernels.attention import PagedAttentionCall, RopeAppendCall
     b = workloads.cfg3(device=device, scale=(args.requests / 8.0 if args.requests else 1.0), seq=2048)
     q_rot = torch.empty_like(b.q_new)
@@ -493,7 +604,7 @@ def measure_mixed(args, device):
     keys, 28q/4kv heads, page 16, 1 Mi-page pool with 40 % of the pages free, 10 % of the requests
     compacted onto fresh pages with kv_paged_scatter before the step). One step = fused RoPE +
     append of the new tokens + bottom-right-causal attention from the pool."""
-    import workloads
+    workloads = load_workloads()
     from kernels.attention import PagedAttentionCall, RopeAppendCall
     from kernels.kv_cache import kv_paged_scatter
     b = workloads.cfg5(device=device)
@@ -660,9 +771,10 @@ def check_against_oracle(res, n_req=2):
     """Cheap sanity outside every timed region: first requests of the batch vs the CPU oracle."""
     import oracle
     b = res["batch"]
-    res["step"].gather = None  # this check runs on one rank alone: local heads, plain combine
+    held, res["step"].gather = res["step"].gather, None  # this check runs on one rank alone: local heads, plain combine
     out = res["step"].run()
     torch.cuda.synchronize()
+    res["step"].gather = held
     n = min(n_req, b.B)
     errs = []
     for r in range(n):
@@ -679,6 +791,11 @@ def check_against_oracle(res, n_req=2):
     return max(errs) if errs else 0.0
 
 
+def emit_block(name: str, block: dict) -> None:
+    """A secondary block as its own stdout line, ahead of the result line."""
+    print(json.dumps({"block": name, **block}), flush=True)
+
+
 def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -688,6 +805,7 @@ def run_ours(args):
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29531", __file__] + sys.argv[1:]
         raise SystemExit(subprocess.call(cmd))
+    use_package()
     from kernels import _native
     _native.lib()  # no fallback: fail here if the CUDA library is missing
     assert torch.cuda.is_available(), "bench.py needs a GPU for --impl ours"
@@ -699,97 +817,118 @@ def run_ours(args):
         dist_mod.init_process_group("nccl", device_id=device)
         dist = dist_mod
 
+    shard = args.shard or "request"
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
-    res = measure(args.workload, args, device, rank, world, dist, sampler=sampler)
+    res = measure(args.workload, args, device, rank, world, dist, sampler=sampler, shard=shard, gather_kind=args.gather)
     clocks = sampler.stop() if sampler else None
+    total_ms, e2e_ms, kernel_ms, all_tokens, all_bytes = whole_job(res, dist, device, shard, world)
 
-    # whole-job numbers: tokens of all ranks over the slowest rank's time
-    t = torch.tensor([res["total_ms"], res["e2e_ms"], res["kernel_ms"]], dtype=torch.float64, device=device)
-    toks = torch.tensor([float(res["tokens"]), float(res["kv_bytes"])], dtype=torch.float64, device=device)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dist.all_reduce(toks, op=dist.ReduceOp.SUM)
-    total_ms, e2e_ms, kernel_ms = t.tolist()
-    all_tokens, all_bytes = toks.tolist()
-    if args.shard == "head" and world > 1:
-        all_tokens = float(res["tokens"])  # every rank works on all requests; count them once
+    peak, peak_kind = measured_peak()
+    line = None
+    if rank == 0:
+        achieved = res["kv_bytes"] / (res["kernel_ms"] * 1e-3) / 1e9  # this rank's kernel, GB/s
+        line = {
+            "metric": METRIC,
+            "value": all_tokens * args.steps / (total_ms * 1e-3),
+            "unit": UNIT,
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True,
+            "scaling": "weak" if shard == "replica" else "strong",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic",
+            "config": line_config(args.workload, shard, {
+                **({"head_gather": args.gather, "head_gather_check": res["gather_check"]}
+                   if shard == "head" and world > 1 else {}),
+                **({"requests_override": args.requests} if args.requests else {}),
+                **({"cuda_graph": True} if args.graph else {})}),
+            "e2e": {"value": all_tokens * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"],
+                    "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": res["launches"],
+            "roofline": {"bound": "hbm", "kernel": "decode_mma_kernel" if res["kernel_kind"] == 1 else "paged_partial_generic_kernel",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
+                         "algorithmic_bytes_per_launch": res["kv_bytes"], "kernel_ms": res["kernel_ms"],
+                         "kernel_ms_min": res["kernel_ms_min"], "traffic": None},
+            "step_fixed_cost_ms": (total_ms / args.steps) - kernel_ms,
+            "clocks": clocks,
+            "device_status_word": res["status"],
+        }
+        # DRAM bytes per algorithmic byte from the ncu captures summarised under profiles/
+        # (decode_mma_kernel_cfg4.md: 16-request case, traffic grows in proportion to the keys;
+        # decode_mma_kernel_cfg2.md: the whole configuration).
+        ratio = {"cfg4": 1.0043, "cfg2": 1.0357}[args.workload]
+        if res["kernel_kind"] == 1:
+            line["roofline"]["traffic"] = ratio * res["kv_bytes"]
+            line["roofline"]["traffic_note"] = f"{ratio} x algorithmic bytes, ncu dram__bytes_read+write, see profiles/"
+        line["max_abs_err_vs_oracle"] = check_against_oracle(res)
+    release(res)
+
+    if world > 1 and args.shard is None:
+        # The same one batch in the other partitionings, all on this run's clock: kv-head sharding with
+        # the gather fused into the combine kernel and with an NCCL all-gather, and independent replicas.
+        others = {}
+        for name, sh, gk in (("head_fused", "head", "fused"), ("head_nccl", "head", "nccl"), ("replica", "replica", None)):
+            if dist is not None:
+                dist.barrier()
+            r2 = measure(args.workload, args, device, rank, world, dist, want_e2e=False, shard=sh, gather_kind=gk or "fused")
+            t_ms, _, k_ms, toks, _ = whole_job(r2, dist, device, sh, world)
+            others[name] = {"value": toks * args.steps / (t_ms * 1e-3), "unit": UNIT, "ms_per_step": t_ms / args.steps,
+                            "kernel_ms": k_ms, "step_fixed_cost_ms": t_ms / args.steps - k_ms,
+                            "scaling": "weak" if sh == "replica" else "strong", "device_status_word": r2["status"],
+                            **({"head_gather_check": r2["gather_check"]} if name == "head_fused" else {})}
+            release(r2)
+        if line is not None:
+            line["other_shards"] = others
 
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
 
-    peak, peak_kind = measured_peak()
-    achieved = res["kv_bytes"] / (res["kernel_ms"] * 1e-3) / 1e9  # this rank's kernel, GB/s
-    line = {
-        "metric": METRIC,
-        "value": all_tokens * args.steps / (total_ms * 1e-3),
-        "unit": UNIT,
-        "n_gpus": world,
-        "steps": args.steps,
-        "warmup": args.warmup,
-        "ms_per_step": total_ms / args.steps,
-        "higher_is_better": True,
-        "scaling": "weak" if args.shard == "replica" else "strong",
-        "vs_baseline": None,
-        "dtype": "bf16",
-        "data": "synthetic",
-        "config": {**workload_desc(args.workload), "shard": args.shard, "l2": res["flush"],
-                   **({"head_gather": args.gather, "head_gather_check": res["gather_check"]}
-                      if args.shard == "head" and world > 1 else {}),
-                   **({"requests_override": args.requests} if args.requests else {}),
-                   **({"cuda_graph": True} if args.graph else {}),
-                   "timing": "CUDA events per step on the launch stream, max over ranks"},
-        "e2e": {"value": all_tokens * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
-                "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"],
-                "ms_per_step": e2e_ms / args.steps},
-        "gpu_launches": res["launches"],
-        "roofline": {"bound": "hbm", "kernel": "decode_mma_kernel" if res["kernel_kind"] == 1 else "paged_partial_generic_kernel",
-                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
-                     "algorithmic_bytes_per_launch": res["kv_bytes"], "kernel_ms": res["kernel_ms"],
-                     "kernel_ms_min": res["kernel_ms_min"], "traffic": None},
-        "clocks": clocks,
-        "device_status_word": res["status"],
-    }
-    # DRAM bytes per algorithmic byte from the ncu captures summarised under profiles/
-    # (decode_mma_kernel_cfg4.md: 16-request case, traffic grows in proportion to the keys;
-    # decode_mma_kernel_cfg2.md: the whole configuration).
-    ratio = {"cfg4": 1.0043, "cfg2": 1.0357}[args.workload]
-    if res["kernel_kind"] == 1:
-        line["roofline"]["traffic"] = ratio * res["kv_bytes"]
-        line["roofline"]["traffic_note"] = f"{ratio} x algorithmic bytes, ncu dram__bytes_read+write, see profiles/"
-    line["max_abs_err_vs_oracle"] = check_against_oracle(res)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args.workload, args.cpu_sample)
     if world == 1 and not args.no_extra:
+        secondary = {}
         other = "cfg2" if args.workload == "cfg4" else "cfg4"
-        del res
-        torch.cuda.empty_cache()
         r2 = measure(other, args, device, rank, world, dist)
         ach2 = r2["kv_bytes"] / (r2["kernel_ms"] * 1e-3) / 1e9
-        line["other_workloads"] = {other: {
-            "config": workload_desc(other)["workload"], "value": r2["tokens"] * args.steps / (r2["total_ms"] * 1e-3),
-            "unit": UNIT, "ms_per_step": r2["total_ms"] / args.steps, "e2e_ms_per_step": r2["e2e_ms"] / args.steps,
-            "roofline_achieved_gbs": ach2, "roofline_frac": ach2 / peak, "kernel_ms": r2["kernel_ms"],
-            "l2": r2["flush"]}}
-        del r2
+        blk = {"config": workload_desc(other)["workload"], "value": r2["tokens"] * args.steps / (r2["total_ms"] * 1e-3),
+               "unit": UNIT, "ms_per_step": r2["total_ms"] / args.steps, "e2e_ms_per_step": r2["e2e_ms"] / args.steps,
+               "roofline_achieved_gbs": ach2, "roofline_frac": ach2 / peak, "kernel_ms": r2["kernel_ms"],
+               "l2": r2["flush"], "device_status_word": r2["status"]}
+        emit_block(other, blk)
+        secondary[f"{other}_frac"] = blk["roofline_frac"]
+        secondary[f"{other}_ms_per_step"] = blk["ms_per_step"]
+        release(r2)
+        blk = measure_prefill(args, device)
+        emit_block("cfg3", blk)
+        secondary.update(cfg3_frac=blk["roofline"]["frac"], cfg3_kernel_ms=blk["kernel_ms"])
         torch.cuda.empty_cache()
-        line["other_workloads"]["cfg3"] = measure_prefill(args, device)
+        blk = measure_mixed(args, device)
+        emit_block("cfg5", blk)
+        secondary.update(cfg5_frac=blk["hbm_frac"], cfg5_kernel_ms=blk["kernel_ms"])
         torch.cuda.empty_cache()
-        line["other_workloads"]["cfg5"] = measure_mixed(args, device)
+        blk = measure_linear_norm(args, device)
+        emit_block("fused_linear_norm", blk)
         torch.cuda.empty_cache()
-        line["other_workloads"]["fused_linear_norm"] = measure_linear_norm(args, device)
-        torch.cuda.empty_cache()
-        line["other_workloads"]["small_ops"] = measure_small_ops(args, device)
+        blk = measure_small_ops(args, device)
+        emit_block("small_ops", blk)
+        secondary["small_ops_frac"] = {k: round(v["frac_of_hbm_peak"], 3) for k, v in blk.items()}
+        line["secondary"] = secondary
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
 
 
 def run_only(args):
+    use_package()
     from kernels import _native
     _native.lib()
     assert torch.cuda.is_available(), "bench.py needs a GPU"
