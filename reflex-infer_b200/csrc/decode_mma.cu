@@ -32,11 +32,12 @@ constexpr int kTile = kPlanTile;    // keys per stage
 constexpr int kGroupWarps = 4;      // warps per consumer group, 16 keys each
 constexpr int kAccPad = 4;          // floats of padding per merge row (bank spread)
 
-struct StageMeta {
+struct alignas(16) StageMeta {  // 32 bytes: the mbarriers behind the array stay 8-byte aligned
     int item;      // -1: no more work
     int n_valid;   // keys of this stage that exist (0..64)
     int flags;     // bit0 first stage of item, bit1 last stage of item, bit2 rotate Q
     int prow;      // first partial row of the item
+    unsigned bad;  // boxes of the stage that were not loaded (page index outside the pool): their keys do not count
 };
 
 struct DecodeParams {
@@ -74,6 +75,7 @@ struct DecodeSmem {
     static constexpr size_t off_ml = off_merge + merge_bytes;             // [group warps][GP][2]
     static constexpr size_t off_meta = off_ml + (size_t)kGroupWarps * GP * 2 * 4;
     static constexpr size_t off_bars = off_meta + (size_t)STAGES * sizeof(StageMeta);
+    static_assert(sizeof(StageMeta) % 8 == 0 && off_meta % 8 == 0, "mbarriers need 8-byte alignment");
     static constexpr size_t total = off_bars + 2 * (size_t)STAGES * 8 + 1024;  // + alignment slack
 };
 
@@ -297,6 +299,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             m.item = ib + j; m.n_valid = n_valid;
                             m.flags = (t == 0 ? 1 : 0) | (t == n_tiles - 1 ? 2 : 0) | (rotate ? 4 : 0);
                             m.prow = prow;
+                            m.bad = wantmask & ~okmask;
                             sMeta[stage] = m;
                             if (okmask != wantmask) atomicOr(P.hdr + HdrStatus, kStatusBadPage);
                             uint32_t tx = 2u * box_bytes * (uint32_t)__popc(okmask);
@@ -349,7 +352,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         if (alive && lane == 0) {
             if (ptx::mbar_wait_bounded(&empty[stage], phase ^ 1u)) {
                 StageMeta m;
-                m.item = -1; m.n_valid = 0; m.flags = 0; m.prow = 0;
+                m.item = -1; m.n_valid = 0; m.flags = 0; m.prow = 0; m.bad = 0;
                 sMeta[stage] = m;
                 ptx::mbar_arrive(&full[stage]);
             } else {
@@ -409,15 +412,17 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         if (group == turn && slice0 < meta.n_valid) {
             const uint32_t kst = sK_u32 + (uint32_t)stage * S::kTileBytes;
             const uint32_t vst = sV_u32 + (uint32_t)stage * S::kTileBytes;
-            const bool tail = meta.n_valid < slice0 + 16;
+            // Keys past the end, and keys of a page whose index is outside the pool, do not count. What
+            // sits in their rows may be anything (stale pages, NaN patterns): their probabilities are
+            // zero but 0*NaN would poison P.V, so those V rows are cleared.
+            const bool tail = meta.n_valid < slice0 + 16 || meta.bad != 0;
+            auto dead = [&](int tk) -> bool { return tk >= meta.n_valid || ((meta.bad >> (tk / R)) & 1u); };
             if (tail) {
-                // Keys past the end may hold anything (stale pages, NaN patterns): their
-                // probabilities are zero but 0*NaN would poison P.V, so clear those V rows.
                 unsigned char* vs = sV + (size_t)stage * S::kTileBytes;
                 for (int i = lane; i < 16 * (S::kRowBytes / 16); i += 32) {
                     const int tk = slice0 + i / (S::kRowBytes / 16);
                     const int ch = i % (S::kRowBytes / 16);
-                    if (tk >= meta.n_valid) {
+                    if (dead(tk)) {
                         const int bx = tk / R, rr = tk - bx * R;
                         *reinterpret_cast<uint4*>(vs + (size_t)bx * box_bytes + (size_t)(ch >> 3) * half_bytes +
                                                   (size_t)rr * 128 + (size_t)(ch & 7) * 16) = make_uint4(0, 0, 0, 0);
@@ -454,7 +459,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     t[i] = fmaf(s[nt][i], P.scale_log2, -m_run[nt][i & 1]);  // +inf while m_run is -inf
-                    if (tail && slice0 + r8 + 8 * (i >> 1) >= meta.n_valid) t[i] = -INFINITY;
+                    if (tail && dead(slice0 + r8 + 8 * (i >> 1))) t[i] = -INFINITY;
                 }
                 const bool exceeds = fmaxf(fmaxf(t[0], t[1]), fmaxf(t[2], t[3])) > 0.f;
                 if (__any_sync(0xffffffffu, exceeds)) {
@@ -462,7 +467,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         v[i] = s[nt][i] * P.scale_log2;
-                        if (tail && slice0 + r8 + 8 * (i >> 1) >= meta.n_valid) v[i] = -INFINITY;
+                        if (tail && dead(slice0 + r8 + 8 * (i >> 1))) v[i] = -INFINITY;
                     }
                     float mx0 = fmaxf(v[0], v[2]), mx1 = fmaxf(v[1], v[3]);
 #pragma unroll

@@ -72,6 +72,28 @@ def test_workspace_size_query(native):
     assert lib.rfx_paged_attention_workspace_bytes(C.byref(p)) > n1
 
 
+def test_workspace_capacity_rule(native):
+    """The partial rows the workspace holds: G * (Hkv * n_q + runs * max_q_len), runs = 8 per SM
+    (148 SMs assumed where no device answers). The plan kernel refuses, on the device, any q_start
+    whose requests exceed max_q_len or whose total differs from n_q, so this host-side size is a
+    bound the kernels never write past."""
+    lib = native.lib()
+    Hq, Hkv, D, n_q, B = 28, 4, 128, 900, 64
+    def size(mq):
+        p = native.PagedAttentionArgs(batch=B, n_q=n_q, num_q_heads=Hq, num_kv_heads=Hkv, head_dim=D, num_blocks=64,
+                                      block_size=16, max_blocks=8, max_q_len=mq, dtype=1)
+        p.q_start = 256  # any non-null pointer: the query only looks at sizes
+        return lib.rfx_paged_attention_workspace_bytes(C.byref(p))
+    G = Hq // Hkv
+    s1, s64 = size(1), size(64)
+    sms = round((s64 - s1) / (G * 8 * 63 * (D + 2) * 4))
+    assert sms >= 100, sms
+    assert abs((s64 - s1) - G * 8 * sms * 63 * (D + 2) * 4) <= 3 * 256
+    rows1 = G * (Hkv * n_q + 8 * sms)
+    assert s1 >= rows1 * (D + 2) * 4
+    assert size(0) == s1  # a bound below one row per request is read as one
+
+
 def test_cpp_header_compiles_and_links(native, tmp_path):
     """The header-only C++ face (reference-style `Status`, args structs, `const Args&` calls)
     compiles as C++17, links against the library and reports an argument error as a status."""

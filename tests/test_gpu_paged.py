@@ -190,8 +190,6 @@ def test_chunked_prefill_mixed_batch(native):
         new_bt = cpu.block_table.clone()
         new_bt[0, :npages] = fresh[:npages]
         new_slots = new_bt[0, t // 16] * 16 + t % 16
-        for cache_cpu, cache_gpu in ((kc, gpu.k_cache), (vc, gpu.v_cache)):
-            pass
         rows_k = kc.permute(0, 2, 1, 3).reshape(-1, 4, 128)[old_slots]
         rows_v = vc.permute(0, 2, 1, 3).reshape(-1, 4, 128)[old_slots]
         oracle.kv_paged_scatter(rows_k, rows_v, kc, vc, new_slots)

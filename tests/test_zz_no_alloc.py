@@ -55,6 +55,10 @@ def test_static_scratch_matches_workspace_path_twice(native):
         assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the amount of free device memory"
         assert torch.equal(out, first)
         assert torch.equal(call.run_static(), first)
+        # the status word of the built-in array (bad page, expired wait, capacity): a NULL workspace asks for it
+        word = C.c_int(-1)
+        assert lib.rfx_paged_attention_status(None, args.stream, C.byref(word)) == N.RFX_SUCCESS
+        assert word.value == 0
 
 
 def test_static_scratch_rejects_oversized_problems(native):
