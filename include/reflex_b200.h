@@ -19,6 +19,14 @@
  *   k_cache, v_cache : [num_blocks, num_kv_heads, block_size, head_dim]
  *   slot             = page * block_size + position_in_page
  *   block_table[b,j] = physical page of logical block j of request b
+ *
+ * int8 KV with one fp32 scale per (position, kv head) -- the reference's `kv_int8` with
+ * `k_scales[kv_pos * n_kv_heads + kv_head]` (src/kernels/attention.cu:91-96,141-150;
+ * include/reflex/infer.h:189-203), carried over to pages:
+ *   k_cache, v_cache : int8 [num_blocks, num_kv_heads, block_size, head_dim]
+ *   k_scales, v_scales : fp32 [num_blocks, num_kv_heads, block_size]
+ *   value = int8 * scale. The writer (rfx_rope_append with kv_int8) quantises each row with
+ *   scale = max|x| / 127 (1 for an all-zero row) and q = round-half-even(x / scale), in fp32.
  */
 #ifndef REFLEX_B200_H_
 #define REFLEX_B200_H_
@@ -30,7 +38,7 @@
 extern "C" {
 #endif
 
-#define RFX_ABI_VERSION 1
+#define RFX_ABI_VERSION 2
 
 /* include/reflex/infer.h:16-23 (first six, same order) + three additions. */
 typedef enum {
@@ -164,6 +172,12 @@ typedef struct {
     int interleaved;
     int dtype;
     rfx_stream stream;
+    /* int8 pool (see the layout note at the top): k_cache/v_cache are int8, contiguous (the strides
+     * above are ignored), and the rotated K rows and the V rows are quantised on the way in; their
+     * scales go to k_scales/v_scales [num_blocks, num_kv_heads, block_size]. q_out stays in `dtype`. */
+    int kv_int8;
+    float* k_scales;
+    float* v_scales;
 } RfxRopeAppendArgs;
 int rfx_rope_append(const RfxRopeAppendArgs* a);
 
@@ -252,6 +266,13 @@ typedef struct {
     void* workspace;
     size_t workspace_bytes;
     rfx_stream stream;
+    /* int8 pool (see the layout note at the top): k_cache/v_cache are int8 and every key's score is
+     * multiplied by its k scale, every probability by its v scale (the dequantisation of
+     * src/kernels/attention.cu:91-96,141-150 moved behind the dot products; same value up to fp32
+     * rounding). q, out and the RoPE tables stay in `dtype`. */
+    int kv_int8;
+    const float* k_scales;       /* [num_blocks, H_kv, block_size] */
+    const float* v_scales;
 } RfxPagedAttentionArgs;
 size_t rfx_paged_attention_workspace_bytes(const RfxPagedAttentionArgs* a);
 int rfx_paged_attention_plan(const RfxPagedAttentionArgs* a);
@@ -266,7 +287,9 @@ int rfx_paged_attention_partials(const RfxPagedAttentionArgs* a);
  * max_q_len <= 512 and pages hold <= 64 keys), 3 = the same split batch with its one-row
  * requests on the decode kernel, 1 = TMA + warp-MMA decode kernel (16-bit, head_dim 64/128,
  * one query row per request, group <= 16, page size a divisor or multiple of 64 and >= 8),
- * 0 = scalar kernel, negative = invalid arguments. */
+ * 0 = scalar kernel, negative = invalid arguments. With kv_int8: 1 = the decode kernel's int8
+ * instantiation (head_dim 128, one query row per request; K and V widened to fp16 in registers,
+ * fp16 warp MMAs), 0 = scalar kernel for everything else. */
 int rfx_paged_attention_kernel_kind(const RfxPagedAttentionArgs* a);
 int rfx_paged_attention_combine(const RfxPagedAttentionArgs* a);
 

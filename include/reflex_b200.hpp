@@ -35,7 +35,7 @@ struct KernelSupport {
     bool decode_attention = true;
     bool paged_decode_attention = true;
     bool rope = true;
-    bool kv_convert = false;  // int8 KV is not built
+    bool kv_convert = true;   // int8 KV with per-position scales: written by rfx_rope_append, read by paged decode
 };
 inline KernelSupport kernel_support() { return {}; }
 
@@ -67,6 +67,11 @@ struct PagedAttentionDecodeArgs {
     void* workspace = nullptr;          // paged_decode_workspace_bytes(args) bytes, 256-byte aligned
     std::size_t workspace_bytes = 0;
     StreamHandle stream = nullptr;
+    // int8 pool, as AttentionDecodeArgs::kv_int8 / k_scales / v_scales (infer.h:199-201): caches int8,
+    // one fp32 scale per (page, kv head, position), scales [num_blocks, n_kv_heads, block_size]
+    bool kv_int8 = false;
+    const float* k_scales = nullptr;
+    const float* v_scales = nullptr;
 };
 
 namespace detail {
@@ -81,6 +86,7 @@ inline RfxPagedAttentionArgs to_c(const PagedAttentionDecodeArgs& a) {
     c.max_q_len = 1; c.sm_scale = a.scale; c.is_causal = 1; c.rope_interleaved = a.rope_interleaved ? 1 : 0;
     c.dtype = static_cast<int>(a.dtype);
     c.workspace = a.workspace; c.workspace_bytes = a.workspace_bytes; c.stream = a.stream;
+    c.kv_int8 = a.kv_int8 ? 1 : 0; c.k_scales = a.k_scales; c.v_scales = a.v_scales;
     return c;
 }
 }  // namespace detail

@@ -15,6 +15,7 @@ __all__ = [
     "kv_paged_append", "kv_paged_scatter", "kv_paged_lookup", "kv_paged_lookup_as_written",
     "build_rope_tables", "apply_rope", "online_softmax", "attention", "naive_attention_f64",
     "paged_attention_composed", "bottom_right_mask", "merge_partials", "fused_linear_norm",
+    "kv_quantize_rows", "kv_paged_append_q8", "kv_dequantize",
 ]
 
 
@@ -203,6 +204,41 @@ def paged_attention_composed(q, k_cache, v_cache, block_table, context_lens, *,
         ob = attention(qb, kd, vd, attn_mask=mask, sm_scale=sm_scale)
         out[r0:r1] = ob[0].transpose(0, 1)
     return out
+
+
+# ---- int8 KV ------------------------------------------------------------------------
+# The reference has the reading side only: its decode kernel takes `kv_int8` with one fp32 scale per
+# (position, kv head) and widens a stored byte as int8 * scale (src/kernels/attention.cu:91-96,141-150;
+# args include/reflex/infer.h:189-203). It ships no quantiser, so the writing side is defined here and
+# the CUDA path is held to it bit for bit: symmetric absmax per row, fp32 arithmetic.
+
+def kv_quantize_rows(x: torch.Tensor):
+    """x [..., D] -> (int8 [..., D], float32 scale [...]): scale = max|x| / 127 (1 where the row is
+    all zero), q = round-half-even(x / scale), clamped to [-127, 127]."""
+    xf = x.float()
+    amax = xf.abs().amax(dim=-1)
+    scale = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
+    q = torch.round(xf / scale.unsqueeze(-1)).clamp_(-127, 127).to(torch.int8)
+    return q, scale
+
+
+def kv_paged_append_q8(k_in, v_in, k_cache, v_cache, k_scales, v_scales, slot_mapping) -> None:
+    """kv_paged_append (triton_kv_paged.py:279-292) into an int8 pool: caches int8
+    [num_blocks, H, bs, D], scales float32 [num_blocks, H, bs]."""
+    block_size = k_cache.shape[2]
+    page = torch.div(slot_mapping, block_size, rounding_mode="floor")
+    pos = torch.remainder(slot_mapping, block_size)
+    kq, ks = kv_quantize_rows(k_in)
+    vq, vs = kv_quantize_rows(v_in)
+    k_cache[page, :, pos, :] = kq
+    v_cache[page, :, pos, :] = vq
+    k_scales[page, :, pos] = ks
+    v_scales[page, :, pos] = vs
+
+
+def kv_dequantize(cache: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """int8 * scale in float32, the widening of src/kernels/attention.cu:94-96,145-147."""
+    return cache.float() * scales.unsqueeze(-1)
 
 
 def merge_partials(m: torch.Tensor, l: torch.Tensor, acc: torch.Tensor) -> torch.Tensor:

@@ -37,11 +37,14 @@ struct RowState {
 
 // Processes keys [j0, j1) (all visible) for one row. row_off(j) gives the element offset
 // of key j's row in the K and V arrays (or -1 when the key has no storage); bias(j) the
-// additive mask.
+// additive mask. int8 pools (T = int8_t) pass their per-row scales: score and probability
+// of key row r are multiplied by kscale[r] and vscale[r], r = element offset / D.
 template <typename T, typename RowOff, typename Bias>
 __device__ inline void attend_keys(RowState& st, const float* qs, const T* __restrict__ kbase,
                                    const T* __restrict__ vbase, int D, float scale, int j0, int j1,
-                                   bool vec_ok, RowOff row_off, Bias bias) {
+                                   bool vec_ok, RowOff row_off, Bias bias,
+                                   const float* __restrict__ kscale = nullptr,
+                                   const float* __restrict__ vscale = nullptr) {
     const int lane = threadIdx.x & 31;
     for (int jc = j0; jc < j1; jc += 32) {
         const int j = jc + lane;
@@ -49,7 +52,11 @@ __device__ inline void attend_keys(RowState& st, const float* qs, const T* __res
         float s = -INFINITY;
         if (j < j1) {
             off = row_off(j);
-            if (off >= 0) s = dot_row<T>(qs, kbase + off, D, vec_ok) * scale + bias(j);
+            if (off >= 0) {
+                s = dot_row<T>(qs, kbase + off, D, vec_ok);
+                if (kscale) s *= kscale[off / D];
+                s = s * scale + bias(j);
+            }
         }
         const float cm = warp_max(s);
         if (cm == -INFINITY) continue;  // nothing visible in this chunk
@@ -62,9 +69,10 @@ __device__ inline void attend_keys(RowState& st, const float* qs, const T* __res
         for (int k = 0; k < kMaxD / 32; ++k) st.acc[k] *= alpha;
         const int cnt = min(32, j1 - jc);
         for (int jj = 0; jj < cnt; ++jj) {
-            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            float pj = __shfl_sync(0xffffffffu, p, jj);
             const long long oj = __shfl_sync(0xffffffffu, off, jj);
             if (pj == 0.f || oj < 0) continue;
+            if (vscale) pj *= vscale[oj / D];
             const T* vr = vbase + oj;
 #pragma unroll
             for (int k = 0; k < kMaxD / 32; ++k) {
@@ -124,9 +132,10 @@ dense_attention_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
 // ---- paged items (split-K partials) ----------------------------------------------
 // One warp per partial row (item, query row, head in group). Rows are enumerated through
 // item_prow, found by binary search.
-template <typename T>
+template <typename T, typename KT>
 __global__ void __launch_bounds__(kGenWarps * 32)
-paged_partial_generic_kernel(const T* __restrict__ q, const T* __restrict__ kc, const T* __restrict__ vc,
+paged_partial_generic_kernel(const T* __restrict__ q, const KT* __restrict__ kc, const KT* __restrict__ vc,
+                             const float* __restrict__ kscale, const float* __restrict__ vscale,
                              const int64_t* __restrict__ block_table, const int32_t* __restrict__ ctx_lens,
                              const int32_t* __restrict__ q_start, const T* __restrict__ rcos,
                              const T* __restrict__ rsin, const int32_t* __restrict__ rpos,
@@ -184,7 +193,7 @@ paged_partial_generic_kernel(const T* __restrict__ q, const T* __restrict__ kc, 
         state_init(st);
         bool bad_page = false;
         if (kb < j1) {
-            attend_keys<T>(st, qsm[warp], kc, vc, D, scale, kb, j1, vec_ok != 0,
+            attend_keys<KT>(st, qsm[warp], kc, vc, D, scale, kb, j1, vec_ok != 0,
                            [&](int j) -> long long {
                                const int64_t lb = j / block_size;
                                if (lb >= max_blocks) { bad_page = true; return -1; }
@@ -192,7 +201,7 @@ paged_partial_generic_kernel(const T* __restrict__ q, const T* __restrict__ kc, 
                                if (page < 0 || page >= num_blocks) { bad_page = true; return -1; }
                                return ((page * Hkv + hkv) * block_size + (j - lb * block_size)) * (long long)D;
                            },
-                           [&](int) { return 0.f; });
+                           [&](int) { return 0.f; }, kscale, vscale);
         }
         if (bad_page) atomicOr(hdr + HdrStatus, kStatusBadPage);
         if (lane == 0) { pm[pr] = st.m; pl[pr] = st.l; }
@@ -206,15 +215,27 @@ paged_partial_generic_kernel(const T* __restrict__ q, const T* __restrict__ kc, 
 }
 
 int launch_paged_generic(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P) {
-    const size_t e = dtype_size(a->dtype);
+    const size_t e = a->kv_int8 ? 1 : dtype_size(a->dtype);
     const int D = (int)a->head_dim;
     const int vec_ok = ((D * e) % 16 == 0 && ((uintptr_t)a->k_cache % 16) == 0 && ((uintptr_t)a->v_cache % 16) == 0) ? 1 : 0;
     int64_t blocks = ceil_div<int64_t>(L.cap_rows, kGenWarps);
     const int64_t cap = (int64_t)sm_count() * 16;
     if (blocks > cap) blocks = cap;
+    if (a->kv_int8) {
+        RFX_DISPATCH_DTYPE(a->dtype, T, {
+            paged_partial_generic_kernel<T, int8_t><<<(int)blocks, kGenWarps * 32, 0, as_stream(a->stream)>>>(
+                (const T*)a->q, (const int8_t*)a->k_cache, (const int8_t*)a->v_cache, a->k_scales, a->v_scales,
+                a->block_table, a->context_lens,
+                a->q_start, (const T*)a->rope_cos, (const T*)a->rope_sin, a->rope_positions,
+                (int)a->num_q_heads, (int)a->num_kv_heads, D, a->num_blocks, (int)a->block_size, a->max_blocks,
+                a->bt_stride_b, a->table_rows, a->sm_scale, a->is_causal, a->rope_interleaved, vec_ok, P.hdr,
+                P.items, P.item_prow, P.m, P.l, P.acc);
+        });
+        return check_launch("rfx_paged_attention (scalar partial kernel, int8 pool)");
+    }
     RFX_DISPATCH_DTYPE(a->dtype, T, {
-        paged_partial_generic_kernel<T><<<(int)blocks, kGenWarps * 32, 0, as_stream(a->stream)>>>(
-            (const T*)a->q, (const T*)a->k_cache, (const T*)a->v_cache, a->block_table, a->context_lens,
+        paged_partial_generic_kernel<T, T><<<(int)blocks, kGenWarps * 32, 0, as_stream(a->stream)>>>(
+            (const T*)a->q, (const T*)a->k_cache, (const T*)a->v_cache, nullptr, nullptr, a->block_table, a->context_lens,
             a->q_start, (const T*)a->rope_cos, (const T*)a->rope_sin, a->rope_positions,
             (int)a->num_q_heads, (int)a->num_kv_heads, D, a->num_blocks, (int)a->block_size, a->max_blocks,
             a->bt_stride_b, a->table_rows, a->sm_scale, a->is_causal, a->rope_interleaved, vec_ok, P.hdr,

@@ -43,6 +43,9 @@ template <> struct Num<__nv_bfloat16> {
     __device__ static float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
     __device__ static __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
 };
+template <> struct Num<int8_t> {  // int8 KV pool: the stored integer; its scale is applied by the caller
+    __device__ static float to_f(int8_t v) { return (float)v; }
+};
 template <> struct Num<__half> {
     __device__ static float to_f(__half v) { return __half2float(v); }
     __device__ static __half from_f(float v) { return __float2half_rn(v); }

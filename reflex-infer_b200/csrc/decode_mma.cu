@@ -58,18 +58,23 @@ struct DecodeParams {
     int Hq, Hkv, G, block_size, box_rows, rope_inter;
     int map2d;         // 1: the maps are 2-D [rows, D] with {64, box_rows} boxes, one copy per 128-byte half
     float scale_log2;  // sm_scale * log2(e)
+    const float* k_scales;  // int8 pool: one fp32 scale per (page, kv head, position), else nullptr
+    const float* v_scales;
 };
 
-template <int HD, int GP, int STAGES>
+template <int HD, int GP, int STAGES, bool Q8 = false>
 struct DecodeSmem {
-    static constexpr int kRowBytes = HD * 2;
-    static constexpr int kTileBytes = kTile * kRowBytes;  // K or V of one stage
+    static constexpr int kRowBytes = HD * 2;              // a query or table row (16-bit)
+    static constexpr int kKvRowBytes = Q8 ? HD : HD * 2;  // a key or value row
+    static constexpr int kTileBytes = kTile * kKvRowBytes;  // K or V of one stage
     static constexpr int kAccStride = HD + kAccPad;
     static constexpr int kQBytes = GP * kRowBytes;        // raw query rows of the group
     static constexpr int kQSlot = kQBytes + 2 * kRowBytes;  // + cos row + sin row
+    static constexpr int kScaleSlot = Q8 ? 2 * kTile * 4 : 0;  // int8: the stage's K scales, then its V scales
     static constexpr size_t off_k = 0;
     static constexpr size_t off_v = (size_t)STAGES * kTileBytes;
-    static constexpr size_t off_q = 2 * (size_t)STAGES * kTileBytes;
+    static constexpr size_t off_sc = 2 * (size_t)STAGES * kTileBytes;
+    static constexpr size_t off_q = off_sc + (size_t)STAGES * kScaleSlot;
     static constexpr size_t off_merge = off_q + (size_t)STAGES * kQSlot;
     static constexpr size_t merge_bytes = (size_t)kGroupWarps * GP * kAccStride * 4;
     static constexpr size_t off_ml = off_merge + merge_bytes;             // [group warps][GP][2]
@@ -98,11 +103,37 @@ template <typename T> __device__ inline uint32_t pack_t(T a, T b) {
     return (uint32_t)lo | ((uint32_t)hi << 16);
 }
 
+// Four int8 (two's complement) in `wx`, already xor-ed with 0x80 (value + 128 as an unsigned byte): the two
+// picked by `sel` (a byte-permute selector that puts each next to the byte 0x64) become fp16 1024 + byte;
+// minus 1152 gives the signed value, exactly.
+__device__ __forceinline__ uint32_t q8_pair_to_h2(uint32_t wx, uint32_t sel) {
+    uint32_t t = __byte_perm(wx, 0x64646464u, sel);
+    const uint32_t bias = 0x64806480u;  // 1152.0, twice
+    __half2 r = __hsub2(*reinterpret_cast<__half2*>(&t), *reinterpret_cast<const __half2*>(&bias));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// Two elements of T side by side in the type the warp MMA runs in: T itself, or fp16 when the pool is
+// int8 (the widened K and V are fp16, so Q has to be too; a bf16 value is exact in fp16 unless it is
+// below 2^-14 in magnitude or above 65504).
+template <typename T, bool Q8> __device__ inline uint32_t pack_mma(T a, T b) {
+    if (Q8 && !std::is_same<T, __half>::value) {
+        __half2 h = __floats2half2_rn(Num<T>::to_f(a), Num<T>::to_f(b));
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+    const uint16_t lo = *reinterpret_cast<uint16_t*>(&a), hi = *reinterpret_cast<uint16_t*>(&b);
+    return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+
 // Builds the A fragments of Q for the item's G heads from the stage's query slot
 // (raw rows, then the cos row, then the sin row), rotating when asked.
 // qa[ks][0] = row g,   dims 16ks + 2c + {0,1};   qa[ks][1] = row g+8, same dims;
 // qa[ks][2] = row g,   dims 16ks + 8 + 2c + ..;  qa[ks][3] = row g+8      (c = lane % 4).
-template <typename T, int HD, int GP>
+//
+// Q8 (int8 pool): ldmatrix hands a thread four consecutive int8 of a key row, i.e. dims 4c..4c+3 of a
+// 16-dim chunk, so the contraction index of the MMA is permuted inside each chunk: MMA columns
+// 2c, 2c+1 stand for dims 4c, 4c+1 and columns 2c+8, 2c+9 for dims 4c+2, 4c+3. The Q fragments follow.
+template <typename T, int HD, int GP, bool Q8>
 __device__ inline void load_q_frags(uint32_t (&qa)[HD / 16][4], const unsigned char* slot, int G, bool rotate,
                                     bool interleaved) {
     const int lane = threadIdx.x & 31;
@@ -110,6 +141,41 @@ __device__ inline void load_q_frags(uint32_t (&qa)[HD / 16][4], const unsigned c
     const T* qs = reinterpret_cast<const T*>(slot);
     const T* cr = qs + GP * HD;
     const T* sr = cr + HD;
+    if constexpr (Q8) {
+#pragma unroll
+        for (int rr = 0; rr < (GP > 8 ? 2 : 1); ++rr) {
+            const int g = g0 + 8 * rr;
+            const bool live = g < G;
+            const T* qr = qs + g * HD;
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+                T y[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int d = 16 * ks + 4 * c + e;
+                    y[e] = live ? qr[d] : Num<T>::from_f(0.f);
+                    if (live && rotate) {
+                        T y1, y2;
+                        if (interleaved) {
+                            const int d0 = d & ~1;
+                            rope_pair<T>(qr[d0], qr[d0 + 1], cr[d0], sr[d0], y1, y2);
+                            y[e] = (d & 1) ? y2 : y1;
+                        } else {
+                            const int d0 = d < HD / 2 ? d : d - HD / 2;
+                            rope_pair<T>(qr[d0], qr[d0 + HD / 2], cr[d0], sr[d0], y1, y2);
+                            y[e] = d < HD / 2 ? y1 : y2;
+                        }
+                    }
+                }
+                qa[ks][rr] = pack_mma<T, true>(y[0], y[1]);
+                qa[ks][2 + rr] = pack_mma<T, true>(y[2], y[3]);
+            }
+        }
+        if (GP <= 8) {
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) { qa[ks][1] = 0; qa[ks][3] = 0; }
+        }
+    } else {
 #pragma unroll
     for (int rr = 0; rr < (GP > 8 ? 2 : 1); ++rr) {
         const int g = g0 + 8 * rr;
@@ -166,14 +232,16 @@ __device__ inline void load_q_frags(uint32_t (&qa)[HD / 16][4], const unsigned c
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) { qa[ks][1] = 0; qa[ks][3] = 0; }
     }
+}  // not Q8
 }
 
-template <typename T, int HD, int GP, int STAGES, int GROUPS>
+template <typename T, int HD, int GP, int STAGES, int GROUPS, bool Q8>
 __global__ void __launch_bounds__((kGroupWarps * GROUPS + 1) * 32, 1)
 decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                   const DecodeParams P) {
-    using S = DecodeSmem<HD, GP, STAGES>;
-    constexpr bool BF = std::is_same<T, __nv_bfloat16>::value;
+    using S = DecodeSmem<HD, GP, STAGES, Q8>;
+    constexpr bool BF = std::is_same<T, __nv_bfloat16>::value && !Q8;  // the type of the warp MMAs
+    using PT = typename std::conditional<Q8, __half, T>::type;         // ... and of the packed probabilities
     constexpr int kConsumers = kGroupWarps * GROUPS;
     extern __shared__ unsigned char smem_raw[];
     // TMA's 128-byte swizzle is a function of the shared-memory address, so tiles must
@@ -182,6 +250,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     unsigned char* sK = smem + S::off_k;
     unsigned char* sV = smem + S::off_v;
     unsigned char* sQ = smem + S::off_q;
+    float* sScale = reinterpret_cast<float*>(smem + S::off_sc);  // int8 pool only
     float* sAcc = reinterpret_cast<float*>(smem + S::off_merge);
     float* sML = reinterpret_cast<float*>(smem + S::off_ml);
     StageMeta* sMeta = reinterpret_cast<StageMeta*>(smem + S::off_meta);
@@ -190,7 +259,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int R = P.box_rows;                 // rows per TMA box = min(block_size, 64)
-    const uint32_t box_bytes = (uint32_t)R * S::kRowBytes;
+    const uint32_t box_bytes = (uint32_t)R * S::kKvRowBytes;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -302,7 +371,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             m.bad = wantmask & ~okmask;
                             sMeta[stage] = m;
                             if (okmask != wantmask) atomicOr(P.hdr + HdrStatus, kStatusBadPage);
-                            uint32_t tx = 2u * box_bytes * (uint32_t)__popc(okmask);
+                            uint32_t tx = (2u * box_bytes + (Q8 ? 8u * (uint32_t)R : 0u)) * (uint32_t)__popc(okmask);
                             if (t == 0) tx += q_bytes + (rotate ? 2u * S::kRowBytes : 0u);
                             ptx::mbar_arrive_expect_tx(&full[stage], tx);
                         }
@@ -311,7 +380,14 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             const int row = (int)((my_page * P.Hkv + hkv) * P.block_size + my_row0);
                             unsigned char* kd = sK + (size_t)stage * S::kTileBytes + (size_t)lane * box_bytes;
                             unsigned char* vd = sV + (size_t)stage * S::kTileBytes + (size_t)lane * box_bytes;
-                            if (!P.map2d) {
+                            if (Q8) {
+                                // a row is one 128-byte line; the scales of the box's keys ride along
+                                ptx::tma_load_2d(kd, &kmap, &full[stage], 0, row);
+                                ptx::tma_load_2d(vd, &vmap, &full[stage], 0, row);
+                                float* sc = sScale + (size_t)stage * (2 * kTile) + lane * R;
+                                ptx::bulk_load(sc, P.k_scales + row, (uint32_t)R * 4u, &full[stage]);
+                                ptx::bulk_load(sc + kTile, P.v_scales + row, (uint32_t)R * 4u, &full[stage]);
+                            } else if (!P.map2d) {
                                 ptx::tma_load_3d(kd, &kmap, &full[stage], 0, row, 0);
                                 ptx::tma_load_3d(vd, &vmap, &full[stage], 0, row, 0);
                             } else {
@@ -370,6 +446,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     constexpr int NT = GP / 8;  // head n-tiles
     const int group = warp / kGroupWarps, wq = warp % kGroupWarps;
     const int r8 = lane >> 2, c4 = lane & 3;
+    // dims (inside a 16-dim block) of the accumulator rows r8 and r8 + 8 of this thread
+    const int dim_lo = Q8 ? 2 * r8 : r8, dim_hi = Q8 ? 2 * r8 + 1 : 8 + r8;
     uint32_t qa[HD / 16][4];
     float o[HD / 16][NT][4];
     float m_run[NT][2], l_run[NT][2];
@@ -380,7 +458,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     const int v_tok = wq * 16 + (mat >> 1) * 8 + rowi;  // V (A operand, transposed): matrices 0,1 keys 0-7; 2,3 keys 8-15
     const int k_box = k_tok / R, k_r = k_tok - k_box * R;
     const int v_box = v_tok / R, v_r = v_tok - v_box * R;
-    const uint32_t k_rowoff = (uint32_t)k_box * box_bytes + (uint32_t)k_r * 128u;
+    const uint32_t k_rowoff = (uint32_t)k_box * box_bytes + (uint32_t)k_r * 128u;  // int8: a row is one 128-byte line
     const uint32_t v_rowoff = (uint32_t)v_box * box_bytes + (uint32_t)v_r * 128u;
     const uint32_t half_bytes = (uint32_t)R * 128u;
     const uint32_t k_sw = (uint32_t)(k_r & 7), v_sw = (uint32_t)(v_r & 7);
@@ -398,7 +476,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         const StageMeta meta = sMeta[stage];
         if (meta.item < 0) break;
         if (meta.flags & 1) {
-            load_q_frags<T, HD, GP>(qa, sQ + (size_t)stage * S::kQSlot, P.G, (meta.flags & 4) != 0, P.rope_inter != 0);
+            load_q_frags<T, HD, GP, Q8>(qa, sQ + (size_t)stage * S::kQSlot, P.G, (meta.flags & 4) != 0, P.rope_inter != 0);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) { m_run[nt][0] = m_run[nt][1] = -INFINITY; l_run[nt][0] = l_run[nt][1] = 0.f; }
 #pragma unroll
@@ -417,7 +495,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             // zero but 0*NaN would poison P.V, so those V rows are cleared.
             const bool tail = meta.n_valid < slice0 + 16 || meta.bad != 0;
             auto dead = [&](int tk) -> bool { return tk >= meta.n_valid || ((meta.bad >> (tk / R)) & 1u); };
-            if (tail) {
+            if (tail && !Q8) {
                 unsigned char* vs = sV + (size_t)stage * S::kTileBytes;
                 for (int i = lane; i < 16 * (S::kRowBytes / 16); i += 32) {
                     const int tk = slice0 + i / (S::kRowBytes / 16);
@@ -437,6 +515,39 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
+            // int8 pool: the scales of this thread's two keys (rows r8 and r8 + 8 of the slice); a key that
+            // does not count gets a zero V scale, since its scale word may be anything
+            float ksl[2] = {P.scale_log2, P.scale_log2}, vsc[2] = {1.f, 1.f};
+            if (Q8) {
+                const float* sc = sScale + (size_t)stage * (2 * kTile) + slice0 + r8;
+                ksl[0] = sc[0] * P.scale_log2; ksl[1] = sc[8] * P.scale_log2;
+                vsc[0] = sc[kTile]; vsc[1] = sc[kTile + 8];
+                if (tail) {
+                    if (dead(slice0 + r8)) vsc[0] = 0.f;
+                    if (dead(slice0 + r8 + 8)) vsc[1] = 0.f;
+                }
+            }
+            if (Q8) {
+                // a 16-byte chunk holds 16 dims: one ldmatrix.x4 feeds two k-steps
+#pragma unroll
+                for (int j = 0; j < HD / 32; ++j) {
+                    const uint32_t chunk = (uint32_t)(2 * j + (mat >> 1));
+                    const uint32_t addr = kst + k_rowoff + (((chunk & 7u) ^ k_sw) << 4);
+                    uint32_t w0, w1, w2, w3;
+                    ptx::ldmatrix_x4(addr, w0, w1, w2, w3);
+                    w0 ^= 0x80808080u; w1 ^= 0x80808080u; w2 ^= 0x80808080u; w3 ^= 0x80808080u;
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const uint32_t lo = hh ? w2 : w0, hi = hh ? w3 : w1;  // keys 0-7 / keys 8-15 of the slice
+                        const uint32_t a0 = q8_pair_to_h2(lo, 0x4140), a1 = q8_pair_to_h2(hi, 0x4140);
+                        const uint32_t a2 = q8_pair_to_h2(lo, 0x4342), a3 = q8_pair_to_h2(hi, 0x4342);
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt)
+                            ptx::mma_16816<BF>(s[nt][0], s[nt][1], s[nt][2], s[nt][3], a0, a1, a2, a3, qa[2 * j + hh][nt],
+                                               qa[2 * j + hh][2 + nt], s[nt][0], s[nt][1], s[nt][2], s[nt][3]);
+                    }
+                }
+            } else {
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
                 const uint32_t chunk = (uint32_t)(2 * ks + (mat >> 1));
@@ -448,6 +559,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     ptx::mma_16816<BF>(s[nt][0], s[nt][1], s[nt][2], s[nt][3], a0, a1, a2, a3, qa[ks][nt],
                                        qa[ks][2 + nt], s[nt][0], s[nt][1], s[nt][2], s[nt][3]);
             }
+            }
             // ---- online softmax down the columns (base-2 domain). Fast path: nothing exceeds
             // the running column maxima (the usual case after the first tiles), so the
             // probabilities come straight from one FMA and one EX2 each; only when some
@@ -458,7 +570,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 float t[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    t[i] = fmaf(s[nt][i], P.scale_log2, -m_run[nt][i & 1]);  // +inf while m_run is -inf
+                    t[i] = fmaf(s[nt][i], ksl[i >> 1], -m_run[nt][i & 1]);  // +inf while m_run is -inf
                     if (tail && dead(slice0 + r8 + 8 * (i >> 1))) t[i] = -INFINITY;
                 }
                 const bool exceeds = fmaxf(fmaxf(t[0], t[1]), fmaxf(t[2], t[3])) > 0.f;
@@ -466,7 +578,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     float v[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        v[i] = s[nt][i] * P.scale_log2;
+                        v[i] = s[nt][i] * ksl[i >> 1];
                         if (tail && dead(slice0 + r8 + 8 * (i >> 1))) v[i] = -INFINITY;
                     }
                     float mx0 = fmaxf(v[0], v[2]), mx1 = fmaxf(v[1], v[3]);
@@ -492,10 +604,35 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 l_run[nt][0] += p0 + p2;
                 l_run[nt][1] += p1 + p3;
                 // C fragment (key rows, head cols) -> B fragment (k = key, n = head)
-                pb[nt][0] = ptx::movmatrix_trans(Pack2<T>::pack(p0, p1));  // keys 0-7 of the slice
-                pb[nt][1] = ptx::movmatrix_trans(Pack2<T>::pack(p2, p3));  // keys 8-15
+                // (int8 pool: the V scale of the key goes into its probability; the row sums above do not see it)
+                pb[nt][0] = ptx::movmatrix_trans(Pack2<PT>::pack(p0 * vsc[0], p1 * vsc[0]));  // keys 0-7 of the slice
+                pb[nt][1] = ptx::movmatrix_trans(Pack2<PT>::pack(p2 * vsc[1], p3 * vsc[1]));  // keys 8-15
             }
             // ---- O^T += V^T.P^T : rows = 16 dims per tile, cols = heads
+            if (Q8) {
+                // The transposing load moves 16-bit units, i.e. pairs of neighbouring dims: a thread ends up
+                // with dims (2e, 2e+1) of keys (2c, 2c+1), e = lane / 4. MMA row e then stands for dim 2e of
+                // the 16-dim block and row e + 8 for dim 2e + 1; the accumulators are read out accordingly.
+#pragma unroll
+                for (int j2 = 0; j2 < HD / 32; ++j2) {
+                    const uint32_t chunk = (uint32_t)(2 * j2 + (mat & 1));
+                    const uint32_t addr = vst + v_rowoff + (((chunk & 7u) ^ v_sw) << 4);
+                    uint32_t w0, w1, w2, w3;  // (keys 0-7, block 2j2) (keys 0-7, block 2j2+1) (keys 8-15, 2j2) (keys 8-15, 2j2+1)
+                    ptx::ldmatrix_x4_trans(addr, w0, w1, w2, w3);
+                    w0 ^= 0x80808080u; w1 ^= 0x80808080u; w2 ^= 0x80808080u; w3 ^= 0x80808080u;
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const uint32_t lo = hh ? w1 : w0, hi = hh ? w3 : w2;
+                        const uint32_t a0 = q8_pair_to_h2(lo, 0x4240), a1 = q8_pair_to_h2(lo, 0x4341);
+                        const uint32_t a2 = q8_pair_to_h2(hi, 0x4240), a3 = q8_pair_to_h2(hi, 0x4341);
+                        const int j = 2 * j2 + hh;
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt)
+                            ptx::mma_16816<BF>(o[j][nt][0], o[j][nt][1], o[j][nt][2], o[j][nt][3], a0, a1, a2, a3, pb[nt][0],
+                                               pb[nt][1], o[j][nt][0], o[j][nt][1], o[j][nt][2], o[j][nt][3]);
+                    }
+                }
+            } else {
 #pragma unroll
             for (int j = 0; j < HD / 16; ++j) {
                 const uint32_t chunk = (uint32_t)(2 * j + (mat & 1));
@@ -506,6 +643,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 for (int nt = 0; nt < NT; ++nt)
                     ptx::mma_16816<BF>(o[j][nt][0], o[j][nt][1], o[j][nt][2], o[j][nt][3], a0, a1, a2, a3, pb[nt][0],
                                        pb[nt][1], o[j][nt][0], o[j][nt][1], o[j][nt][2], o[j][nt][3]);
+            }
             }
         }
         // release the stage to the producer
@@ -542,8 +680,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         float* ar = sAcc + (size_t)(wq * GP + g) * S::kAccStride;
 #pragma unroll
                         for (int j = 0; j < HD / 16; ++j) {
-                            ar[16 * j + r8] = o[j][nt][i];
-                            ar[16 * j + 8 + r8] = o[j][nt][2 + i];
+                            ar[16 * j + dim_lo] = o[j][nt][i];
+                            ar[16 * j + dim_hi] = o[j][nt][2 + i];
                         }
                     }
             };
@@ -565,8 +703,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         const float* ar = sAcc + (size_t)(wq * GP + g) * S::kAccStride;
 #pragma unroll
                         for (int j = 0; j < HD / 16; ++j) {
-                            o[j][nt][i] = o[j][nt][i] * wa + ar[16 * j + r8] * wb;
-                            o[j][nt][2 + i] = o[j][nt][2 + i] * wa + ar[16 * j + 8 + r8] * wb;
+                            o[j][nt][i] = o[j][nt][i] * wa + ar[16 * j + dim_lo] * wb;
+                            o[j][nt][2 + i] = o[j][nt][2 + i] * wa + ar[16 * j + dim_hi] * wb;
                         }
                         l_tot[nt][i] = l_tot[nt][i] * wa + lb * wb;
                         m_run[nt][i] = M;
@@ -665,6 +803,20 @@ static int encode_rows_map_2d(CUtensorMap* map, const void* base, uint64_t rows,
     return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+// int8 pool: [rows, 128] bytes, one 128-byte line per key row, {128, box_rows} boxes.
+static int encode_rows_map_u8(CUtensorMap* map, const void* base, uint64_t rows, uint32_t row_bytes, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return -1;
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {row_bytes, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
 static bool box_rows_ok(int64_t bs) {
     if (bs >= 64) return bs % 64 == 0;
     return bs >= 8 && 64 % bs == 0;
@@ -675,6 +827,8 @@ bool decode_mma_shape_ok(const RfxPagedAttentionArgs* a) {
     if (a->force_generic) return false;
     if (a->dtype != RFX_BF16 && a->dtype != RFX_F16) return false;
     if (a->head_dim != 128 && a->head_dim != 64) return false;
+    if (a->kv_int8 && (a->head_dim != 128 || ((uintptr_t)a->k_scales % 16) || ((uintptr_t)a->v_scales % 16)))
+        return false;  // an int8 row has to be one 128-byte line
     const int64_t G = a->num_q_heads / a->num_kv_heads;
     if (G > 16) return false;
     if ((G * a->head_dim * 2) % 16) return false;  // bulk copies move multiples of 16 bytes
@@ -692,12 +846,12 @@ bool decode_mma_supported(const RfxPagedAttentionArgs* a) {
 
 int decode_mma_ctas(const RfxPagedAttentionArgs*) { return sm_count(); }
 
-template <typename T, int HD, int GP, int STAGES, int GROUPS = 1>
+template <typename T, int HD, int GP, int STAGES, int GROUPS = 1, bool Q8 = false>
 static int launch_decode_t(const RfxPagedAttentionArgs* a, const CUtensorMap& km, const CUtensorMap& vm,
                            const DecodeParams& P) {
-    using S = DecodeSmem<HD, GP, STAGES>;
+    using S = DecodeSmem<HD, GP, STAGES, Q8>;
     static_assert(S::total <= 232448, "decode kernel shared memory exceeds the sm_100 per-CTA limit");
-    auto kern = decode_mma_kernel<T, HD, GP, STAGES, GROUPS>;
+    auto kern = decode_mma_kernel<T, HD, GP, STAGES, GROUPS, Q8>;
     static bool attr_set[64] = {};  // per instantiation and device
     int dev = 0;
     cudaGetDevice(&dev);
@@ -725,12 +879,17 @@ int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const P
     }
     int map2d = force_2d;
     int r1 = 0, r2 = 0;
-    if (!map2d) {
+    if (a->kv_int8) {
+        map2d = 0;
+        r1 = encode_rows_map_u8(&km, a->k_cache, rows, (uint32_t)HD, (uint32_t)R);
+        r2 = encode_rows_map_u8(&vm, a->v_cache, rows, (uint32_t)HD, (uint32_t)R);
+        if (r1 || r2) return fail(RFX_CUDA_ERROR, "cuTensorMapEncodeTiled (int8 pool) failed (%d, %d)", r1, r2);
+    } else if (!map2d) {
         r1 = encode_rows_map_3d(&km, a->k_cache, rows, (uint32_t)HD, (uint32_t)R);
         r2 = encode_rows_map_3d(&vm, a->v_cache, rows, (uint32_t)HD, (uint32_t)R);
         if (r1 || r2) map2d = 1;
     }
-    if (map2d) {
+    if (map2d && !a->kv_int8) {
         r1 = encode_rows_map_2d(&km, a->k_cache, rows, (uint32_t)HD, (uint32_t)R);
         r2 = encode_rows_map_2d(&vm, a->v_cache, rows, (uint32_t)HD, (uint32_t)R);
         if (r1 || r2) return fail(RFX_CUDA_ERROR, "cuTensorMapEncodeTiled failed (%d, %d)", r1, r2);
@@ -748,6 +907,17 @@ int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const P
     P.block_size = (int)a->block_size; P.box_rows = R; P.rope_inter = a->rope_interleaved;
     P.scale_log2 = a->sm_scale * 1.4426950408889634f;
     P.map2d = map2d;
+    P.k_scales = a->kv_int8 ? a->k_scales : nullptr;
+    P.v_scales = a->kv_int8 ? a->v_scales : nullptr;
+    if (a->kv_int8) {
+        // half the bytes per stage: ten (eight) stages fit where the 16-bit pool has six (five)
+        if (a->dtype == RFX_BF16) {
+            if (G <= 8) return launch_decode_t<__nv_bfloat16, 128, 8, 10, 1, true>(a, km, vm, P);
+            return launch_decode_t<__nv_bfloat16, 128, 16, 8, 1, true>(a, km, vm, P);
+        }
+        if (G <= 8) return launch_decode_t<__half, 128, 8, 10, 1, true>(a, km, vm, P);
+        return launch_decode_t<__half, 128, 16, 8, 1, true>(a, km, vm, P);
+    }
 
 #define RFX_DECODE_CASE(T)                                                                   \
     if (HD == 128) {                                                                         \

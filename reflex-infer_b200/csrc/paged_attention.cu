@@ -23,6 +23,7 @@ static int validate(const RfxPagedAttentionArgs* a, const char* name) {
     RFX_REQUIRE((a->rope_cos == nullptr) == (a->rope_sin == nullptr), "%s: rope_cos and rope_sin go together", name);
     RFX_REQUIRE(a->rope_cos == nullptr || (a->rope_positions != nullptr && a->head_dim % 2 == 0),
                 "%s: fused RoPE needs rope_positions and an even head_dim", name);
+    RFX_REQUIRE(!a->kv_int8 || (a->k_scales && a->v_scales), "%s: an int8 pool needs k_scales and v_scales", name);
     return RFX_SUCCESS;
 }
 

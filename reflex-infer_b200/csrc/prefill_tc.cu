@@ -665,6 +665,7 @@ int launch_dense_tensor(const RfxAttentionArgs* a) {
 bool prefill_paged_supported(const RfxPagedAttentionArgs* a) {
     if (a->force_generic || getenv("REFLEX_B200_NO_TC")) return false;
     if (a->dtype != RFX_BF16 && a->dtype != RFX_F16) return false;
+    if (a->kv_int8) return false;  // query chunks over an int8 pool run the scalar kernel
     if (a->head_dim != kPfHD || a->rope_cos) return false;
     if (a->q_start == nullptr || a->max_q_len < 1) return false;
     const int64_t G = a->num_q_heads / a->num_kv_heads;

@@ -201,6 +201,88 @@ rope_append_kernel(const T* __restrict__ k_in, const T* __restrict__ v_in, const
     }
 }
 
+// Fused RoPE + append into an int8 pool: one warp per row of a token -- [0, Hkv) K rotate and
+// quantise, [Hkv, 2Hkv) V quantise, then Hq Q rows rotated in T. The rotation carries the same per-op
+// rounding as above, so the values that are quantised are the rows the 16-bit pool would hold.
+// Quantiser (fp32): scale = max|x| / 127 (1 for an all-zero row), q = rint(x / scale).
+template <typename T, bool INTER>
+__global__ void __launch_bounds__(256)
+rope_append_q8_kernel(const T* __restrict__ k_in, const T* __restrict__ v_in, const T* q_in, T* q_out,
+                      int8_t* __restrict__ k_cache, int8_t* __restrict__ v_cache, float* __restrict__ k_scales,
+                      float* __restrict__ v_scales, const int64_t* __restrict__ slots,
+                      const int32_t* __restrict__ positions, const T* __restrict__ cosb,
+                      const T* __restrict__ sinb, int64_t N, int Hq, int Hkv, int D, int64_t num_slots,
+                      int block_size, int64_t table_rows) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the split-K plan may start alongside
+    constexpr int kMaxPairs = 4;  // head_dim <= 256: at most 4 pairs per lane
+    const int lane = threadIdx.x & 31;
+    const int rows_per_tok = 2 * Hkv + Hq;
+    const int64_t total = N * rows_per_tok;
+    const int half = D >> 1;
+    for (int64_t w = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5; w < total;
+         w += ((int64_t)gridDim.x * blockDim.x) >> 5) {
+        const int row = (int)(w % rows_per_tok);
+        const int64_t n = w / rows_per_tok;
+        const int64_t pos = positions[n];
+        if (pos < 0 || pos >= table_rows) continue;  // no table row: leave the token untouched
+        const bool is_v = row >= Hkv && row < 2 * Hkv;
+        const bool is_q = row >= 2 * Hkv;
+        const int h = is_q ? row - 2 * Hkv : (is_v ? row - Hkv : row);
+        const T* x = is_q ? q_in + (n * Hq + h) * D : (is_v ? v_in : k_in) + (n * Hkv + h) * D;
+        // element pairs (d1, d2) of this lane, rotated unless this is a V row
+        float y1[kMaxPairs], y2[kMaxPairs];
+        T t1[kMaxPairs], t2[kMaxPairs];
+        float amax = 0.f;
+#pragma unroll
+        for (int k = 0; k < kMaxPairs; ++k) {
+            const int p = lane + 32 * k;
+            y1[k] = y2[k] = 0.f;
+            if (p >= half) continue;
+            const int d1 = INTER ? 2 * p : p, d2 = INTER ? 2 * p + 1 : p + half;
+            T a = x[d1], b = x[d2];
+            if (!is_v) {
+                const T* cr = cosb + pos * D;
+                const T* sr = sinb + pos * D;
+                T r1, r2;
+                rope_pair<T>(a, b, cr[d1], sr[d1], r1, r2);
+                a = r1; b = r2;
+            }
+            t1[k] = a; t2[k] = b;
+            y1[k] = Num<T>::to_f(a); y2[k] = Num<T>::to_f(b);
+            amax = fmaxf(amax, fmaxf(fabsf(y1[k]), fabsf(y2[k])));
+        }
+        if (is_q) {
+            T* y = q_out + (n * Hq + h) * D;
+#pragma unroll
+            for (int k = 0; k < kMaxPairs; ++k) {
+                const int p = lane + 32 * k;
+                if (p >= half) continue;
+                y[INTER ? 2 * p : p] = t1[k];
+                y[INTER ? 2 * p + 1 : p + half] = t2[k];
+            }
+            continue;
+        }
+        const int64_t slot = slots[n];
+        if (slot < 0 || slot >= num_slots) continue;
+        const int64_t page = slot / block_size;
+        const int at = (int)(slot - page * block_size);
+        amax = warp_max(amax);
+        const float scale = amax > 0.f ? __fdiv_rn(amax, 127.f) : 1.f;
+        const int64_t r = (page * Hkv + h) * block_size + at;
+        int8_t* dst = (is_v ? v_cache : k_cache) + r * D;
+        if (lane == 0) (is_v ? v_scales : k_scales)[r] = scale;
+#pragma unroll
+        for (int k = 0; k < kMaxPairs; ++k) {
+            const int p = lane + 32 * k;
+            if (p >= half) continue;
+            const float q1 = fminf(127.f, fmaxf(-127.f, rintf(__fdiv_rn(y1[k], scale))));
+            const float q2 = fminf(127.f, fmaxf(-127.f, rintf(__fdiv_rn(y2[k], scale))));
+            dst[INTER ? 2 * p : p] = (int8_t)q1;
+            dst[INTER ? 2 * p + 1 : p + half] = (int8_t)q2;
+        }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 rope_table_kernel(T* __restrict__ cosb, T* __restrict__ sinb, const float* __restrict__ inv_freq,
@@ -354,6 +436,25 @@ extern "C" int rfx_rope_append(const RfxRopeAppendArgs* a) {
     const size_t e = dtype_size(a->dtype);
     const int D = (int)a->head_dim;
     const bool inter = a->interleaved != 0;
+    if (a->kv_int8) {
+        RFX_REQUIRE(a->k_scales && a->v_scales, "%s: an int8 pool needs k_scales and v_scales", name);
+        RFX_REQUIRE(D <= 256, "%s: head_dim %d > 256", name, D);
+        const int Hq8 = has_q ? (int)a->num_q_heads : 0;
+        const int64_t warps = a->n_tokens * (2 * a->num_kv_heads + Hq8);
+        const int grid8 = grid_for(warps * 32);
+        cudaStream_t s8 = as_stream(a->stream);
+#define RFX_RA8(T, II)                                                                                        \
+    rope_append_q8_kernel<T, II><<<grid8, 256, 0, s8>>>(                                                      \
+        (const T*)a->k_in, (const T*)a->v_in, (const T*)a->q_in, (T*)a->q_out, (int8_t*)a->k_cache,           \
+        (int8_t*)a->v_cache, a->k_scales, a->v_scales, a->slot_mapping, a->positions, (const T*)a->cos,       \
+        (const T*)a->sin, a->n_tokens, Hq8, (int)a->num_kv_heads, D, a->num_blocks * a->block_size,           \
+        (int)a->block_size, a->table_rows)
+        RFX_DISPATCH_DTYPE(a->dtype, T, {
+            if (inter) RFX_RA8(T, true); else RFX_RA8(T, false);
+        });
+#undef RFX_RA8
+        return check_launch(name);
+    }
     const size_t q[] = {(size_t)a->k_in,
                         (size_t)a->v_in,
                         (size_t)a->q_in,

@@ -85,6 +85,7 @@ class RopeAppendArgs(C.Structure):
         ("num_blocks", i64), ("block_size", i64), ("table_rows", i64),
         ("cache_stride_blk", i64), ("cache_stride_h", i64), ("cache_stride_pos", i64),
         ("interleaved", C.c_int), ("dtype", C.c_int), ("stream", vp),
+        ("kv_int8", C.c_int), ("k_scales", vp), ("v_scales", vp),
     ]
 
 
@@ -116,6 +117,7 @@ class PagedAttentionArgs(C.Structure):
         ("reuse_plan", C.c_int), ("force_generic", C.c_int),
         ("target_chunk", i64),
         ("workspace", vp), ("workspace_bytes", C.c_size_t), ("stream", vp),
+        ("kv_int8", C.c_int), ("k_scales", vp), ("v_scales", vp),
     ]
 
 

@@ -13,6 +13,12 @@ Paged (additive; none of them changes the functions above):
     ``paged_decode_step``  ``rope_append`` + ``paged_decode`` for one decode step
     ``PagedWorkspace``     caller-owned scratch for the split-K plan and partials
     ``splitk_combine``     merge caller-provided (m, l, acc) partials
+
+int8 KV: a pool whose caches are ``torch.int8`` with fp32 scales ``[num_blocks, H_kv, block_size]``
+(one per position and kv head, the reference's ``kv_int8`` / ``k_scales`` / ``v_scales`` of
+``include/reflex/infer.h:189-203`` on pages). ``rope_append`` quantises on the way in
+(``scale = max|row| / 127``, ``q = round(row / scale)``), the paged entry points take
+``k_scales=`` / ``v_scales=``; ``int8_pool`` allocates such a pool.
 """
 from __future__ import annotations
 
@@ -140,11 +146,12 @@ class PagedAttentionCall:
 
     def __init__(self, q, k_cache, v_cache, block_table, context_lens, *, q_start=None, max_q_len=None,
                  is_causal=True, sm_scale=None, rope_cos=None, rope_sin=None, rope_positions=None,
-                 rope_interleaved=False, workspace=None, out=None, force_generic=False, target_chunk=0):
+                 rope_interleaved=False, workspace=None, out=None, force_generic=False, target_chunk=0,
+                 k_scales=None, v_scales=None):
         import ctypes as C
         name = "paged_attention"
         dev = N.require_cuda(name, q, k_cache, v_cache, block_table, context_lens, q_start, rope_cos, rope_sin,
-                             rope_positions, out)
+                             rope_positions, out, k_scales, v_scales)
         if q.dim() != 3:
             raise ValueError(f"{name}: q must be [N_q, H_q, D], got {tuple(q.shape)}")
         if k_cache.dim() != 4 or v_cache.shape != k_cache.shape:
@@ -154,7 +161,14 @@ class PagedAttentionCall:
         if Dc != D:
             raise ValueError(f"{name}: head_dim of q ({D}) and cache ({Dc}) differ")
         _resolve_head_repeat(Hq, Hkv)
-        if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        kv_int8 = k_cache.dtype == torch.int8
+        if kv_int8:
+            if v_cache.dtype != torch.int8 or k_scales is None or v_scales is None:
+                raise ValueError(f"{name}: an int8 pool needs int8 k_cache and v_cache and k_scales, v_scales")
+            for t in (k_scales, v_scales):
+                if t.dtype != torch.float32 or tuple(t.shape) != (nb, Hkv, bs) or not t.is_contiguous():
+                    raise ValueError(f"{name}: scales must be contiguous float32 [{nb}, {Hkv}, {bs}]")
+        elif k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
             raise RuntimeError(f"{name}: q dtype {q.dtype} differs from the cache dtype {k_cache.dtype}")
         if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
             raise ValueError(f"{name}: the caches must be contiguous")
@@ -209,6 +223,8 @@ class PagedAttentionCall:
             sm_scale=float(sm_scale), is_causal=int(bool(is_causal)), rope_interleaved=int(bool(rope_interleaved)),
             dtype=N.dtype_code(q), reuse_plan=0, force_generic=int(bool(force_generic)),
             target_chunk=int(target_chunk), workspace=None, workspace_bytes=0, stream=None,
+            kv_int8=int(kv_int8), k_scales=N.ptr(k_scales) if kv_int8 else None,
+            v_scales=N.ptr(v_scales) if kv_int8 else None,
         )
         lib = N.lib()
         need = lib.rfx_paged_attention_workspace_bytes(C.byref(a))
@@ -224,7 +240,8 @@ class PagedAttentionCall:
         self._args = a
         self._ref = C.byref(a)
         self._lib = lib
-        self._keep = (q, k_cache, v_cache, block_table, context_lens, q_start, rope_cos, rope_sin, rope_positions, buf)
+        self._keep = (q, k_cache, v_cache, block_table, context_lens, q_start, rope_cos, rope_sin, rope_positions, buf,
+                      k_scales, v_scales)
 
     def _call(self, fn):
         self._args.stream = N.stream_handle(self.device)
@@ -300,6 +317,8 @@ def paged_attention(
     reuse_plan: bool = False,
     force_generic: bool = False,
     target_chunk: int = 0,
+    k_scales: Optional[torch.Tensor] = None,
+    v_scales: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Attention of ragged query chunks over the paged pool.
 
@@ -317,7 +336,8 @@ def paged_attention(
     call = PagedAttentionCall(q, k_cache, v_cache, block_table, context_lens, q_start=q_start, max_q_len=max_q_len,
                               is_causal=is_causal, sm_scale=sm_scale, rope_cos=rope_cos, rope_sin=rope_sin,
                               rope_positions=rope_positions, rope_interleaved=rope_interleaved, workspace=workspace,
-                              out=out, force_generic=force_generic, target_chunk=target_chunk)
+                              out=out, force_generic=force_generic, target_chunk=target_chunk,
+                              k_scales=k_scales, v_scales=v_scales)
     return call.run(reuse_plan=reuse_plan)
 
 
@@ -332,10 +352,11 @@ class RopeAppendCall:
     """A validated, ready-to-launch fused RoPE + append over fixed buffers (see ``rope_append``)."""
 
     def __init__(self, k_new, v_new, k_cache, v_cache, slot_mapping, positions, cos, sin, *, q=None, q_out=None,
-                 interleaved=False):
+                 interleaved=False, k_scales=None, v_scales=None):
         import ctypes as C
         name = "rope_append"
-        dev = N.require_cuda(name, k_new, v_new, k_cache, v_cache, slot_mapping, positions, cos, sin, q, q_out)
+        dev = N.require_cuda(name, k_new, v_new, k_cache, v_cache, slot_mapping, positions, cos, sin, q, q_out,
+                             k_scales, v_scales)
         if k_new.dim() != 3 or v_new.shape != k_new.shape:
             raise ValueError(f"{name}: k_new and v_new must both be [N, H_kv, D]")
         n, Hkv, D = k_new.shape
@@ -348,7 +369,18 @@ class RopeAppendCall:
             raise ValueError(f"{name}: the head_dim axis of the caches must be contiguous")
         if D % 2 != 0:
             raise ValueError("head_dim must be even for RoPE")
-        if k_new.dtype != k_cache.dtype or v_new.dtype != k_cache.dtype:
+        kv_int8 = k_cache.dtype == torch.int8
+        if kv_int8:
+            if v_cache.dtype != torch.int8 or k_scales is None or v_scales is None:
+                raise ValueError(f"{name}: an int8 pool needs int8 k_cache and v_cache and k_scales, v_scales")
+            if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+                raise ValueError(f"{name}: an int8 pool must be contiguous")
+            for t in (k_scales, v_scales):
+                if t.dtype != torch.float32 or tuple(t.shape) != (nb, ch, bs) or not t.is_contiguous():
+                    raise ValueError(f"{name}: scales must be contiguous float32 [{nb}, {ch}, {bs}]")
+            if v_new.dtype != k_new.dtype:
+                raise RuntimeError(f"{name}: k_new and v_new dtypes differ")
+        elif k_new.dtype != k_cache.dtype or v_new.dtype != k_cache.dtype:
             raise RuntimeError(f"{name}: input dtype {k_new.dtype} does not match cache dtype {k_cache.dtype}")
         k_new, v_new = k_new.contiguous(), v_new.contiguous()
         slot_mapping = slot_mapping.to(torch.int64).contiguous()
@@ -379,12 +411,14 @@ class RopeAppendCall:
             table_rows=cos.shape[0],
             cache_stride_blk=k_cache.stride(0), cache_stride_h=k_cache.stride(1), cache_stride_pos=k_cache.stride(2),
             interleaved=int(bool(interleaved)), dtype=N.dtype_code(k_new), stream=None,
+            kv_int8=int(kv_int8), k_scales=N.ptr(k_scales) if kv_int8 else None,
+            v_scales=N.ptr(v_scales) if kv_int8 else None,
         )
         self._ref = C.byref(self._args)
         self._fn = N.lib().rfx_rope_append
         self.device = dev
         self.q_out = q_out
-        self._keep = (k_new, v_new, q, k_cache, v_cache, slot_mapping, positions, cos, sin)
+        self._keep = (k_new, v_new, q, k_cache, v_cache, slot_mapping, positions, cos, sin, k_scales, v_scales)
 
     def run(self) -> Optional[torch.Tensor]:
         self._args.stream = N.stream_handle(self.device)
@@ -406,15 +440,27 @@ def rope_append(
     q: Optional[torch.Tensor] = None,
     q_out: Optional[torch.Tensor] = None,
     interleaved: bool = False,
+    k_scales: Optional[torch.Tensor] = None,
+    v_scales: Optional[torch.Tensor] = None,
 ) -> Optional[torch.Tensor]:
     """Rotate ``k_new`` with table rows ``positions`` and write it and ``v_new`` into the
     pool at ``slot_mapping`` in one launch; with ``q`` also returns the rotated queries.
 
     Pool contents equal ``kv_paged_append(apply_rope(k_new...), v_new, ...)`` of the
-    reference bit for bit (tables in the activation dtype).
+    reference bit for bit (tables in the activation dtype). With an int8 pool (``torch.int8``
+    caches plus ``k_scales`` / ``v_scales``) the rotated K rows and the V rows are quantised
+    row by row: ``scale = max|row| / 127`` (1 for an all-zero row), ``q = round(row / scale)``.
     """
     return RopeAppendCall(k_new, v_new, k_cache, v_cache, slot_mapping, positions, cos, sin, q=q, q_out=q_out,
-                          interleaved=interleaved).run()
+                          interleaved=interleaved, k_scales=k_scales, v_scales=v_scales).run()
+
+
+def int8_pool(num_blocks: int, num_kv_heads: int, block_size: int, head_dim: int, device):
+    """An empty int8 KV pool: ``(k_cache, v_cache, k_scales, v_scales)``, caches
+    ``[num_blocks, H_kv, block_size, D]`` int8, scales ``[num_blocks, H_kv, block_size]`` float32."""
+    k = torch.zeros((num_blocks, num_kv_heads, block_size, head_dim), dtype=torch.int8, device=device)
+    ks = torch.ones((num_blocks, num_kv_heads, block_size), dtype=torch.float32, device=device)
+    return k, torch.zeros_like(k), ks, torch.ones_like(ks)
 
 
 def paged_decode_step(
@@ -434,16 +480,19 @@ def paged_decode_step(
     interleaved: bool = False,
     workspace: Optional[PagedWorkspace] = None,
     out: Optional[torch.Tensor] = None,
+    k_scales: Optional[torch.Tensor] = None,
+    v_scales: Optional[torch.Tensor] = None,
     **kw,
 ) -> torch.Tensor:
     """One decode step of one layer: append the new token's rotated K and its V to the
     pool, then attend the rotated query over ``context_lens`` keys (which count the new
     token). Three launches on top of the plan: RoPE+append, split-K partials with RoPE
     fused into the Q load, combine."""
-    rope_append(k_new, v_new, k_cache, v_cache, slot_mapping, positions, cos, sin, interleaved=interleaved)
+    rope_append(k_new, v_new, k_cache, v_cache, slot_mapping, positions, cos, sin, interleaved=interleaved,
+                k_scales=k_scales, v_scales=v_scales)
     return paged_decode(q_new, k_cache, v_cache, block_table, context_lens, sm_scale=sm_scale,
                         rope_cos=cos, rope_sin=sin, rope_positions=positions, rope_interleaved=interleaved,
-                        workspace=workspace, out=out, **kw)
+                        workspace=workspace, out=out, k_scales=k_scales, v_scales=v_scales, **kw)
 
 
 def splitk_combine(acc: torch.Tensor, m: torch.Tensor, l: torch.Tensor, split_begin: torch.Tensor,
@@ -472,6 +521,7 @@ __all__ = [
     "paged_decode_step",
     "rope_append",
     "splitk_combine",
+    "int8_pool",
     "PagedWorkspace",
     "PagedAttentionCall",
     "RopeAppendCall",

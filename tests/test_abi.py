@@ -32,7 +32,7 @@ def test_struct_sizes_match(native):
     for i, mirror in enumerate(native.ARG_STRUCTS):
         assert lib.rfx_args_size(i) == C.sizeof(mirror), mirror.__name__
     assert lib.rfx_args_size(99) == 0
-    assert lib.rfx_abi_version() == 1
+    assert lib.rfx_abi_version() == 2
 
 
 def test_status_strings(native):
