@@ -90,7 +90,7 @@ def parse_args():
     ap.add_argument("--shard", default=None, choices=["replica", "request", "head"],
                     help="default: request (strong scaling); a multi-GPU run without this flag also measures "
                          "the other modes and reports them under other_shards")
-    ap.add_argument("--only", default=None, choices=["cfg3", "cfg5", "linear_norm", "small_ops"],
+    ap.add_argument("--only", default=None, choices=["cfg3", "cfg5", "linear_norm", "small_ops", "int8_kv"],
                     help="run just that secondary block on one GPU and print it (small profiling cases: "
                          "--only cfg3 --requests 2)")
     ap.add_argument("--cpu-sample", type=int, default=0, help="requests in the CPU-baseline sample (0 = auto)")
@@ -665,6 +665,72 @@ def measure_mixed(args, device):
             "l2": "inputs larger than L2", "status": attn.workspace.status()}
 
 
+def measure_int8_kv(args, device):
+    """The headline decode configuration (cfg4) on an int8 pool with one fp32 scale per (position, kv
+    head): the same step -- quantising RoPE + append, plan, the decode kernel's int8 instantiation,
+    combine -- with the K+V bytes roughly halved. Algorithmic bytes: (D + 4) per key and kv head for
+    K and for V."""
+    workloads = load_workloads()
+    from kernels.attention import PagedAttentionCall, PagedWorkspace, RopeAppendCall
+    b = workloads.cfg4(device=device, seed=3, B=args.requests or None)
+
+    def quantise(cache):  # row-wise absmax quantiser with torch ops, a slice of pages at a time
+        q = torch.empty(cache.shape, dtype=torch.int8, device=device)
+        sc = torch.empty(cache.shape[:3], dtype=torch.float32, device=device)
+        step = 4096
+        for i in range(0, cache.shape[0], step):
+            x = cache[i:i + step].float()
+            amax = x.abs().amax(dim=-1)
+            s_ = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
+            q[i:i + step] = torch.round(x / s_.unsqueeze(-1)).clamp_(-127, 127).to(torch.int8)
+            sc[i:i + step] = s_
+        return q, sc
+
+    kq, ks = quantise(b.k_cache)
+    b.k_cache = None
+    vq, vs = quantise(b.v_cache)
+    b.v_cache = None
+    torch.cuda.empty_cache()
+    ws = PagedWorkspace(device)
+    ra = RopeAppendCall(b.k_new, b.v_new, kq, vq, b.slot_mapping, b.positions, b.cos, b.sin, k_scales=ks, v_scales=vs)
+    attn = PagedAttentionCall(b.q_new, kq, vq, b.block_table, b.context_lens, rope_cos=b.cos, rope_sin=b.sin,
+                              rope_positions=b.positions, workspace=ws, k_scales=ks, v_scales=vs)
+
+    def run(ev0=None, ev1=None):
+        ra.run()
+        attn.plan()
+        if ev0 is not None:
+            ev0.record()
+        attn.partials()
+        if ev1 is not None:
+            ev1.record()
+        attn.combine()
+
+    total_ms, _ = timed_steps(lambda: run(), args.steps, args.warmup, None, None)
+    _, kern_ms = timed_steps(run, args.steps, 1, None, None, with_kernel_events=True)
+    km = statistics.mean(kern_ms)
+    keys = int(b.context_lens.sum().item())
+    nbytes = 2.0 * b.Hkv * keys * (b.D + 4)
+    peak, _ = measured_peak()
+    # sanity against the oracle on the first request (float32 attention over the dequantised pages)
+    import oracle
+    r, ctx = 0, int(b.context_lens[0])
+    pages = b.block_table[r, :(ctx + b.block_size - 1) // b.block_size]
+    kd = oracle.kv_dequantize(kq[pages].cpu(), ks[pages].cpu())
+    vd = oracle.kv_dequantize(vq[pages].cpu(), vs[pages].cpu())
+    pos = b.positions[r:r + 1].cpu().long()
+    q_rot = oracle.apply_rope(b.q_new[r:r + 1].cpu().unsqueeze(0), b.cos.cpu()[pos], b.sin.cpu()[pos])[0]
+    ref = oracle.paged_attention_composed(q_rot.float(), kd, vd, torch.arange(pages.numel()).view(1, -1),
+                                          torch.tensor([ctx], dtype=torch.int32))
+    err = (attn.out[r].cpu().float() - ref[0]).abs().max().item()
+    return {"config": "cfg4 on an int8 pool: 256 requests, ctx U[8192,32768], 64q/8kv heads, D=128, page 32, int8 K and V "
+                      "with one fp32 scale per (position, kv head)",
+            "value": b.n_tokens * args.steps / (total_ms * 1e-3), "unit": UNIT, "ms_per_step": total_ms / args.steps,
+            "kernel": "decode_mma_kernel (int8)" if attn.kernel_kind == 1 else "scalar", "kernel_ms": km,
+            "kv_gigabytes": nbytes / 1e9, "hbm_gbs": nbytes / (km * 1e-3) / 1e9, "hbm_frac": nbytes / (km * 1e-3) / 1e9 / peak,
+            "max_abs_err_vs_oracle": err, "status": ws.status()}
+
+
 def measure_linear_norm(args, device):
     """Fused linear + norm on the shapes of the reference's own benchmark
     (benchmark/bench_fused_linear_norm.py:24-29): one call = GEMM with the row statistics in its
@@ -915,6 +981,10 @@ def run_ours(args):
         emit_block("cfg5", blk)
         secondary.update(cfg5_frac=blk["hbm_frac"], cfg5_kernel_ms=blk["kernel_ms"])
         torch.cuda.empty_cache()
+        blk = measure_int8_kv(args, device)
+        emit_block("cfg4_int8_kv", blk)
+        secondary.update(cfg4_int8_frac=blk["hbm_frac"], cfg4_int8_ms_per_step=blk["ms_per_step"])
+        torch.cuda.empty_cache()
         blk = measure_linear_norm(args, device)
         emit_block("fused_linear_norm", blk)
         torch.cuda.empty_cache()
@@ -935,7 +1005,7 @@ def run_only(args):
     device = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     block = {"cfg3": measure_prefill, "cfg5": measure_mixed, "linear_norm": measure_linear_norm,
-             "small_ops": measure_small_ops}[args.only](args, device)
+             "small_ops": measure_small_ops, "int8_kv": measure_int8_kv}[args.only](args, device)
     print(json.dumps({"only": args.only, "steps": args.steps, "warmup": args.warmup, **block}), flush=True)
 
 

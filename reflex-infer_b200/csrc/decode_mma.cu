@@ -30,6 +30,7 @@ namespace rfx {
 
 constexpr int kTile = kPlanTile;    // keys per stage
 constexpr int kGroupWarps = 4;      // warps per consumer group, 16 keys each
+constexpr int kProducers = 4;       // producer warps; stage n of a CTA's sequence belongs to warp n % 4
 constexpr int kAccPad = 4;          // floats of padding per merge row (bank spread)
 
 struct alignas(16) StageMeta {  // 32 bytes: the mbarriers behind the array stay 8-byte aligned
@@ -236,7 +237,7 @@ __device__ inline void load_q_frags(uint32_t (&qa)[HD / 16][4], const unsigned c
 }
 
 template <typename T, int HD, int GP, int STAGES, int GROUPS, bool Q8>
-__global__ void __launch_bounds__((kGroupWarps * GROUPS + 1) * 32, 1)
+__global__ void __launch_bounds__((kGroupWarps * GROUPS + kProducers) * 32, 1)
 decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                   const DecodeParams P) {
     using S = DecodeSmem<HD, GP, STAGES, Q8>;
@@ -272,15 +273,22 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     ptx::pdl_trigger();  // the combine kernel may be scheduled behind this one already
     ptx::pdl_wait();     // everything below reads what earlier kernels wrote (plan, pool, Q)
 
-    if (warp == kConsumers) {  // the last warp
-        // ------------------------------------------------------------ producer --
-        if (lane == 0) {
+    if (warp >= kConsumers) {  // the last warps
+        // ------------------------------------------------------------ producers --
+        // Filling a stage costs its producer well over a thousand cycles (a barrier poll, the page
+        // look-up, one instruction per copy, each a round trip to a unit that is busy), more than the
+        // stage's bytes take to arrive, so four warps share the work: every one walks the whole run
+        // (the bookkeeping is cheap) and fills the stages whose number in the CTA's sequence is its own
+        // modulo four. A ring slot is therefore always filled by one warp at a time.
+        const int pw = warp - kConsumers;
+        if (lane == 0 && pw == 0) {
             ptx::prefetch_tensormap(&kmap);
             ptx::prefetch_tensormap(&vmap);
         }
         const int n_parts = P.hdr[HdrNumParts];
         int stage = 0;
         uint32_t phase = 0;
+        int turn = 0;  // whose stage comes next
         bool alive = true;
         for (int part = blockIdx.x; part < n_parts && alive; part += gridDim.x) {
             const int i_begin = P.part_first[part], i_end = P.part_first[part + 1];
@@ -336,6 +344,18 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     const int n_tiles = (ke - kb + kTile - 1) / kTile;
                     for (int t = 0; t < n_tiles && alive; ++t) {
                         const int tok0 = kb + t * kTile;
+                        const bool mine = turn == pw;
+                        if (++turn == kProducers) turn = 0;
+                        if (!mine) {
+                            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                            const int next_lb = (tok0 + kTile) / P.block_size;
+                            if (next_lb - win0 >= 32 && t + 1 < n_tiles) {
+                                win0 += 32;
+                                pg_cur = pg_nxt;
+                                pg_nxt = load_win(bt, win0 + 32, ke);
+                            }
+                            continue;
+                        }
                         const int n_valid = min(kTile, ke - tok0);
                         const int n_boxes = (n_valid + R - 1) / R;
                         int ok = 1;
@@ -424,8 +444,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 }
             }
         }
-        // Tell the consumers there is nothing left.
-        if (alive && lane == 0) {
+        // Tell the consumers there is nothing left (the warp whose turn it is).
+        if (alive && lane == 0 && turn == pw) {
             if (ptx::mbar_wait_bounded(&empty[stage], phase ^ 1u)) {
                 StageMeta m;
                 m.item = -1; m.n_valid = 0; m.flags = 0; m.prow = 0; m.bad = 0;
@@ -860,7 +880,7 @@ static int launch_decode_t(const RfxPagedAttentionArgs* a, const CUtensorMap& km
         if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "decode smem opt-in (%zu B): %s", S::total, cudaGetErrorString(e));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    cudaError_t le = launch_pdl(kern, dim3(decode_mma_ctas(a)), dim3((kGroupWarps * GROUPS + 1) * 32), S::total,
+    cudaError_t le = launch_pdl(kern, dim3(decode_mma_ctas(a)), dim3((kGroupWarps * GROUPS + kProducers) * 32), S::total,
                                 as_stream(a->stream), km, vm, P);
     if (le != cudaSuccess) return fail(RFX_CUDA_ERROR, "decode kernel launch: %s", cudaGetErrorString(le));
     return check_launch("rfx_paged_attention (decode MMA kernel)");
@@ -912,11 +932,11 @@ int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const P
     if (a->kv_int8) {
         // half the bytes per stage: ten (eight) stages fit where the 16-bit pool has six (five)
         if (a->dtype == RFX_BF16) {
-            if (G <= 8) return launch_decode_t<__nv_bfloat16, 128, 8, 10, 1, true>(a, km, vm, P);
-            return launch_decode_t<__nv_bfloat16, 128, 16, 8, 1, true>(a, km, vm, P);
+            if (G <= 8) return launch_decode_t<__nv_bfloat16, 128, 8, 10, 2, true>(a, km, vm, P);
+            return launch_decode_t<__nv_bfloat16, 128, 16, 8, 2, true>(a, km, vm, P);
         }
-        if (G <= 8) return launch_decode_t<__half, 128, 8, 10, 1, true>(a, km, vm, P);
-        return launch_decode_t<__half, 128, 16, 8, 1, true>(a, km, vm, P);
+        if (G <= 8) return launch_decode_t<__half, 128, 8, 10, 2, true>(a, km, vm, P);
+        return launch_decode_t<__half, 128, 16, 8, 2, true>(a, km, vm, P);
     }
 
 #define RFX_DECODE_CASE(T)                                                                   \
