@@ -347,14 +347,23 @@ class DecodeStep:
                                        batch.context_lens, rope_cos=batch.cos, rope_sin=batch.sin,
                                        rope_positions=batch.positions, workspace=self.ws, target_chunk=chunk)
         self.out = self.attn.out
-        self.kernel_launches = 4
         self.gather = None  # a sharding.FusedHeadGather: the combine then writes every rank's full output
+        self.fused = self.attn.kernel_kind == 1  # the decode kernel finishes its rows: no combine launch
+
+    @property
+    def kernel_launches(self):
+        return 3 if self.fused and self.gather is None else 4
 
     def run(self, ev0=None, ev1=None):
         self.append.run()
         self.attn.plan()
         if ev0 is not None:
             ev0.record()
+        if self.fused and self.gather is None:
+            self.attn.partials_final()
+            if ev1 is not None:
+                ev1.record()
+            return self.out
         self.attn.partials()
         if ev1 is not None:
             ev1.record()
@@ -484,8 +493,10 @@ def measure(workload, args, device, rank, world, dist, want_e2e=True, sampler=No
         from sharding import FusedHeadGather, HeadGather
         gather = HeadGather(step.out, dist)
         if gather_kind == "fused":
-            # same step twice: NCCL all-gather of the local heads, then the gathering combine
-            want = gather.run(step.run()).clone()
+            # same step twice: NCCL all-gather of the local heads (combine kernel, the arithmetic of the
+            # gathering combine), then the gathering combine
+            step.append.run(); step.attn.plan(); step.attn.partials()
+            want = gather.run(step.attn.combine()).clone()
             step.gather = FusedHeadGather(step.out.shape[0], batch.Hq, batch.D, batch.dtype, device, dist)
             got = step.run()
             torch.cuda.synchronize()
@@ -701,10 +712,9 @@ def measure_int8_kv(args, device):
         attn.plan()
         if ev0 is not None:
             ev0.record()
-        attn.partials()
+        attn.partials_final()
         if ev1 is not None:
             ev1.record()
-        attn.combine()
 
     total_ms, _ = timed_steps(lambda: run(), args.steps, args.warmup, None, None)
     _, kern_ms = timed_steps(run, args.steps, 1, None, None, with_kernel_events=True)

@@ -238,7 +238,9 @@ int rfx_fused_attention_kernel_kind(const RfxAttentionArgs* a);
  * rfx_paged_attention_plan, each item leaves an un-normalised (m, l, acc) partial in
  * the workspace, and rfx_splitk_combine merges them with the recurrence of
  * kernels/softmax/triton_softmax.py:84-89 / triton_fused_attention.py:205-227.
- * rfx_paged_attention runs plan (unless reuse_plan), partial kernel and combine. */
+ * rfx_paged_attention runs plan (unless reuse_plan), partial kernel and combine; where the decode
+ * kernel runs, the merge happens inside it (see rfx_paged_attention_partials_final) and the step is
+ * two launches. */
 typedef struct {
     const void* q;               /* [N_q, H_q, D] contiguous */
     void* out;                   /* [N_q, H_q, D] */
@@ -281,6 +283,13 @@ int rfx_paged_attention(const RfxPagedAttentionArgs* a);
  * CUDA graph, per-kernel timing): the split-K partial kernel over an existing plan, and
  * the combine that turns the partials into `out` and re-arms the plan for the next use. */
 int rfx_paged_attention_partials(const RfxPagedAttentionArgs* a);
+/* The decode kernel (kernel kind 1) can finish its rows itself: an item that is a whole (request, kv
+ * head) pair writes `out` directly, and of a pair cut into several items the last one to finish merges
+ * all their partials (a counter per pair in the workspace). rfx_paged_attention does exactly that and
+ * launches no combine kernel then. This entry is that partial kernel alone, over an existing plan, for
+ * callers that time or sequence the stages themselves; RFX_NOT_IMPLEMENTED for the other kernel kinds
+ * (use rfx_paged_attention_partials + rfx_paged_attention_combine). */
+int rfx_paged_attention_partials_final(const RfxPagedAttentionArgs* a);
 /* Which kernel the arguments select: 2 = tcgen05 prefill kernel (16-bit, head_dim 128, ragged
  * query chunks given by q_start, queries already rotated, page size >= 8 dividing or a
  * multiple of 128; whole rows per CTA, or split over the keys with plan and combine when

@@ -39,6 +39,9 @@ struct alignas(16) StageMeta {  // 32 bytes: the mbarriers behind the array stay
     int flags;     // bit0 first stage of item, bit1 last stage of item, bit2 rotate Q
     int prow;      // first partial row of the item
     unsigned bad;  // boxes of the stage that were not loaded (page index outside the pool): their keys do not count
+    int pair;      // request * Hkv + kv head
+    int item0;     // first item of the pair
+    int ns;        // items of the pair (1: the item is the whole pair)
 };
 
 struct DecodeParams {
@@ -61,6 +64,14 @@ struct DecodeParams {
     float scale_log2;  // sm_scale * log2(e)
     const float* k_scales;  // int8 pool: one fp32 scale per (page, kv head, position), else nullptr
     const float* v_scales;
+    // Merge inside the kernel (out != nullptr): an item that is a whole pair writes its output rows
+    // itself; of a pair cut into several items the last one to finish merges the partials of all. Then
+    // no combine kernel follows. pair_counter[B*Hkv] counts the finished items of each pair (zero
+    // between launches: the last arriver puts it back).
+    void* out;
+    const int32_t* pair_item_begin;
+    int32_t* pair_counter;
+    int n_pairs;
 };
 
 template <int HD, int GP, int STAGES, bool Q8 = false>
@@ -79,7 +90,7 @@ struct DecodeSmem {
     static constexpr size_t off_merge = off_q + (size_t)STAGES * kQSlot;
     static constexpr size_t merge_bytes = (size_t)kGroupWarps * GP * kAccStride * 4;
     static constexpr size_t off_ml = off_merge + merge_bytes;             // [group warps][GP][2]
-    static constexpr size_t off_meta = off_ml + (size_t)kGroupWarps * GP * 2 * 4;
+    static constexpr size_t off_meta = off_ml + (size_t)kGroupWarps * GP * 2 * 4 + 16;  // + the "last item of its pair" flag
     static constexpr size_t off_bars = off_meta + (size_t)STAGES * sizeof(StageMeta);
     static_assert(sizeof(StageMeta) % 8 == 0 && off_meta % 8 == 0, "mbarriers need 8-byte alignment");
     static constexpr size_t total = off_bars + 2 * (size_t)STAGES * 8 + 1024;  // + alignment slack
@@ -296,10 +307,15 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 // one round trip: lane j holds the descriptor of item ib + j
                 const int my_id = ib + lane;
                 int4 my_desc = make_int4(0, 0, 0, 0);
-                int my_prow = 0, my_pos = -1, my_qrow = -1;
+                int my_prow = 0, my_pos = -1, my_qrow = -1, my_item0 = 0, my_ns = 1;
                 if (my_id < i_end) {
                     my_desc = P.items[my_id];
                     my_prow = P.item_prow[my_id];
+                    if (P.out) {
+                        const int pr = my_desc.x * P.Hkv + my_desc.y;
+                        my_item0 = P.pair_item_begin[pr];
+                        my_ns = P.pair_item_begin[pr + 1] - my_item0;
+                    }
                     if (P.rcos) my_pos = P.rpos[my_desc.x];
                     my_qrow = my_desc.x;
                     if (P.q_start) {
@@ -328,6 +344,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     const int prow = __shfl_sync(0xffffffffu, my_prow, j);
                     const int pos = __shfl_sync(0xffffffffu, my_pos, j);
                     const int qrow = __shfl_sync(0xffffffffu, my_qrow, j);
+                    const int item0 = __shfl_sync(0xffffffffu, my_item0, j), ns = __shfl_sync(0xffffffffu, my_ns, j);
                     const bool rotate = P.rcos != nullptr && pos >= 0 && (int64_t)pos < P.table_rows;
                     const int64_t* bt = P.block_table + (int64_t)b * P.bt_sb;
                     int win0 = kb / P.block_size;
@@ -389,6 +406,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             m.flags = (t == 0 ? 1 : 0) | (t == n_tiles - 1 ? 2 : 0) | (rotate ? 4 : 0);
                             m.prow = prow;
                             m.bad = wantmask & ~okmask;
+                            m.pair = b * P.Hkv + hkv; m.item0 = item0; m.ns = ns;
                             sMeta[stage] = m;
                             if (okmask != wantmask) atomicOr(P.hdr + HdrStatus, kStatusBadPage);
                             uint32_t tx = (2u * box_bytes + (Q8 ? 8u * (uint32_t)R : 0u)) * (uint32_t)__popc(okmask);
@@ -448,7 +466,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         if (alive && lane == 0 && turn == pw) {
             if (ptx::mbar_wait_bounded(&empty[stage], phase ^ 1u)) {
                 StageMeta m;
-                m.item = -1; m.n_valid = 0; m.flags = 0; m.prow = 0; m.bad = 0;
+                m.item = -1; m.n_valid = 0; m.flags = 0; m.prow = 0; m.bad = 0; m.pair = 0; m.item0 = 0; m.ns = 1;
                 sMeta[stage] = m;
                 ptx::mbar_arrive(&full[stage]);
             } else {
@@ -484,6 +502,16 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     const uint32_t k_sw = (uint32_t)(k_r & 7), v_sw = (uint32_t)(v_r & 7);
     const uint32_t sK_u32 = ptx::smem_u32(sK), sV_u32 = ptx::smem_u32(sV);
 
+    if (P.out) {
+        // A request without keys has no item: nobody else would write its output rows (zeros).
+        T* outp = static_cast<T*>(P.out);
+        for (int pr = blockIdx.x * kConsumers + warp; pr < P.n_pairs; pr += gridDim.x * kConsumers) {
+            if (P.pair_item_begin[pr + 1] != P.pair_item_begin[pr]) continue;
+            const int b = pr / P.Hkv, hkv = pr - b * P.Hkv;
+            T* orow = outp + ((int64_t)b * P.Hq + (int64_t)hkv * P.G) * HD;
+            for (int i = lane; i < P.G * HD; i += 32) orow[i] = Num<T>::from_f(0.f);
+        }
+    }
     int stage = 0;
     uint32_t phase = 0;
     int turn = 0;  // which group computes the current stage
@@ -735,6 +763,10 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             }
             ptx::named_bar_sync(1, kConsumers * 32);
             const int tid = threadIdx.x;  // consumer threads come first
+            const bool direct = P.out != nullptr && meta.ns == 1;  // the item is the whole pair: final rows
+            T* outp = static_cast<T*>(P.out);
+            const int ob = meta.pair / P.Hkv, ohkv = meta.pair - ob * P.Hkv;
+            const int64_t orow0 = ((int64_t)ob * P.Hq + (int64_t)ohkv * P.G) * HD;  // decode: query row = request
             for (int idx = tid; idx < P.G * HD; idx += kConsumers * 32) {
                 const int g = idx / HD, d = idx - g * HD;
                 float M = -INFINITY;
@@ -748,11 +780,59 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     L += sML[(w * GP + g) * 2 + 1] * wt;
                     A += sAcc[(size_t)(w * GP + g) * S::kAccStride + d] * wt;
                 }
+                if (direct) {
+                    outp[orow0 + idx] = Num<T>::from_f(A * (L > 0.f ? 1.f / L : 0.f));  // as the combine kernel rounds
+                    continue;
+                }
                 const int64_t pr = (int64_t)meta.prow + g;
                 P.pacc[pr * HD + d] = A;
                 if (d == 0) {
                     P.pm[pr] = M * 0.6931471805599453f;  // back to the natural-log domain
                     P.pl[pr] = L;
+                }
+            }
+            if (P.out != nullptr && meta.ns > 1) {
+                // One of several items of its pair: count it; the last one to arrive merges them all
+                // (maximum first, then the weighted sums: the result does not depend on the order).
+                __threadfence();
+                ptx::named_bar_sync(1, kConsumers * 32);
+                if (tid == 0) {
+                    const int prev = atomicAdd(P.pair_counter + meta.pair, 1);
+                    const int last = prev == meta.ns - 1 ? 1 : 0;
+                    if (last) P.pair_counter[meta.pair] = 0;  // for the next launch
+                    reinterpret_cast<volatile int*>(sML)[kGroupWarps * GP * 2] = last;
+                }
+                ptx::named_bar_sync(1, kConsumers * 32);
+                if (reinterpret_cast<volatile int*>(sML)[kGroupWarps * GP * 2]) {
+                    __threadfence();
+                    for (int idx = tid; idx < P.G * HD; idx += kConsumers * 32) {
+                        const int g = idx / HD, d = idx - g * HD;
+                        // four items at a time, every load of the group issued before the first use (one
+                        // round trip to L2 per group; a pair is rarely cut more often than that)
+                        float M = -INFINITY, L = 0.f, A = 0.f;
+                        for (int s0 = 0; s0 < meta.ns; s0 += 4) {
+                            float mw[4], lw[4], aw[4];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const bool in = s0 + k < meta.ns;
+                                const int64_t pr = (int64_t)(meta.item0 + (in ? s0 + k : 0)) * P.G + g;
+                                mw[k] = in ? __ldcg(P.pm + pr) : -INFINITY;
+                                lw[k] = in ? __ldcg(P.pl + pr) : 0.f;
+                                aw[k] = in ? __ldcg(P.pacc + pr * HD + d) : 0.f;
+                            }
+                            const float Mn = fmaxf(fmaxf(M, fmaxf(mw[0], mw[1])), fmaxf(mw[2], mw[3]));
+                            const float keep = (M == -INFINITY) ? 0.f : expf(M - Mn);
+                            L *= keep; A *= keep;
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const float wt = (mw[k] == -INFINITY) ? 0.f : expf(mw[k] - Mn);
+                                L = fmaf(lw[k], wt, L);
+                                A = fmaf(aw[k], wt, A);
+                            }
+                            M = Mn;
+                        }
+                        outp[orow0 + idx] = Num<T>::from_f(A * (L > 0.f ? 1.f / L : 0.f));  // as the combine kernel rounds
+                    }
                 }
             }
             ptx::named_bar_sync(1, kConsumers * 32);  // merge buffers free for the next item
@@ -886,7 +966,8 @@ static int launch_decode_t(const RfxPagedAttentionArgs* a, const CUtensorMap& km
     return check_launch("rfx_paged_attention (decode MMA kernel)");
 }
 
-int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const PlanPtrs& Pp, bool single_row_requests_only) {
+int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const PlanPtrs& Pp, bool single_row_requests_only,
+                      bool merge_in_kernel) {
     const int HD = (int)a->head_dim;
     const int G = (int)(a->num_q_heads / a->num_kv_heads);
     const int R = (int)(a->block_size < 64 ? a->block_size : 64);
@@ -929,22 +1010,27 @@ int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const P
     P.map2d = map2d;
     P.k_scales = a->kv_int8 ? a->k_scales : nullptr;
     P.v_scales = a->kv_int8 ? a->v_scales : nullptr;
+    const bool merge = merge_in_kernel && !single_row_requests_only && a->out != nullptr;
+    P.out = merge ? a->out : nullptr;
+    P.pair_item_begin = Pp.pair_item_begin;
+    P.pair_counter = Pp.pair_counter;
+    P.n_pairs = (int)(a->batch * a->num_kv_heads);
     if (a->kv_int8) {
         // half the bytes per stage: ten (eight) stages fit where the 16-bit pool has six (five)
         if (a->dtype == RFX_BF16) {
             if (G <= 8) return launch_decode_t<__nv_bfloat16, 128, 8, 10, 2, true>(a, km, vm, P);
-            return launch_decode_t<__nv_bfloat16, 128, 16, 8, 2, true>(a, km, vm, P);
+            return launch_decode_t<__nv_bfloat16, 128, 16, 8, 1, true>(a, km, vm, P);
         }
         if (G <= 8) return launch_decode_t<__half, 128, 8, 10, 2, true>(a, km, vm, P);
-        return launch_decode_t<__half, 128, 16, 8, 2, true>(a, km, vm, P);
+        return launch_decode_t<__half, 128, 16, 8, 1, true>(a, km, vm, P);
     }
 
 #define RFX_DECODE_CASE(T)                                                                   \
     if (HD == 128) {                                                                         \
-        if (G <= 8) return launch_decode_t<T, 128, 8, 6>(a, km, vm, P);                      \
+        if (G <= 8) return launch_decode_t<T, 128, 8, 6, 2>(a, km, vm, P);                   \
         return launch_decode_t<T, 128, 16, 5>(a, km, vm, P);                                 \
     } else {                                                                                 \
-        if (G <= 8) return launch_decode_t<T, 64, 8, 8>(a, km, vm, P);                       \
+        if (G <= 8) return launch_decode_t<T, 64, 8, 8, 2>(a, km, vm, P);                    \
         return launch_decode_t<T, 64, 16, 8>(a, km, vm, P);                                  \
     }
     if (a->dtype == RFX_BF16) { RFX_DECODE_CASE(__nv_bfloat16) }

@@ -111,11 +111,14 @@ static int run_stages(const RfxPagedAttentionArgs* a, const char* name, int stag
         st = launch_plan(a, L, P, mma ? decode_mma_ctas(a) : sm_count() * 4);
         if (st != RFX_SUCCESS) return st;
     }
+    // One call for the whole step and no gather: the decode kernel merges the split pairs itself and
+    // writes `out`; the combine kernel is for the staged calls, the gather and the scalar kernel.
+    const bool merge_in_kernel = mma && !gather && (stages & kStagePartials) && (stages & kStageCombine);
     if (stages & kStagePartials) {
-        st = mma ? launch_decode_mma(a, L, P) : launch_paged_generic(a, L, P);
+        st = mma ? launch_decode_mma(a, L, P, false, merge_in_kernel) : launch_paged_generic(a, L, P);
         if (st != RFX_SUCCESS) return st;
     }
-    if (stages & kStageCombine) return launch_paged_combine(a, L, P, gather);
+    if ((stages & kStageCombine) && !merge_in_kernel) return launch_paged_combine(a, L, P, gather);
     return RFX_SUCCESS;
 }
 }  // namespace rfx
@@ -128,6 +131,14 @@ extern "C" int rfx_paged_attention(const RfxPagedAttentionArgs* a) {
 
 extern "C" int rfx_paged_attention_partials(const RfxPagedAttentionArgs* a) {
     return rfx::run_stages(a, "rfx_paged_attention_partials", rfx::kStagePartials);
+}
+
+extern "C" int rfx_paged_attention_partials_final(const RfxPagedAttentionArgs* a) {
+    using namespace rfx;
+    if (validate(a, "rfx_paged_attention_partials_final") != RFX_SUCCESS) return RFX_INVALID_ARGUMENT;
+    if (prefill_paged_supported(a) || !decode_mma_supported(a))
+        return fail(RFX_NOT_IMPLEMENTED, "rfx_paged_attention_partials_final: only the decode kernel finishes its own rows");
+    return run_stages(a, "rfx_paged_attention_partials_final", kStagePartials | kStageCombine);
 }
 
 extern "C" int rfx_paged_attention_kernel_kind(const RfxPagedAttentionArgs* a) {

@@ -8,6 +8,8 @@
 //
 //   header          : 64 int32 (see Hdr*)
 //   pair_item_begin : int32[B*Hkv+1]      first item of each (request, kv_head) pair
+//   pair_counter    : int32[B*Hkv]        finished items of each pair (decode kernel's in-kernel merge;
+//                                         zeroed by the plan, put back to zero by the last item of a pair)
 //   part_first      : int32[max_parts+1]  first item of each run
 //   items           : int4[max_items]     (request, kv_head, key_begin, key_end)
 //   item_prow       : int32[max_items+1]  first partial row of each item
@@ -38,7 +40,7 @@ constexpr int kStatusCapacity = 4;   // the device-side row counts exceed what t
 constexpr int kPlanTile = 64;  // keys per tile of the stream
 
 struct PlanLayout {
-    size_t off_pair_begin, off_part_first, off_items, off_item_prow, off_m, off_l, off_acc, total;
+    size_t off_pair_begin, off_pair_counter, off_part_first, off_items, off_item_prow, off_m, off_l, off_acc, total;
     int64_t max_parts, max_items, cap_rows;
 };
 
@@ -54,6 +56,7 @@ inline PlanLayout plan_layout(int64_t B, int64_t Hkv, int64_t G, int64_t n_q, in
     L.cap_rows = G * (Hkv * n_q + L.max_parts * (max_q_len < 1 ? 1 : max_q_len));
     size_t o = HdrWords * sizeof(int32_t);
     L.off_pair_begin = o; o = align_up(o + (size_t)(B * Hkv + 1) * 4, 256);
+    L.off_pair_counter = o; o = align_up(o + (size_t)(B * Hkv) * 4, 256);
     L.off_part_first = o; o = align_up(o + (size_t)(L.max_parts + 1) * 4, 256);
     L.off_items = o;      o = align_up(o + (size_t)L.max_items * 16, 256);
     L.off_item_prow = o;  o = align_up(o + (size_t)(L.max_items + 1) * 4, 256);
@@ -67,6 +70,7 @@ inline PlanLayout plan_layout(int64_t B, int64_t Hkv, int64_t G, int64_t n_q, in
 struct PlanPtrs {
     int32_t* hdr;
     int32_t* pair_item_begin;
+    int32_t* pair_counter;
     int32_t* part_first;
     int4* items;
     int32_t* item_prow;
@@ -80,6 +84,7 @@ inline PlanPtrs plan_ptrs(void* ws, const PlanLayout& L) {
     PlanPtrs r;
     r.hdr = (int32_t*)p;
     r.pair_item_begin = (int32_t*)(p + L.off_pair_begin);
+    r.pair_counter = (int32_t*)(p + L.off_pair_counter);
     r.part_first = (int32_t*)(p + L.off_part_first);
     r.items = (int4*)(p + L.off_items);
     r.item_prow = (int32_t*)(p + L.off_item_prow);
@@ -99,9 +104,10 @@ int launch_paged_combine(const RfxPagedAttentionArgs* a, const PlanLayout& L, co
 bool decode_mma_supported(const RfxPagedAttentionArgs* a);
 bool decode_mma_shape_ok(const RfxPagedAttentionArgs* a);  // ... whatever the number of query rows per request
 // `single_row_requests_only`: a mixed batch (q_start given); requests with more than one query
-// row are left to the tcgen05 kernel.
+// row are left to the tcgen05 kernel. `merge_in_kernel`: the kernel writes `out` itself (whole pairs
+// directly, cut pairs merged by their last item) and no combine kernel is needed.
 int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P,
-                      bool single_row_requests_only = false);
+                      bool single_row_requests_only = false, bool merge_in_kernel = false);
 int decode_mma_ctas(const RfxPagedAttentionArgs* a);
 // tcgen05 kernel for ragged query chunks (prefill_tc.cu).
 bool prefill_paged_supported(const RfxPagedAttentionArgs* a);

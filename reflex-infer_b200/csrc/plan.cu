@@ -38,10 +38,11 @@ __global__ void __launch_bounds__(kPlanThreads)
 plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_start, int B, int Hkv,
             int G, long long max_parts, long long target_chunk, int parts_hint, long long max_items,
             long long cap_rows, long long max_q_len, long long n_q, int32_t* hdr,
-            int32_t* pair_item_begin, int32_t* part_first, int4* items, int32_t* item_prow) {
+            int32_t* pair_item_begin, int32_t* pair_counter, int32_t* part_first, int4* items, int32_t* item_prow) {
     __shared__ long long red[kPlanThreads / 32][2];
     ptx::pdl_trigger();  // the partial kernel may set itself up while the plan is computed
     const int tid = threadIdx.x;
+    for (long long i = tid; i < (long long)B * Hkv; i += kPlanThreads) pair_counter[i] = 0;
     const int per = (B + kPlanThreads - 1) / kPlanThreads;  // requests per thread, contiguous
     const int b0 = min(B, tid * per), b1 = min(B, b0 + per);
 
@@ -154,7 +155,7 @@ int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanP
                                a->q_start, (int)a->batch, (int)a->num_kv_heads, G, (long long)L.max_parts,
                                (long long)a->target_chunk, parts_hint, (long long)L.max_items, (long long)L.cap_rows,
                                (long long)(a->max_q_len < 1 ? 1 : a->max_q_len), (long long)a->n_q, P.hdr,
-                               P.pair_item_begin, P.part_first, P.items, P.item_prow);
+                               P.pair_item_begin, P.pair_counter, P.part_first, P.items, P.item_prow);
     if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "rfx_paged_attention_plan: %s", cudaGetErrorString(e));
     return check_launch("rfx_paged_attention_plan");
 }

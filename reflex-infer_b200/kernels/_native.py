@@ -171,6 +171,7 @@ EXPORTS = {
     "rfx_paged_attention_plan": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_paged_attention": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_paged_attention_partials": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
+    "rfx_paged_attention_partials_final": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_paged_attention_combine": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_paged_attention_kernel_kind": (C.c_int, [C.POINTER(PagedAttentionArgs)]),
     "rfx_fused_attention_kernel_kind": (C.c_int, [C.POINTER(AttentionArgs)]),

@@ -270,6 +270,12 @@ class PagedAttentionCall:
     def partials(self) -> None:
         self._call(self._lib.rfx_paged_attention_partials)
 
+    def partials_final(self) -> torch.Tensor:
+        """The decode kernel alone (``kernel_kind == 1``) over the existing plan, finishing its rows
+        itself: no ``combine()`` follows. This is what ``run()`` launches after the plan."""
+        self._call(self._lib.rfx_paged_attention_partials_final)
+        return self.out
+
     def combine(self) -> torch.Tensor:
         self._call(self._lib.rfx_paged_attention_combine)
         return self.out
