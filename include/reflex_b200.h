@@ -67,6 +67,14 @@ size_t rfx_args_size(int which);
 const char* rfx_status_string(int status);
 /* Thread-local text of the last non-success status returned on this host thread. */
 const char* rfx_last_error(void);
+/* Debug switches (tests, cross-checks; no counterpart in the reference). The library reads the
+ * environment variable REFLEX_B200_DEBUG once, as comma-separated words:
+ *   no_tc            scalar kernels where a tcgen05 kernel would run (attention, linear + norm)
+ *   prefill_nosplit  chunked prefill is not split over the keys
+ *   mixed=1 / mixed=0  one-row requests of a split batch always / never go to the decode kernel
+ *   tma2d            the decode kernel's 2-D tensor maps
+ * rfx_debug_set_flags(words) replaces them for the whole process (NULL: back to the environment's). */
+int rfx_debug_set_flags(const char* words);
 
 /* ------------------------------------------------------------------ kv_cache ---- */
 
@@ -372,6 +380,13 @@ typedef struct {
     uint32_t epoch;                      /* > 0, strictly increasing from step to step */
     int wait;                            /* 1: do not complete before every rank has published epoch */
     int64_t spin_limit;                  /* polls (about 100 ns each) before giving up; 0 = 10 million */
+    /* Replayable form, for a step captured once in a CUDA graph (launch arguments are frozen at capture):
+     * with epoch_word set, `epoch` is ignored; the kernel takes the step's epoch from that local device word
+     * (its value + 1, the same for every CTA of the launch; the last CTA stores it back), and writes to
+     * peer_out[p] + (epoch & 1) * out_alt_offset bytes, so peer_out[] then names the first of the two output
+     * buffers of every rank. The word starts at zero and must not be written by anyone else. */
+    uint32_t* epoch_word;
+    int64_t out_alt_offset;
 } RfxHeadGatherArgs;
 /* Combine stage of rfx_paged_attention (after rfx_paged_attention_partials) with the gather. */
 int rfx_paged_attention_combine_gather(const RfxPagedAttentionArgs* a, const RfxHeadGatherArgs* g);

@@ -33,6 +33,8 @@ struct HeadGatherDev {
     long long spin_limit;
     uint32_t epoch;
     int world, rank, wait;
+    uint32_t* epoch_word;   // replayable form: the epoch lives on the device (see RfxHeadGatherArgs)
+    long long out_alt_offset;
 };
 
 // The same row slice stored into every rank's full output (plain stores through peer mappings).
@@ -40,10 +42,11 @@ template <typename T>
 struct PeerRows {
     const HeadGatherDev* hg;
     int64_t elem;  // offset of the row slice inside a full output
+    long long buf_off;  // bytes: which of the two output buffers this step writes (replayable form)
     __device__ inline void put(int d, const float4& v, int n) const {
         T t[4] = {Num<T>::from_f(v.x), Num<T>::from_f(v.y), Num<T>::from_f(v.z), Num<T>::from_f(v.w)};
         for (int p = 0; p < hg->world; ++p) {
-            T* row = reinterpret_cast<T*>(hg->out[p]) + elem;
+            T* row = reinterpret_cast<T*>(reinterpret_cast<char*>(hg->out[p]) + buf_off) + elem;
             if (n == 4 && sizeof(T) == 2) {
                 *reinterpret_cast<uint2*>(row + d) = *reinterpret_cast<const uint2*>(t);  // d % 4 == 0
             } else {
@@ -155,6 +158,14 @@ paged_combine_kernel(T* __restrict__ out, const __grid_constant__ HeadGatherDev 
                      const int32_t* __restrict__ item_prow, const float* __restrict__ pm,
                      const float* __restrict__ pl, const float* __restrict__ pacc) {
     ptx::pdl_wait();  // partials come from the kernel just before this one
+    // The step's epoch: a launch argument, or (replayable form) the device word + 1 -- no CTA of this
+    // launch changes the word before every CTA has finished, so all read the same value.
+    uint32_t epoch = hg.epoch;
+    long long buf_off = 0;
+    if (GATHER && hg.epoch_word) {
+        epoch = *reinterpret_cast<volatile uint32_t*>(hg.epoch_word) + 1u;
+        buf_off = (long long)(epoch & 1u) * hg.out_alt_offset;
+    }
     const int warp = threadIdx.x >> 5;
     const int G = Hq / Hkv;
     const int64_t rows = n_q * Hq;
@@ -188,7 +199,7 @@ paged_combine_kernel(T* __restrict__ out, const __grid_constant__ HeadGatherDev 
                                sink);
         };
         if (GATHER)
-            run(PeerRows<T>{&hg, (r * ((int64_t)hg.world * Hq) + (int64_t)hg.rank * Hq + h) * D});
+            run(PeerRows<T>{&hg, (r * ((int64_t)hg.world * Hq) + (int64_t)hg.rank * Hq + h) * D, buf_off});
         else
             run(LocalRow<T>{out + orow * D});
     }
@@ -203,7 +214,8 @@ paged_combine_kernel(T* __restrict__ out, const __grid_constant__ HeadGatherDev 
                 *hg.counter = 0;  // for the next launch on this stream
                 __threadfence_system();
                 for (int p = 0; p < hg.world; ++p)
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(hg.flags[p] + hg.rank), "r"(hg.epoch) : "memory");
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(hg.flags[p] + hg.rank), "r"(epoch) : "memory");
+                if (hg.epoch_word) *reinterpret_cast<volatile uint32_t*>(hg.epoch_word) = epoch;
                 if (hg.wait) {
                     bool expired = false;
                     for (int q = 0; q < hg.world && !expired; ++q) {
@@ -212,7 +224,7 @@ paged_combine_kernel(T* __restrict__ out, const __grid_constant__ HeadGatherDev 
                         for (;;) {
                             uint32_t v;
                             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-                            if ((int32_t)(v - hg.epoch) >= 0) break;
+                            if ((int32_t)(v - epoch) >= 0) break;
                             if (++polls > hg.spin_limit) { expired = true; break; }
                             __nanosleep(100);
                         }
@@ -249,7 +261,8 @@ int launch_paged_combine(const RfxPagedAttentionArgs* a, const PlanLayout& L, co
         const char* name = "rfx_paged_attention_combine_gather";
         RFX_REQUIRE(g->world >= 1 && g->world <= RFX_MAX_PEERS && g->rank >= 0 && g->rank < g->world,
                     "%s: rank %d of %d (at most %d ranks)", name, g->rank, g->world, RFX_MAX_PEERS);
-        RFX_REQUIRE(g->epoch > 0 && g->arrival_counter, "%s: epoch must be > 0 and arrival_counter set", name);
+        RFX_REQUIRE((g->epoch > 0 || g->epoch_word) && g->arrival_counter,
+                    "%s: epoch must be > 0 (or epoch_word given) and arrival_counter set", name);
         for (int p = 0; p < g->world; ++p) {
             RFX_REQUIRE(g->peer_out[p] && g->peer_flags[p], "%s: null pointer for rank %d", name, p);
             RFX_REQUIRE(((uintptr_t)g->peer_out[p] % 16) == 0 && ((uintptr_t)g->peer_flags[p] % 4) == 0,
@@ -261,6 +274,8 @@ int launch_paged_combine(const RfxPagedAttentionArgs* a, const PlanLayout& L, co
         hg.status = P.hdr + HdrStatus;
         hg.spin_limit = g->spin_limit > 0 ? g->spin_limit : 10000000ll;
         hg.epoch = g->epoch;
+        hg.epoch_word = g->epoch_word;
+        hg.out_alt_offset = g->out_alt_offset;
         hg.world = g->world; hg.rank = g->rank; hg.wait = g->wait ? 1 : 0;
     }
     RFX_DISPATCH_DTYPE(a->dtype, T, {

@@ -8,6 +8,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <atomic>
+
 #include "../../include/reflex_b200.h"
 
 namespace rfx {
@@ -19,6 +21,27 @@ int fail(int status, const char* fmt, ...);
 int check_device();
 int sm_count();
 int check_launch(const char* what);
+
+// Debug switches: the comma-separated words of the environment variable REFLEX_B200_DEBUG, read once
+// (std::call_once), or whatever rfx_debug_set_flags() put in their place. One atomic word; nothing
+// else in the library looks at the environment.
+enum : uint32_t {
+    kDbgNoTensorCore = 1u,    // "no_tc": the scalar kernels instead of the tcgen05 ones (attention, linear + norm)
+    kDbgPrefillNoSplit = 2u,  // "prefill_nosplit": chunked prefill streams whole contexts per CTA
+    kDbgMixedOn = 4u,         // "mixed=1": one-row requests of a split batch always go to the decode kernel
+    kDbgMixedOff = 8u,        // "mixed=0": never
+    kDbgTma2d = 16u,          // "tma2d": the decode kernel's 2-D tensor maps (one copy per 128-byte half)
+};
+uint32_t debug_flags();
+
+// "Done once per device" marks (an opt-in attribute set, a cached query). Atomic, so that host threads
+// may race to do the work twice but never see a torn value.
+struct PerDeviceOnce {
+    std::atomic<int> v[64];
+    bool done(int dev) const { return dev >= 0 && dev < 64 && v[dev].load(std::memory_order_acquire) != 0; }
+    void mark(int dev, int value = 1) { if (dev >= 0 && dev < 64) v[dev].store(value, std::memory_order_release); }
+    int value(int dev) const { return (dev >= 0 && dev < 64) ? v[dev].load(std::memory_order_acquire) : 0; }
+};
 
 #define RFX_REQUIRE(cond, ...)                                   \
     do {                                                         \

@@ -1,6 +1,9 @@
 // Status plumbing and device checks shared by every entry point of libreflex_b200.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
+
+#include <mutex>
 
 #include "common.cuh"
 
@@ -29,8 +32,10 @@ struct DevInfo {
     int major = 0, minor = 0;
 };
 static DevInfo g_dev[64];
+static std::mutex g_dev_mutex;
 
 static int probe(int dev) {
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
     DevInfo& d = g_dev[dev];
     if (d.known) return d.known;
     cudaDeviceProp p;
@@ -67,6 +72,35 @@ int sm_count() {
     return g_dev[dev].sms > 0 ? g_dev[dev].sms : 148;
 }
 
+static uint32_t parse_debug_words(const char* csv) {
+    uint32_t f = 0;
+    if (!csv) return 0;
+    const char* p = csv;
+    while (*p) {
+        const char* e = strchr(p, ',');
+        const size_t n = e ? (size_t)(e - p) : strlen(p);
+        auto is = [&](const char* w) { return strlen(w) == n && strncmp(p, w, n) == 0; };
+        if (is("no_tc")) f |= kDbgNoTensorCore;
+        else if (is("prefill_nosplit")) f |= kDbgPrefillNoSplit;
+        else if (is("mixed=1")) f |= kDbgMixedOn;
+        else if (is("mixed=0")) f |= kDbgMixedOff;
+        else if (is("tma2d")) f |= kDbgTma2d;
+        p += n + (e ? 1 : 0);
+    }
+    return f;
+}
+
+static std::atomic<uint32_t> g_debug_flags{0};
+static std::atomic<int> g_debug_set{0};  // 1: rfx_debug_set_flags has spoken
+static std::once_flag g_debug_env_once;
+
+uint32_t debug_flags() {
+    if (g_debug_set.load(std::memory_order_acquire)) return g_debug_flags.load(std::memory_order_acquire);
+    static uint32_t from_env = 0;
+    std::call_once(g_debug_env_once, [] { from_env = parse_debug_words(getenv("REFLEX_B200_DEBUG")); });
+    return from_env;
+}
+
 int check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "%s: %s", what, cudaGetErrorString(e));
@@ -80,6 +114,17 @@ extern "C" {
 int rfx_abi_version(void) { return RFX_ABI_VERSION; }
 
 const char* rfx_last_error(void) { return rfx::g_err; }
+
+int rfx_debug_set_flags(const char* words) {
+    using namespace rfx;
+    if (!words) {  // back to what the environment said
+        g_debug_set.store(0, std::memory_order_release);
+        return RFX_SUCCESS;
+    }
+    g_debug_flags.store(parse_debug_words(words), std::memory_order_release);
+    g_debug_set.store(1, std::memory_order_release);
+    return RFX_SUCCESS;
+}
 
 size_t rfx_args_size(int which) {
     switch (which) {

@@ -2,25 +2,33 @@
 //
 // HBM-bound: every item (a run of 64-key tiles of one (request, kv_head) pair) streams its
 // K and V pages exactly once. One persistent CTA per SM owns one equal run of the tile
-// stream and has one producer warp and one (optionally two) group of four consumer warps:
-//   producer : loads its run's item descriptors in one round trip, keeps the block-table
-//              entries of the current and the next item in registers (32 per lane-window),
-//              and issues one TMA tile copy per page for K and for V into a ring of 64-key
-//              stages; each copy lands the page as [half][row][128 B] with the 128-byte
-//              swizzle, completion counted on the stage's mbarrier. With an item's first
-//              stage it also bulk-copies the G query rows and the RoPE table rows;
+// stream; it has four producer warps and one or two groups of four consumer warps:
+//   producers: each loads the run's item descriptors in one round trip, keeps the block-table
+//              entries of the current and the next item in registers (32 per lane-window), and
+//              fills the stages whose number in the CTA's sequence is its own modulo four: one
+//              TMA tile copy per page for K and for V into a ring of 64-key stages; each copy
+//              lands the page as [half][row][128 B] with the 128-byte swizzle, completion counted
+//              on the stage's mbarrier. With an item's first stage go the G query rows and the
+//              RoPE table rows. (Filling a stage costs a warp 1200-1900 cycles -- a barrier
+//              poll, the page look-up, 90 cycles per copy instruction -- while the stage's bytes
+//              arrive in 770-1500: a single producer warp was the limit of the kernel.)
 //   consumers: each warp takes 16 of the stage's 64 keys as the 16 MMA rows and the group's
 //              heads as the columns: S^T = K.Q^T, softmax down the columns, O^T += V^T.P^T,
 //              all through m16n8k16 warp MMAs fed by conflict-free ldmatrix. At the item's
-//              last stage the warps merge (m, l, acc) through shared memory and write one
-//              partial. With two groups, stages alternate between them.
-// RoPE is fused into the Q load with torch's per-op rounding.
+//              last stage the warps merge (m, l, acc) through shared memory. With two groups,
+//              stages alternate between them (a lone warp per scheduler runs at a third of an
+//              instruction per cycle; two hide each other's latencies).
+// An item that is a whole pair writes its output rows directly; of a pair cut into several
+// items the last one to finish merges the partials of all (a counter per pair), so that no
+// combine kernel follows. RoPE is fused into the Q load with torch's per-op rounding.
+// int8 pools (one fp32 scale per position and kv head) widen K and V to fp16 in registers
+// and run the same MMAs in fp16; the scales multiply the scores and the probabilities.
 //
 // Algorithmic bytes per item: 2 * keys * D * e (K and V). Arithmetic is G FLOP/byte, far
-// below what the warp MMA path sustains; the kernel's roofline is HBM bandwidth, and on a
-// 1000 W part streaming at full rate what is left to tune is the energy spent per byte.
+// below what the warp MMA path sustains; the kernel's roofline is HBM bandwidth.
 #include <stdlib.h>
 
+#include <mutex>
 #include <type_traits>
 
 #include "paged_plan.cuh"
@@ -848,15 +856,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 static EncodeTiledFn encode_fn() {
     static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
+    static std::once_flag once;
+    std::call_once(once, [] {
         void* p = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
             q == cudaDriverEntryPointSuccess)
             fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
+    });
     return fn;
 }
 
@@ -952,13 +959,13 @@ static int launch_decode_t(const RfxPagedAttentionArgs* a, const CUtensorMap& km
     using S = DecodeSmem<HD, GP, STAGES, Q8>;
     static_assert(S::total <= 232448, "decode kernel shared memory exceeds the sm_100 per-CTA limit");
     auto kern = decode_mma_kernel<T, HD, GP, STAGES, GROUPS, Q8>;
-    static bool attr_set[64] = {};  // per instantiation and device
+    static PerDeviceOnce attr_set;  // per instantiation
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (!attr_set.done(dev)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::total);
         if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "decode smem opt-in (%zu B): %s", S::total, cudaGetErrorString(e));
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        attr_set.mark(dev);
     }
     cudaError_t le = launch_pdl(kern, dim3(decode_mma_ctas(a)), dim3((kGroupWarps * GROUPS + kProducers) * 32), S::total,
                                 as_stream(a->stream), km, vm, P);
@@ -973,12 +980,7 @@ int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const P
     const int R = (int)(a->block_size < 64 ? a->block_size : 64);
     CUtensorMap km, vm;
     const uint64_t rows = (uint64_t)(a->num_blocks * a->num_kv_heads * a->block_size);
-    static int force_2d = -1;  // REFLEX_B200_TMA2D=1 selects the 2-D maps (debugging aid)
-    if (force_2d < 0) {
-        const char* e = getenv("REFLEX_B200_TMA2D");
-        force_2d = (e && e[0] == '1') ? 1 : 0;
-    }
-    int map2d = force_2d;
+    int map2d = (debug_flags() & kDbgTma2d) ? 1 : 0;  // the 2-D maps: a debugging aid
     int r1 = 0, r2 = 0;
     if (a->kv_int8) {
         map2d = 0;

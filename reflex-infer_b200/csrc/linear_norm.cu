@@ -343,13 +343,13 @@ norm_rows_kernel(T* __restrict__ out, const float* __restrict__ stats, const T* 
 template <typename T>
 static int launch_ln_tc(const CUtensorMap& xm, const CUtensorMap& wm, const LnGemmParams& P, dim3 grid, cudaStream_t s) {
     auto kern = linear_stats_tc_kernel<T>;
-    static bool attr_set[64] = {};  // per instantiation and device
+    static PerDeviceOnce attr_set;  // per instantiation
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (!attr_set.done(dev)) {
         cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLnSmem);
         if (ce != cudaSuccess) return fail(RFX_CUDA_ERROR, "linear GEMM smem opt-in: %s", cudaGetErrorString(ce));
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        attr_set.mark(dev);
     }
     kern<<<grid, kLnThreads, kLnSmem, s>>>(xm, wm, P);
     return check_launch("rfx_fused_linear_norm (GEMM)");
@@ -366,7 +366,7 @@ static int validate_ln(const RfxLinearNormArgs* a, const char* name) {
 }
 
 static bool ln_tensor_ok(const RfxLinearNormArgs* a) {
-    if (a->force_generic || getenv("REFLEX_B200_NO_TC")) return false;
+    if (a->force_generic || (debug_flags() & kDbgNoTensorCore)) return false;
     if (a->dtype != RFX_BF16 && a->dtype != RFX_F16) return false;
     if (a->K % 8 || a->N % 8) return false;  // 16-byte row pitch for the tensor maps and the vector stores
     if (((uintptr_t)a->x % 16) || ((uintptr_t)a->weight % 16) || ((uintptr_t)a->out % 16)) return false;

@@ -3,6 +3,8 @@
 // buffers and flag arrays of the head gather. Setup-time code, nothing here is on a hot path.
 #include <cuda.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace rfx {
@@ -11,15 +13,14 @@ using AddressRangeFn = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
 
 static AddressRangeFn address_range_fn() {
     static AddressRangeFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
+    static std::once_flag once;
+    std::call_once(once, [] {
         void* p = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) == cudaSuccess &&
             q == cudaDriverEntryPointSuccess)
             fn = reinterpret_cast<AddressRangeFn>(p);
-    }
+    });
     return fn;
 }
 

@@ -578,13 +578,13 @@ template <typename T, bool MASK = false>
 static int launch_prefill_t(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm,
                             const PrefillParams& P, int grid, cudaStream_t stream) {
     auto kern = prefill_tc_kernel<T, MASK>;
-    static bool attr_set[64] = {};
+    static PerDeviceOnce attr_set;  // per instantiation
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (!attr_set.done(dev)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PfSmem::total);
         if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "prefill smem opt-in: %s", cudaGetErrorString(e));
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        attr_set.mark(dev);
     }
     kern<<<grid, kPfThreads, PfSmem::total, stream>>>(qm, km, vm, P);
     return check_launch("prefill_tc_kernel");
@@ -603,7 +603,7 @@ static int log2_of(int v) {
 // Dense fused_attention on tensor cores: q [B,H,Sq,D], k/v [B,Hkv,Sk,D]. Returns
 // RFX_NOT_IMPLEMENTED for shapes the kernel does not cover (the caller then runs the scalar kernel).
 bool dense_tensor_ok(const RfxAttentionArgs* a) {
-    if (getenv("REFLEX_B200_NO_TC")) return false;
+    if (debug_flags() & kDbgNoTensorCore) return false;
     if (a->dtype != RFX_BF16 && a->dtype != RFX_F16) return false;
     if (a->head_dim != kPfHD) return false;
     if (a->attn_mask && !(a->sm_scale > 0.f)) return false;  // the mask is folded in as mask / scale
@@ -663,7 +663,7 @@ int launch_dense_tensor(const RfxAttentionArgs* a) {
 
 // Paged (chunked) prefill: q [N,Hq,D] already rotated, K/V in the pool.
 bool prefill_paged_supported(const RfxPagedAttentionArgs* a) {
-    if (a->force_generic || getenv("REFLEX_B200_NO_TC")) return false;
+    if (a->force_generic || (debug_flags() & kDbgNoTensorCore)) return false;
     if (a->dtype != RFX_BF16 && a->dtype != RFX_F16) return false;
     if (a->kv_int8) return false;  // query chunks over an int8 pool run the scalar kernel
     if (a->head_dim != kPfHD || a->rope_cos) return false;
@@ -680,7 +680,7 @@ bool prefill_paged_supported(const RfxPagedAttentionArgs* a) {
 // head, tile pair) would otherwise stream a whole context, however uneven the contexts are).
 // It needs key ranges that start on a K/V box boundary: items start at multiples of 64 keys.
 bool prefill_paged_split(const RfxPagedAttentionArgs* a) {
-    if (a->target_chunk < 0 || getenv("REFLEX_B200_PREFILL_NOSPLIT")) return false;
+    if (a->target_chunk < 0 || (debug_flags() & kDbgPrefillNoSplit)) return false;
     return a->block_size <= kPlanTile && kPlanTile % a->block_size == 0 && a->max_q_len <= 512;
 }
 
@@ -694,10 +694,10 @@ int prefill_paged_parts(const RfxPagedAttentionArgs* a) { (void)a; return 4 * sm
 // at HBM speed, and both kernels leave partials for the one combine. With few decode rows the
 // hand-over does not pay: the decode kernel's CTAs take the plan's runs in a fixed order and
 // the decode rows are spread unevenly over them. The host sees only the totals, so the rule is
-// "at most four query rows per request on average"; REFLEX_B200_MIXED=0/1 overrides it.
+// "at most four query rows per request on average"; the debug words mixed=0 / mixed=1 override it.
 bool prefill_paged_mixed(const RfxPagedAttentionArgs* a) {
     if (!prefill_paged_split(a) || !decode_mma_shape_ok(a)) return false;
-    if (const char* e = getenv("REFLEX_B200_MIXED")) return e[0] == '1';
+    if (debug_flags() & (kDbgMixedOn | kDbgMixedOff)) return (debug_flags() & kDbgMixedOn) != 0;
     return a->n_q <= 4 * a->batch;
 }
 

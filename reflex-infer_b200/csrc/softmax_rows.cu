@@ -354,9 +354,15 @@ extern "C" int rfx_online_softmax(const RfxSoftmaxArgs* a) {
 #define RFX_SOFTMAX_REG(T, TPR, ITEMS)                                                                          \
     do {                                                                                                        \
         auto kern = (ITEMS <= 2) ? softmax_rows_reg_small_kernel<T, TPR, ITEMS> : softmax_rows_reg_kernel<T, TPR, ITEMS>; \
-        static int per_sm = 0;                                                                                  \
-        if (!per_sm && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kVecThreads, 0) != cudaSuccess) \
-            per_sm = 1;                                                                                         \
+        static PerDeviceOnce occ;  /* resident CTAs per SM of this instantiation, by device */                   \
+        int dev_ = 0;                                                                                           \
+        cudaGetDevice(&dev_);                                                                                   \
+        int per_sm = occ.value(dev_);                                                                           \
+        if (!per_sm) {                                                                                          \
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kVecThreads, 0) != cudaSuccess || per_sm < 1) \
+                per_sm = 1;                                                                                     \
+            occ.mark(dev_, per_sm);                                                                             \
+        }                                                                                                       \
         const int64_t wave = (TPR == 32 || sizeof(T) != 4 || ITEMS < 4) ? cap : (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);  \
         const int64_t g2 = groups < wave ? groups : wave;                                                       \
         kern<<<(int)g2, kVecThreads, 0, s>>>((const T*)a->x, (T*)a->y, a->rows, n, a->is_causal, a->log);       \

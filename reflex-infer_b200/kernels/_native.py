@@ -145,6 +145,7 @@ class HeadGatherArgs(C.Structure):
         ("world", C.c_int), ("rank", C.c_int),
         ("peer_out", vp * RFX_MAX_PEERS), ("peer_flags", vp * RFX_MAX_PEERS),
         ("arrival_counter", vp), ("epoch", C.c_uint32), ("wait", C.c_int), ("spin_limit", i64),
+        ("epoch_word", vp), ("out_alt_offset", i64),
     ]
 
 
@@ -155,6 +156,7 @@ class PeerHandle(C.Structure):
 # Every symbol include/reflex_b200.h declares: (name, restype, argtypes).
 EXPORTS = {
     "rfx_abi_version": (C.c_int, []),
+    "rfx_debug_set_flags": (C.c_int, [C.c_char_p]),
     "rfx_args_size": (C.c_size_t, [C.c_int]),
     "rfx_status_string": (C.c_char_p, [C.c_int]),
     "rfx_last_error": (C.c_char_p, []),

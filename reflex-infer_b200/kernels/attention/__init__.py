@@ -293,6 +293,17 @@ class PagedAttentionCall:
             N.check(self._lib.rfx_paged_attention_gather(self._ref, C.byref(g)))
         return full
 
+    def run_gather_replayable(self, gather) -> None:
+        """``run_gather`` in the form a CUDA graph can replay: nothing in the launch arguments changes
+        from step to step (``gather.replayable_args()``); the n-th launch leaves its result in
+        ``gather.output_of(n)``."""
+        import ctypes as C
+        g = gather.replayable_args()
+        self._args.reuse_plan = 0
+        self._args.stream = N.stream_handle(self.device)
+        with torch.cuda.device(self.device):
+            N.check(self._lib.rfx_paged_attention_gather(self._ref, C.byref(g)))
+
     def combine_gather(self, gather) -> torch.Tensor:
         """The combine stage alone, with the gather (after ``plan()`` and ``partials()``)."""
         import ctypes as C

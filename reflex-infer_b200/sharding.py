@@ -191,6 +191,23 @@ class FusedHeadGather:
             a.peer_out[p] = self.ptrs[p] + off
         return a, self.full[self.epoch & 1]
 
+    def replayable_args(self):
+        """Arguments for a step that is captured once in a CUDA graph and replayed: the epoch lives in
+        a device word the kernel advances itself, and the kernel picks the output buffer from the
+        epoch's parity. ``output_of(n)`` is the tensor the n-th launch (n = 1, 2, ...) wrote."""
+        if not hasattr(self, "epoch_word"):
+            self.epoch_word = torch.zeros(1, dtype=torch.int32, device=self.device)
+        a = self._args
+        a.epoch = 0
+        a.epoch_word = self.epoch_word.data_ptr()
+        a.out_alt_offset = self.out_bytes
+        for p in range(self.world):
+            a.peer_out[p] = self.ptrs[p] + self.FLAG_BYTES
+        return a
+
+    def output_of(self, n: int) -> torch.Tensor:
+        return self.full[n & 1]
+
     def close(self) -> None:
         from kernels import _native as N
         torch.cuda.synchronize(self.device)

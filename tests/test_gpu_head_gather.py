@@ -102,3 +102,31 @@ def test_gather_argument_checks(native):
     gather._args.rank = 3                      # outside the group
     with pytest.raises(ValueError):
         call.run_gather(gather)
+
+
+def test_gather_step_replays_from_a_cuda_graph(native):
+    """The step with the gathering combine captured once and replayed: the epoch advances in a device
+    word and the kernel alternates between the two output buffers by itself (one rank; its own flag
+    is the only one it waits for)."""
+    cpu, g = _batch(seed=31)
+    call = _call(g)
+    want = _staged(call)
+    gather = FusedHeadGather(g.q_new.shape[0], g.Hq, g.D, g.dtype, DEV, None)
+    call.run_gather_replayable(gather)          # launch 1, outside the graph (first use of the kernels)
+    torch.cuda.synchronize()
+    assert torch.equal(gather.output_of(1), want)
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            call.run_gather_replayable(gather)
+    torch.cuda.synchronize()
+    for n in (2, 3, 4):
+        gather.output_of(n).fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert call.workspace.status() == 0
+        assert int(gather.epoch_word.item()) == n
+        assert torch.equal(gather.output_of(n), want), f"replay {n}"
+        flags = gather.buf[:4].view(torch.int32)
+        assert int(flags[0]) == n

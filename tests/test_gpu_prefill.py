@@ -16,6 +16,19 @@ pytestmark = [pytest.mark.gpu]
 DEV = "cuda"
 
 
+import contextlib
+
+
+@contextlib.contextmanager
+def _debug(native, words):
+    """The library's debug switches for the duration of a block (rfx_debug_set_flags)."""
+    native.lib().rfx_debug_set_flags(words.encode())
+    try:
+        yield
+    finally:
+        native.lib().rfx_debug_set_flags(None)
+
+
 def _causal(n):
     return torch.triu(torch.full((n, n), float("-inf")), 1)
 
@@ -62,9 +75,9 @@ def test_dense_additive_mask_on_tensor_core_kernel(B, H, Hkv, Sq, Sk, causal, dt
     refb = oracle.naive_attention_f64(q, k, v, mask=torch.zeros(Sq, Sk).masked_fill(far, float("-inf")).double()
                                       + (_causal(Sq) if causal else 0.0))
     torch.testing.assert_close(ob.cpu().double(), refb, atol=tol, rtol=tol)
-    monkeypatch.setenv("REFLEX_B200_NO_TC", "1")
-    os_ = fused_attention(q.to(DEV), k.to(DEV), v.to(DEV), attn_mask=bias.to(DEV), is_causal=causal)
-    assert kernels.attention.last_dense_kernel_kind == 0
+    with _debug(native, "no_tc"):
+        os_ = fused_attention(q.to(DEV), k.to(DEV), v.to(DEV), attn_mask=bias.to(DEV), is_causal=causal)
+        assert kernels.attention.last_dense_kernel_kind == 0
     torch.testing.assert_close(o.float(), os_.float(), atol=tol, rtol=tol)
 
 
@@ -73,8 +86,8 @@ def test_dense_prefill_matches_scalar_kernel(native, monkeypatch):
     k = golden_io.pattern((1, 2, 384, 128), torch.bfloat16, 5, scale=0.5).to(DEV)
     v = golden_io.pattern((1, 2, 384, 128), torch.bfloat16, 6).to(DEV)
     a = fused_attention(q, k, v, is_causal=True)
-    monkeypatch.setenv("REFLEX_B200_NO_TC", "1")
-    b = fused_attention(q, k, v, is_causal=True)
+    with _debug(native, "no_tc"):
+        b = fused_attention(q, k, v, is_causal=True)
     torch.testing.assert_close(a.float(), b.float(), atol=2e-2, rtol=2e-2)
 
 
@@ -142,11 +155,11 @@ def test_chunked_prefill_mixed_batch_tensor_core(bs, native, monkeypatch):
         assert ws.status() == 0 and torch.isfinite(out_c).all()
         torch.testing.assert_close(out_c.cpu().float(), ref.float(), atol=2e-2, rtol=2e-2)
     # the one-row requests handed to the decode kernel (on by itself only for decode-heavy batches)
-    monkeypatch.setenv("REFLEX_B200_MIXED", "1")
-    call = PagedAttentionCall(q_rot.to(DEV), kc.to(DEV), vc.to(DEV), g.block_table, g.context_lens, **kw)
-    if bs <= 64:
-        assert call.kernel_kind == 3
-    out_m = call.run()
+    with _debug(native, "mixed=1"):
+        call = PagedAttentionCall(q_rot.to(DEV), kc.to(DEV), vc.to(DEV), g.block_table, g.context_lens, **kw)
+        if bs <= 64:
+            assert call.kernel_kind == 3
+        out_m = call.run()
     assert ws.status() == 0
     torch.testing.assert_close(out_m.cpu().float(), ref.float(), atol=2e-2, rtol=2e-2)
 
