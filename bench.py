@@ -90,7 +90,7 @@ def parse_args():
     ap.add_argument("--shard", default=None, choices=["replica", "request", "head"],
                     help="default: request (strong scaling); a multi-GPU run without this flag also measures "
                          "the other modes and reports them under other_shards")
-    ap.add_argument("--only", default=None, choices=["cfg3", "cfg5", "linear_norm", "small_ops", "int8_kv"],
+    ap.add_argument("--only", default=None, choices=["cfg3", "cfg5", "linear_norm", "small_ops", "int8_kv", "clocks"],
                     help="run just that secondary block on one GPU and print it (small profiling cases: "
                          "--only cfg3 --requests 2)")
     ap.add_argument("--cpu-sample", type=int, default=0, help="requests in the CPU-baseline sample (0 = auto)")
@@ -749,6 +749,32 @@ def measure_int8_kv(args, device):
             "max_abs_err_vs_oracle": err, "status": ws.status()}
 
 
+def measure_steps_vs_clocks(args, device):
+    """The headline decode step timed over a short and a long run in one process, with the SM clock and
+    the board power sampled during each: does the rate depend on how long the GPU has been under load
+    (power cap, clocks)? `kernel_ms x MHz` is the kernel's length in SM cycles (millions)."""
+    out = {}
+    batch = build_batch("cfg4", device, 3, "request", 0, 1, args.requests)
+    packed, batch = pack_step_inputs(batch)
+    step = DecodeStep(batch)
+    kv = batch.kv_bytes()
+    for steps in (20, 400):
+        sampler = ClockSampler(device.index or 0)
+        sampler.start()
+        time.sleep(0.3)
+        sampler.mark_begin()
+        _, kern = timed_steps(step.run, steps, 3, None, None, with_kernel_events=True)
+        sampler.mark_end()
+        c = sampler.stop()
+        km = statistics.mean(kern)
+        out[f"{steps}_steps"] = {"kernel_ms": km, "kernel_ms_first5": statistics.mean(kern[:5]), "kernel_ms_last5": statistics.mean(kern[-5:]),
+                                 "gbs": kv / (km * 1e-3) / 1e9, "sm_mhz_median": c["sm_mhz"], "power_w_median": c.get("power_w_median"),
+                                 "power_w_max": c.get("power_w_max"), "reasons": c["reasons"],
+                                 "kernel_mcycles": km * 1e-3 * (c["sm_mhz"] or 0)}
+        time.sleep(1.0)
+    return out
+
+
 def measure_linear_norm(args, device):
     """Fused linear + norm on the shapes of the reference's own benchmark
     (benchmark/bench_fused_linear_norm.py:24-29): one call = GEMM with the row statistics in its
@@ -1055,7 +1081,7 @@ def run_only(args):
     device = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     block = {"cfg3": measure_prefill, "cfg5": measure_mixed, "linear_norm": measure_linear_norm,
-             "small_ops": measure_small_ops, "int8_kv": measure_int8_kv}[args.only](args, device)
+             "small_ops": measure_small_ops, "int8_kv": measure_int8_kv, "clocks": measure_steps_vs_clocks}[args.only](args, device)
     print(json.dumps({"only": args.only, "steps": args.steps, "warmup": args.warmup, **block}), flush=True)
 
 
