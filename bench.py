@@ -1003,7 +1003,7 @@ def run_ours(args):
         # DRAM bytes per algorithmic byte from the ncu captures summarised under profiles/
         # (decode_mma_kernel_cfg4.md: 16-request case, traffic grows in proportion to the keys;
         # decode_mma_kernel_cfg2.md: the whole configuration).
-        ratio = {"cfg4": 1.0043, "cfg2": 1.0357}[args.workload]
+        ratio = {"cfg4": 1.0049, "cfg2": 1.0386}[args.workload]
         if res["kernel_kind"] == 1:
             line["roofline"]["traffic"] = ratio * res["kv_bytes"]
             line["roofline"]["traffic_note"] = f"{ratio} x algorithmic bytes, ncu dram__bytes_read+write, see profiles/"
