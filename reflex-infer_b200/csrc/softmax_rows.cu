@@ -9,6 +9,8 @@
 //     vectors over the aligned body of the row with scalar head and tail, so odd lengths and
 //     unaligned rows still move full sectors;
 //   * longer rows: three passes over global memory.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace rfx {
@@ -25,6 +27,23 @@ __device__ inline float block_reduce(float v, bool is_max, float* red) {
     __syncthreads();
     float r = is_max ? -INFINITY : 0.f;
     for (int i = 0; i < nw; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];
+    return r;
+}
+
+// Over the TPR threads that share a row: a warp (shuffles only) or the whole CTA of TPR threads.
+template <int TPR>
+__device__ inline float row_reduce(float v, bool is_max, float* red) {
+    if (TPR == 32) return is_max ? warp_max(v) : warp_sum(v);
+    if (TPR == kVecThreads) return block_reduce(v, is_max, red);
+    constexpr int WPR = TPR / 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, first = (warp / WPR) * WPR;
+    v = is_max ? warp_max(v) : warp_sum(v);
+    __syncthreads();  // red[] may still be read from a previous reduction
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = is_max ? -INFINITY : 0.f;
+#pragma unroll
+    for (int i = 0; i < WPR; ++i) r = is_max ? fmaxf(r, red[first + i]) : r + red[first + i];
     return r;
 }
 
@@ -51,6 +70,35 @@ template <> __device__ __forceinline__ void put2<__half>(__half* dst, float a, f
     *reinterpret_cast<__half2*>(dst) = __floats2half2_rn(a, b);
 }
 
+// Two 16-bit values in one 32-bit word: widened to fp32 (bf16 by moving bits, fp16 by the packed
+// conversion) and compared two at a time (the maximum of two 16-bit values is one of them, so the
+// packed maximum is exact and, like fmaxf, returns the other operand when one is NaN).
+template <typename T> __device__ __forceinline__ float2 widen2(uint32_t w);
+template <> __device__ __forceinline__ float2 widen2<__nv_bfloat16>(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 widen2<__half>(uint32_t w) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+template <typename T> __device__ __forceinline__ uint32_t max2_16(uint32_t a, uint32_t b);
+template <> __device__ __forceinline__ uint32_t max2_16<__nv_bfloat16>(uint32_t a, uint32_t b) {
+    const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <> __device__ __forceinline__ uint32_t max2_16<__half>(uint32_t a, uint32_t b) {
+    const __half2 r = __hmax2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <typename T> __device__ __forceinline__ uint32_t pack2_16(float2 v);
+template <> __device__ __forceinline__ uint32_t pack2_16<__nv_bfloat16>(float2 v) {
+    const __nv_bfloat162 r = __floats2bfloat162_rn(v.x, v.y);
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <> __device__ __forceinline__ uint32_t pack2_16<__half>(float2 v) {
+    const __half2 r = __floats2half2_rn(v.x, v.y);
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
 // Register kernel: n % V == 0, rows 16-byte aligned, n <= TPR * kVecItems * V. TPR threads
 // share a row: a whole CTA (two block reductions) or one warp (shuffles only, eight rows
 // per CTA). exp through ex2 of the pre-scaled difference, one reciprocal per row.
@@ -60,7 +108,7 @@ template <typename T, int TPR, int ITEMS>
 __device__ __forceinline__ void
 softmax_rows_reg_body(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n, int causal, int is_log) {
     constexpr int V = 16 / sizeof(T);
-    constexpr int RPC = kVecThreads / TPR;  // rows per CTA
+    constexpr int RPC = TPR == 32 ? kVecThreads / 32 : 1;  // rows per CTA: eight warps with a row each, or one row
     constexpr float kLog2e = 1.4426950408889634f;
     __shared__ float red[32];
     const int nvec = n / V;
@@ -73,7 +121,7 @@ softmax_rows_reg_body(const T* __restrict__ x, T* __restrict__ y, int64_t rows, 
     // current row's reductions and stores (fp32 8192 x 8192: 152 -> 91 us, 4096 x 4096: 39 -> 29 us).
     // Measured slower with it, and so left as they were: 16-bit rows (twice the arithmetic per
     // byte; 8192 x 8192 bf16 72 -> 90 us), short rows, and a warp per row.
-    constexpr bool PIPE = TPR != 32 && sizeof(T) == 4 && ITEMS >= 4;
+    constexpr bool PIPE = TPR == kVecThreads && sizeof(T) == 4 && ITEMS >= 4;
     Vec16<T> nxt[PIPE ? ITEMS : 1];
     auto fetch = [&](int64_t grp) {
         const int64_t row = grp * RPC + sub;
@@ -95,6 +143,88 @@ softmax_rows_reg_body(const T* __restrict__ x, T* __restrict__ y, int64_t rows, 
         const Vec16<T>* xr = reinterpret_cast<const Vec16<T>*>(x + row * (int64_t)n);
         Vec16<T>* yr = reinterpret_cast<Vec16<T>*>(y + row * (int64_t)n);
         const int valid = causal ? (int)(row % n) + 1 : n;  // columns [0, valid) take part
+        if constexpr (sizeof(T) == 2) {
+            // 16-bit rows stay in registers in their own type (four registers per 16-byte vector, as for
+            // fp32 rows) and are widened in each of the three passes: what bounds these rows is the bytes a
+            // thread has in flight, and as fp32 copies they took twice the registers per byte of an fp32 row.
+            // The exponentials are evaluated twice (sum, output). Two elements per instruction wherever the
+            // arithmetic allows it (packed maximum on the raw words, packed fp32 multiply-add / add / multiply).
+            constexpr int W = V / 2;  // 32-bit words per vector
+            constexpr uint32_t kNegInf2 = std::is_same<T, __nv_bfloat16>::value ? 0xff80ff80u : 0xfc00fc00u;
+            constexpr uint32_t kNegInfLo = kNegInf2 & 0xffffu, kNegInfHi = kNegInf2 & 0xffff0000u;
+            uint32_t raw[ITEMS][W];
+            uint32_t m2 = kNegInf2;
+#pragma unroll
+            for (int it = 0; it < ITEMS; ++it) {
+                const int vi = it * TPR + tr;
+#pragma unroll
+                for (int k = 0; k < W; ++k) raw[it][k] = kNegInf2;  // masked columns and vectors past the row
+                if (live && vi < nvec && vi * V < valid) {
+                    const Vec16<T> p = xr[vi];
+                    const uint32_t* w = reinterpret_cast<const uint32_t*>(&p);
+#pragma unroll
+                    for (int k = 0; k < W; ++k) raw[it][k] = w[k];
+                    if (vi * V + V > valid) {  // the vector the causal boundary cuts
+#pragma unroll
+                        for (int k = 0; k < W; ++k) {
+                            if (vi * V + 2 * k >= valid) raw[it][k] = (raw[it][k] & 0xffff0000u) | kNegInfLo;
+                            if (vi * V + 2 * k + 1 >= valid) raw[it][k] = (raw[it][k] & 0xffffu) | kNegInfHi;
+                        }
+                    }
+#pragma unroll
+                    for (int k = 0; k < W; ++k) m2 = max2_16<T>(m2, raw[it][k]);
+                }
+            }
+            // The compiler must not keep the widened values from one pass to the next (it would: widening is
+            // pure), or the row is back to eight registers per vector.
+            auto forget = [&]() {
+#pragma unroll
+                for (int it = 0; it < ITEMS; ++it)
+#pragma unroll
+                    for (int k = 0; k < W; ++k) asm volatile("" : "+r"(raw[it][k]));
+            };
+            const float2 mm = widen2<T>(m2);
+            float m = fmaxf(mm.x, mm.y);
+            m = row_reduce<TPR>(m, true, red);
+            forget();
+            const float mb = m * kLog2e;
+            const float2 k2 = make_float2(kLog2e, kLog2e), nmb2 = make_float2(-mb, -mb);
+            float2 l2 = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int it = 0; it < ITEMS; ++it) {
+#pragma unroll
+                for (int k = 0; k < W; ++k) {
+                    const float2 t = __ffma2_rn(widen2<T>(raw[it][k]), k2, nmb2);
+                    l2 = __fadd2_rn(l2, make_float2(ex2_fast(t.x), ex2_fast(t.y)));  // 0 for masked columns
+                }
+            }
+            float l = l2.x + l2.y;
+            l = row_reduce<TPR>(l, false, red);
+            forget();
+            const float logl = logf(l);
+            const float inv = 1.0f / l;
+            const float2 inv2 = make_float2(inv, inv), nm2 = make_float2(-m, -m), nlogl2 = make_float2(-logl, -logl);
+#pragma unroll
+            for (int it = 0; it < ITEMS; ++it) {
+                const int vi = it * TPR + tr;
+                if (live && vi < nvec) {
+                    Vec16<T> o;
+                    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+                    for (int k = 0; k < W; ++k) {
+                        const float2 f = widen2<T>(raw[it][k]);
+                        if (is_log) {
+                            ow[k] = pack2_16<T>(__fadd2_rn(__fadd2_rn(f, nm2), nlogl2));
+                        } else {
+                            const float2 t = __ffma2_rn(f, k2, nmb2);
+                            ow[k] = pack2_16<T>(__fmul2_rn(make_float2(ex2_fast(t.x), ex2_fast(t.y)), inv2));
+                        }
+                    }
+                    yr[vi] = o;
+                }
+            }
+            continue;
+        }
         float f[ITEMS][V];
         float m = -INFINITY;
 #pragma unroll
@@ -125,7 +255,7 @@ softmax_rows_reg_body(const T* __restrict__ x, T* __restrict__ y, int64_t rows, 
             }
         }
         if (PIPE) fetch(grp + gridDim.x);
-        m = (TPR == 32) ? warp_max(m) : block_reduce(m, true, red);
+        m = row_reduce<TPR>(m, true, red);
         const float mb = m * kLog2e;
         float l = 0.f;
 #pragma unroll
@@ -144,7 +274,7 @@ softmax_rows_reg_body(const T* __restrict__ x, T* __restrict__ y, int64_t rows, 
                 }
             }
         }
-        l = (TPR == 32) ? warp_sum(l) : block_reduce(l, false, red);
+        l = row_reduce<TPR>(l, false, red);
         const float logl = logf(l);
         const float inv = 1.0f / l;
 #pragma unroll
@@ -165,19 +295,15 @@ softmax_rows_reg_body(const T* __restrict__ x, T* __restrict__ y, int64_t rows, 
     }
 }
 
-// Two entry points over the same body. Rows of one or two vectors per thread are bound by the warps
-// in flight (ncu: 40 of 64 warps at 48 registers): eight CTAs per SM asked for, which fits them
-// into 32 registers without spills (4096 x 4096 bf16 24.6 -> 22.5 us). Longer rows keep the plain
-// bound: any minimum-blocks hint made them slower (32768 x 1024 bf16 41 -> 61 us at the same
-// register count).
-template <typename T, int TPR, int ITEMS>
-__global__ void __launch_bounds__(kVecThreads)
+// MINB = resident CTAs per SM asked of the compiler. Rows of one or two fp32 vectors per thread are
+// bound by the warps in flight (ncu: 40 of 64 warps at 48 registers): eight CTAs per SM, which fits them
+// into 32 registers without spills (4096 x 4096 bf16 24.6 -> 22.5 us); longer fp32 rows keep the plain
+// bound (a hint made them slower). 16-bit rows are held raw, four registers per vector, and take the
+// bound that leaves room for just that: unbounded, the compiler spreads the widened values of a whole
+// pass over 120-240 registers and the occupancy is gone.
+template <typename T, int TPR, int ITEMS, int MINB>
+__global__ void __launch_bounds__(kVecThreads, MINB)
 softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n, int causal, int is_log) {
-    softmax_rows_reg_body<T, TPR, ITEMS>(x, y, rows, n, causal, is_log);
-}
-template <typename T, int TPR, int ITEMS>
-__global__ void __launch_bounds__(kVecThreads, 8)
-softmax_rows_reg_small_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n, int causal, int is_log) {
     softmax_rows_reg_body<T, TPR, ITEMS>(x, y, rows, n, causal, is_log);
 }
 
@@ -245,12 +371,23 @@ __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, 
             struct alignas(16) Vec { T v[V]; };
             const Vec* gb = reinterpret_cast<const Vec*>(xr + head);
             Vec* sb = reinterpret_cast<Vec*>(sr + head);
+            [[maybe_unused]] uint32_t m2 = std::is_same<T, __nv_bfloat16>::value ? 0xff80ff80u : 0xfc00fc00u;  // (-inf, -inf)
 #pragma unroll 4
             for (int vi = threadIdx.x; vi < nbody; vi += blockDim.x) {
                 const Vec p = gb[vi];
                 sb[vi] = p;
+                if constexpr (sizeof(T) == 2) {
+                    const uint32_t* w = reinterpret_cast<const uint32_t*>(&p);
 #pragma unroll
-                for (int j = 0; j < V; ++j) m = fmaxf(m, Num<T>::to_f(p.v[j]));
+                    for (int k = 0; k < V / 2; ++k) m2 = max2_16<T>(m2, w[k]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < V; ++j) m = fmaxf(m, Num<T>::to_f(p.v[j]));
+                }
+            }
+            if constexpr (sizeof(T) == 2) {
+                const float2 mm = widen2<T>(m2);
+                m = fmaxf(m, fmaxf(mm.x, mm.y));
             }
             for (int i = head + nbody * V + threadIdx.x; i < valid; i += blockDim.x) { const T v = xr[i]; sr[i] = v; m = fmaxf(m, Num<T>::to_f(v)); }
             m = block_reduce(m, true, red);  // also orders the smem writes before the reads below
@@ -260,11 +397,23 @@ __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, 
             float l = 0.f;
             const int tail0 = head + nbody * V;
             for (int i = threadIdx.x; i < head; i += blockDim.x) l += ex2_fast(fmaf(Num<T>::to_f(sr[i]), kLog2e, -mb));
+            [[maybe_unused]] const float2 k2 = make_float2(kLog2e, kLog2e), nmb2 = make_float2(-mb, -mb);
+            [[maybe_unused]] float2 l2 = make_float2(0.f, 0.f);
             for (int vi = threadIdx.x; vi < nbody; vi += blockDim.x) {
                 const Vec p = sb[vi];
+                if constexpr (sizeof(T) == 2) {
+                    const uint32_t* w = reinterpret_cast<const uint32_t*>(&p);
 #pragma unroll
-                for (int j = 0; j < V; ++j) l += ex2_fast(fmaf(Num<T>::to_f(p.v[j]), kLog2e, -mb));
+                    for (int k = 0; k < V / 2; ++k) {
+                        const float2 t = __ffma2_rn(widen2<T>(w[k]), k2, nmb2);
+                        l2 = __fadd2_rn(l2, make_float2(ex2_fast(t.x), ex2_fast(t.y)));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < V; ++j) l += ex2_fast(fmaf(Num<T>::to_f(p.v[j]), kLog2e, -mb));
+                }
             }
+            if constexpr (sizeof(T) == 2) l += l2.x + l2.y;
             for (int i = tail0 + threadIdx.x; i < valid; i += blockDim.x) l += ex2_fast(fmaf(Num<T>::to_f(sr[i]), kLog2e, -mb));
             l = block_reduce(l, false, red);
             const float logl = logf(l), inv = 1.0f / l;
@@ -284,10 +433,21 @@ __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, 
                     Vec o;
                     const int c0 = head_y + vi * V;
                     if (c0 + V <= valid && !is_log) {  // the usual case, two results per conversion
+                        if constexpr (sizeof(T) == 2) {
+                            const uint32_t* w = reinterpret_cast<const uint32_t*>(&p);
+                            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+                            const float2 inv2 = make_float2(inv, inv);
 #pragma unroll
-                        for (int j = 0; j < V; j += 2)
-                            put2<T>(&o.v[j], ex2_fast(fmaf(Num<T>::to_f(p.v[j]), kLog2e, -mb)) * inv,
-                                    ex2_fast(fmaf(Num<T>::to_f(p.v[j + 1]), kLog2e, -mb)) * inv);
+                            for (int k = 0; k < V / 2; ++k) {
+                                const float2 t = __ffma2_rn(widen2<T>(w[k]), k2, nmb2);
+                                ow[k] = pack2_16<T>(__fmul2_rn(make_float2(ex2_fast(t.x), ex2_fast(t.y)), inv2));
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < V; j += 2)
+                                put2<T>(&o.v[j], ex2_fast(fmaf(Num<T>::to_f(p.v[j]), kLog2e, -mb)) * inv,
+                                        ex2_fast(fmaf(Num<T>::to_f(p.v[j + 1]), kLog2e, -mb)) * inv);
+                        }
                     } else {
 #pragma unroll
                         for (int j = 0; j < V; ++j) o.v[j] = Num<T>::from_f(out_of(c0 + j, Num<T>::to_f(p.v[j])));
@@ -318,6 +478,40 @@ __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, 
     }
 }
 
+// One instantiation of the register kernel. The grid is one wave of resident CTAs (what the occupancy
+// query says fits) for long fp32 rows, each CTA walking several rows; the usual cap otherwise.
+template <typename T, int TPR, int ITEMS>
+static void launch_softmax_reg(const RfxSoftmaxArgs* a, int64_t groups, int64_t cap, cudaStream_t s) {
+    constexpr int kMinB = sizeof(T) == 2 ? (ITEMS <= 4 ? 8 : ITEMS <= 8 ? 4 : 2) : (ITEMS <= 2 ? 8 : 0);
+    auto kern = softmax_rows_reg_kernel<T, TPR, ITEMS, kMinB>;
+    static PerDeviceOnce occ;  // resident CTAs per SM of this instantiation, by device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int per_sm = occ.value(dev);
+    if (!per_sm) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, TPR == 32 ? kVecThreads : TPR, 0) != cudaSuccess || per_sm < 1)
+            per_sm = 1;
+        occ.mark(dev, per_sm);
+    }
+    const int64_t wave = (TPR == 32 || sizeof(T) != 4 || ITEMS < 4) ? cap : (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);
+    const int64_t g2 = groups < wave ? groups : wave;
+    kern<<<(int)g2, TPR == 32 ? kVecThreads : TPR, 0, s>>>((const T*)a->x, (T*)a->y, a->rows, (int)a->n, a->is_causal, a->log);
+}
+
+template <typename T, int TPR>
+static void launch_softmax_reg_items(const RfxSoftmaxArgs* a, int need, int64_t groups, int64_t cap, cudaStream_t s) {
+    if (need <= 1) launch_softmax_reg<T, TPR, 1>(a, groups, cap, s);
+    else if (need <= 2) launch_softmax_reg<T, TPR, 2>(a, groups, cap, s);
+    else if (need <= 4) launch_softmax_reg<T, TPR, 4>(a, groups, cap, s);
+    else launch_softmax_reg<T, TPR, 8>(a, groups, cap, s);
+}
+
+// 128 threads per row, four vectors each: 16-bit rows only.
+template <typename T>
+static void launch_softmax_reg_part(const RfxSoftmaxArgs* a, int64_t groups, int64_t cap, cudaStream_t s) {
+    if constexpr (sizeof(T) == 2) launch_softmax_reg<T, 128, 4>(a, groups, cap, s);
+}
+
 }  // namespace rfx
 
 extern "C" int rfx_online_softmax(const RfxSoftmaxArgs* a) {
@@ -346,38 +540,23 @@ extern "C" int rfx_online_softmax(const RfxSoftmaxArgs* a) {
     const bool reg_ok = n % V == 0 && n <= kVecThreads * kVecItems * V && ((uintptr_t)a->x % 16) == 0 &&
                         ((uintptr_t)a->y % 16) == 0;
     if (reg_ok) {
-        const bool warp_rows = n <= 32 * kVecItems * V;  // a warp per row, eight rows per CTA
-        const int64_t groups = warp_rows ? (a->rows + 7) / 8 : a->rows;
-        const int tpr = warp_rows ? 32 : kVecThreads;
-        const int need = ((n / V) + tpr - 1) / tpr;  // vectors per thread
-        // the grid is one wave of resident CTAs (what the occupancy query says fits), each walking several rows
-#define RFX_SOFTMAX_REG(T, TPR, ITEMS)                                                                          \
-    do {                                                                                                        \
-        auto kern = (ITEMS <= 2) ? softmax_rows_reg_small_kernel<T, TPR, ITEMS> : softmax_rows_reg_kernel<T, TPR, ITEMS>; \
-        static PerDeviceOnce occ;  /* resident CTAs per SM of this instantiation, by device */                   \
-        int dev_ = 0;                                                                                           \
-        cudaGetDevice(&dev_);                                                                                   \
-        int per_sm = occ.value(dev_);                                                                           \
-        if (!per_sm) {                                                                                          \
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kVecThreads, 0) != cudaSuccess || per_sm < 1) \
-                per_sm = 1;                                                                                     \
-            occ.mark(dev_, per_sm);                                                                             \
-        }                                                                                                       \
-        const int64_t wave = (TPR == 32 || sizeof(T) != 4 || ITEMS < 4) ? cap : (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);  \
-        const int64_t g2 = groups < wave ? groups : wave;                                                       \
-        kern<<<(int)g2, kVecThreads, 0, s>>>((const T*)a->x, (T*)a->y, a->rows, n, a->is_causal, a->log);       \
-    } while (0)
-#define RFX_SOFTMAX_ITEMS(T, TPR)                    \
-    if (need <= 1) RFX_SOFTMAX_REG(T, TPR, 1);       \
-    else if (need <= 2) RFX_SOFTMAX_REG(T, TPR, 2);  \
-    else if (need <= 4) RFX_SOFTMAX_REG(T, TPR, 4);  \
-    else RFX_SOFTMAX_REG(T, TPR, 8)
+        // Threads per row: a warp (eight rows per CTA of 256 threads) up to eight vectors per lane, else a
+        // CTA per row. What bounds these rows is the bytes in flight per SM = resident rows x row bytes, so
+        // a 16-bit row of up to 4096 elements takes a CTA of 128 threads (sixteen of them per SM; 4096 x 4096
+        // bf16 with 256 threads: 0.65 of the copy rate). Several rows in one CTA that reduce together, or a
+        // warp per row with sixteen vectors per lane, were measured slower (0.56 / 0.40).
+        const int nvec = n / V;
+        int tpr = kVecThreads;
+        if (nvec <= 32 * kVecItems) tpr = 32;
+        else if (e == 2 && nvec <= 128 * 4) tpr = 128;
+        const int rpc = tpr == 32 ? kVecThreads / 32 : 1;
+        const int64_t groups = (a->rows + rpc - 1) / rpc;
+        const int need = (nvec + tpr - 1) / tpr;  // vectors per thread
         RFX_DISPATCH_DTYPE(a->dtype, T, {
-            if (warp_rows) { RFX_SOFTMAX_ITEMS(T, 32); }
-            else { RFX_SOFTMAX_ITEMS(T, kVecThreads); }
+            if (tpr == 32) launch_softmax_reg_items<T, 32>(a, need, groups, cap, s);
+            else if (tpr == kVecThreads) launch_softmax_reg_items<T, kVecThreads>(a, need, groups, cap, s);
+            else launch_softmax_reg_part<T>(a, groups, 2 * cap, s);
         });
-#undef RFX_SOFTMAX_ITEMS
-#undef RFX_SOFTMAX_REG
         return check_launch(name);
     }
     const int threads = n <= 512 ? 64 : n <= 4096 ? 128 : n <= 16384 ? 256 : 1024;
