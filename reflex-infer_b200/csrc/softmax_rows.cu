@@ -195,7 +195,13 @@ softmax_rows_reg_body(const T* __restrict__ x, T* __restrict__ y, int64_t rows, 
 #pragma unroll
                 for (int k = 0; k < W; ++k) {
                     const float2 t = __ffma2_rn(widen2<T>(raw[it][k]), k2, nmb2);
-                    l2 = __fadd2_rn(l2, make_float2(ex2_fast(t.x), ex2_fast(t.y)));  // 0 for masked columns
+                    const float2 ex = make_float2(ex2_fast(t.x), ex2_fast(t.y));  // 0 for masked columns
+                    l2 = __fadd2_rn(l2, ex);
+                    // The exponentials take the place of the inputs, rounded to the row's type (the sum is
+                    // taken before the rounding): one exponential per element instead of two -- the XU pipe
+                    // was more than half busy -- at the price of a second rounding of the result, which stays
+                    // within one unit of the 16-bit type.
+                    if (!is_log) raw[it][k] = pack2_16<T>(ex);
                 }
             }
             float l = l2.x + l2.y;
@@ -213,12 +219,7 @@ softmax_rows_reg_body(const T* __restrict__ x, T* __restrict__ y, int64_t rows, 
 #pragma unroll
                     for (int k = 0; k < W; ++k) {
                         const float2 f = widen2<T>(raw[it][k]);
-                        if (is_log) {
-                            ow[k] = pack2_16<T>(__fadd2_rn(__fadd2_rn(f, nm2), nlogl2));
-                        } else {
-                            const float2 t = __ffma2_rn(f, k2, nmb2);
-                            ow[k] = pack2_16<T>(__fmul2_rn(make_float2(ex2_fast(t.x), ex2_fast(t.y)), inv2));
-                        }
+                        ow[k] = pack2_16<T>(is_log ? __fadd2_rn(__fadd2_rn(f, nm2), nlogl2) : __fmul2_rn(f, inv2));
                     }
                     yr[vi] = o;
                 }
@@ -372,7 +373,7 @@ __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, 
             const Vec* gb = reinterpret_cast<const Vec*>(xr + head);
             Vec* sb = reinterpret_cast<Vec*>(sr + head);
             [[maybe_unused]] uint32_t m2 = std::is_same<T, __nv_bfloat16>::value ? 0xff80ff80u : 0xfc00fc00u;  // (-inf, -inf)
-#pragma unroll 4
+#pragma unroll 8
             for (int vi = threadIdx.x; vi < nbody; vi += blockDim.x) {
                 const Vec p = gb[vi];
                 sb[vi] = p;
@@ -394,32 +395,45 @@ __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, 
             const float mb = m * kLog2e;
             // The two passes over the staged row read it as 16-byte vectors too: with one element per
             // load the kernel was bound by its instruction count, not by memory.
+            // For 16-bit rows of the plain softmax the exponentials replace the staged inputs, rounded to the
+            // row's type (the sum is taken before the rounding): one exponential per element instead of two
+            // (at two, the XU pipe needs 3.3 us for a 50 257-element row, which did not overlap the 4.6 us
+            // of memory time) at the price of a second rounding of the result, within one unit of the type.
+            constexpr bool kKeep = sizeof(T) == 2;
             float l = 0.f;
             const int tail0 = head + nbody * V;
-            for (int i = threadIdx.x; i < head; i += blockDim.x) l += ex2_fast(fmaf(Num<T>::to_f(sr[i]), kLog2e, -mb));
+            auto one = [&](int i) {
+                const float ex = ex2_fast(fmaf(Num<T>::to_f(sr[i]), kLog2e, -mb));
+                l += ex;
+                if (kKeep && !is_log) sr[i] = Num<T>::from_f(ex);
+            };
+            for (int i = threadIdx.x; i < head; i += blockDim.x) one(i);
             [[maybe_unused]] const float2 k2 = make_float2(kLog2e, kLog2e), nmb2 = make_float2(-mb, -mb);
             [[maybe_unused]] float2 l2 = make_float2(0.f, 0.f);
             for (int vi = threadIdx.x; vi < nbody; vi += blockDim.x) {
-                const Vec p = sb[vi];
+                Vec p = sb[vi];
                 if constexpr (sizeof(T) == 2) {
-                    const uint32_t* w = reinterpret_cast<const uint32_t*>(&p);
+                    uint32_t* w = reinterpret_cast<uint32_t*>(&p);
 #pragma unroll
                     for (int k = 0; k < V / 2; ++k) {
                         const float2 t = __ffma2_rn(widen2<T>(w[k]), k2, nmb2);
-                        l2 = __fadd2_rn(l2, make_float2(ex2_fast(t.x), ex2_fast(t.y)));
+                        const float2 ex = make_float2(ex2_fast(t.x), ex2_fast(t.y));
+                        l2 = __fadd2_rn(l2, ex);
+                        w[k] = pack2_16<T>(ex);
                     }
+                    if (!is_log) sb[vi] = p;
                 } else {
 #pragma unroll
                     for (int j = 0; j < V; ++j) l += ex2_fast(fmaf(Num<T>::to_f(p.v[j]), kLog2e, -mb));
                 }
             }
             if constexpr (sizeof(T) == 2) l += l2.x + l2.y;
-            for (int i = tail0 + threadIdx.x; i < valid; i += blockDim.x) l += ex2_fast(fmaf(Num<T>::to_f(sr[i]), kLog2e, -mb));
+            for (int i = tail0 + threadIdx.x; i < valid; i += blockDim.x) one(i);
             l = block_reduce(l, false, red);
             const float logl = logf(l), inv = 1.0f / l;
-            auto out_of = [&](int i, float v) -> float {
+            auto out_of = [&](int i, float v) -> float {  // v: the staged value (16-bit rows, plain softmax: its exponential)
                 if (i >= valid) return is_log ? -INFINITY : 0.f;
-                return is_log ? (v - m) - logl : ex2_fast(fmaf(v, kLog2e, -mb)) * inv;
+                return is_log ? (v - m) - logl : (kKeep ? v : ex2_fast(fmaf(v, kLog2e, -mb))) * inv;
             };
             if ((int)(((uintptr_t)yr % 16) / sizeof(T)) == mis) {
                 // output row aligned like the input row: vector k of the staged body is vector k of the output
@@ -438,10 +452,7 @@ __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, 
                             uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
                             const float2 inv2 = make_float2(inv, inv);
 #pragma unroll
-                            for (int k = 0; k < V / 2; ++k) {
-                                const float2 t = __ffma2_rn(widen2<T>(w[k]), k2, nmb2);
-                                ow[k] = pack2_16<T>(__fmul2_rn(make_float2(ex2_fast(t.x), ex2_fast(t.y)), inv2));
-                            }
+                            for (int k = 0; k < V / 2; ++k) ow[k] = pack2_16<T>(__fmul2_rn(widen2<T>(w[k]), inv2));
                         } else {
 #pragma unroll
                             for (int j = 0; j < V; j += 2)
@@ -559,8 +570,8 @@ extern "C" int rfx_online_softmax(const RfxSoftmaxArgs* a) {
         });
         return check_launch(name);
     }
-    const int threads = n <= 512 ? 64 : n <= 4096 ? 128 : n <= 16384 ? 256 : 1024;
     const size_t smem_need = (size_t)n * e + 32;  // the row in its own type + room for its misalignment
+    const int threads = n <= 512 ? 64 : n <= 4096 ? 128 : n <= 16384 ? 256 : 1024;
     const bool staged = smem_need <= (size_t)kSoftmaxMaxSmemBytes;
     const size_t smem = staged ? smem_need : 0;
     RFX_DISPATCH_DTYPE(a->dtype, T, {

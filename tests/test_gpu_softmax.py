@@ -45,6 +45,42 @@ def test_long_fp32_rows_many_per_cta(native, n):
     torch.testing.assert_close(y[0, 0].sum(-1), torch.ones(n, device=DEV), atol=1e-4, rtol=0)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("n", [512, 2048, 4096, 8192, 16384])
+def test_16bit_rows_held_raw_in_registers(native, dtype, n):
+    """16-bit rows stay in registers in their own type: a warp per row (up to 2048 elements), 128 threads
+    (up to 4096), a CTA of 256 (up to 16 384). Plain, log and causal, against the oracle."""
+    tol = TOL[dtype]
+    x = (torch.randn(600, n, device=DEV, generator=torch.Generator(device=DEV).manual_seed(n)) * 3).to(dtype)
+    torch.testing.assert_close(online_softmax(x).cpu().float(), oracle.online_softmax(x.cpu()).float(), atol=tol, rtol=tol)
+    torch.testing.assert_close(online_softmax(x, log=True).cpu().float(), oracle.online_softmax(x.cpu(), log=True).float(),
+                               atol=tol * 10, rtol=tol)
+    if n <= 2048:
+        sq = (torch.randn(2, n, n, device=DEV, generator=torch.Generator(device=DEV).manual_seed(n + 1)) * 3).to(dtype)
+        y = online_softmax(sq, is_causal=True)
+        torch.testing.assert_close(y.cpu().float(), oracle.online_softmax(sq.cpu(), is_causal=True).float(), atol=tol, rtol=tol)
+        assert not torch.triu(y[0], diagonal=1).any()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_long_16bit_rows_staged_in_shared_memory(native, dtype):
+    """Vocabulary-sized 16-bit rows, staged in shared memory in their own type, the exponentials kept in
+    place of the inputs; odd length, so every row starts at another alignment. Plain and log against the
+    oracle; causal rows (a 16 392-square) against the oracle on the visible part of sampled rows."""
+    tol = TOL[dtype]
+    x = (torch.randn(400, 50257, device=DEV, generator=torch.Generator(device=DEV).manual_seed(7)) * 3).to(dtype)
+    torch.testing.assert_close(online_softmax(x).cpu().float(), oracle.online_softmax(x.cpu()).float(), atol=tol, rtol=tol)
+    torch.testing.assert_close(online_softmax(x, log=True).cpu().float(), oracle.online_softmax(x.cpu(), log=True).float(),
+                               atol=tol * 10, rtol=tol)
+    n = 16392
+    sq = (torch.randn(1, n, n, device=DEV, generator=torch.Generator(device=DEV).manual_seed(8)) * 3).to(dtype)
+    y = online_softmax(sq, is_causal=True)
+    assert not torch.triu(y[0], diagonal=1).any()
+    for r in (0, 1, 7, 8, 4097, n // 2, n - 2, n - 1):
+        ref = oracle.online_softmax(sq[0, r:r + 1, :r + 1].cpu())
+        torch.testing.assert_close(y[0, r:r + 1, :r + 1].cpu().float(), ref.float(), atol=tol, rtol=tol)
+
+
 @pytest.mark.parametrize("n", [1, 33, 4096, 50257, 60000])
 def test_rows_sum_to_one(native, n):  # reference tests/test_softmax.py:17-33; 60000 takes the unstaged path
     x = torch.randn(6, n, device=DEV, generator=torch.Generator(device=DEV).manual_seed(n))
