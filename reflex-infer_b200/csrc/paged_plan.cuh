@@ -94,9 +94,16 @@ inline PlanPtrs plan_ptrs(void* ws, const PlanLayout& L) {
     return r;
 }
 
+// What finishing a (request, kv head) pair costs a CTA of the decode kernel, in 64-key tiles of
+// streaming time (see plan_kernel).
+#ifndef RFX_DECODE_ITEM_COST
+#define RFX_DECODE_ITEM_COST 4
+#endif
+constexpr int kDecodeItemCost = RFX_DECODE_ITEM_COST;
+
 // Host launchers implemented in their own files. `parts_hint` is the number of runs the
 // partial kernel wants (its CTA count).
-int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int parts_hint);
+int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int parts_hint, int item_cost = 0);
 int launch_paged_generic(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P);
 // `gather` != nullptr: rows go to every rank's full output (see RfxHeadGatherArgs).
 int launch_paged_combine(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P,

@@ -36,7 +36,7 @@ __device__ inline void block_exscan2(long long& a, long long& b, long long (*red
 
 __global__ void __launch_bounds__(kPlanThreads)
 plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_start, int B, int Hkv,
-            int G, long long max_parts, long long target_chunk, int parts_hint, long long max_items,
+            int G, long long max_parts, long long target_chunk, int parts_hint, long long item_cost, long long max_items,
             long long cap_rows, long long max_q_len, long long n_q, int32_t* hdr,
             int32_t* pair_item_begin, int32_t* pair_counter, int32_t* part_first, int4* items, int32_t* item_prow) {
     __shared__ long long red[kPlanThreads / 32][2];
@@ -54,11 +54,24 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
     auto ctx_of = [&](int b) { return single ? ctx_reg : max(0, ctx_lens[b]); };
     auto nq_of = [&](int b) -> long long { return single ? nq_reg : (q_start ? max(0, q_start[b + 1] - q_start[b]) : 1); };
 
-    // tiles before each request (per kv head), and in total
-    long long tile_pre = 0, unused = 0, tiles_all, t2;
-    for (int b = b0; b < b1; ++b) tile_pre += (ctx_of(b) + kPlanTile - 1) / kPlanTile;
-    block_exscan2(tile_pre, unused, red, tiles_all, t2);
-    const long long T = tiles_all * Hkv;
+    // tiles and non-empty requests before each request (per kv head), and in total
+    long long tile_pre = 0, ne_pre = 0, tiles_all, ne_all;
+    for (int b = b0; b < b1; ++b) {
+        tile_pre += (ctx_of(b) + kPlanTile - 1) / kPlanTile;
+        ne_pre += ctx_of(b) > 0 ? 1 : 0;
+    }
+    block_exscan2(tile_pre, ne_pre, red, tiles_all, ne_all);
+    const long long T_tiles = tiles_all * Hkv;
+    // The stream that is cut into equal runs holds, between two consecutive pairs, `item_cost` units that
+    // stand for no tile: finishing a pair (merging the warps' partials, writing rows or a partial and
+    // counting it) costs a CTA about as much as streaming that many tiles, and a run that holds several
+    // pairs would otherwise end later than the others. Only when runs are long against that cost.
+    long long c = item_cost;
+    {
+        long long parts0 = parts_hint < 1 ? 1 : parts_hint;
+        if (target_chunk > 0 || T_tiles < 4 * c * parts0) c = 0;
+    }
+    const long long T = T_tiles > 0 ? T_tiles + c * (ne_all * Hkv - 1) : 0;
 
     // tiles per run
     long long parts = parts_hint;
@@ -72,17 +85,19 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
     // items and partial rows before each request
     long long item_pre = 0, row_pre = 0, n_items, n_rows;
     {
-        long long pre = tile_pre;
+        long long pre = tile_pre, ne = ne_pre;
         for (int b = b0; b < b1; ++b) {
             const long long tb = (ctx_of(b) + kPlanTile - 1) / kPlanTile;
             const long long nq = nq_of(b);
-            if (tb > 0)
+            if (tb > 0) {
                 for (int h = 0; h < Hkv; ++h) {
-                    const long long off = pre * Hkv + h * tb;
+                    const long long off = pre * Hkv + h * tb + c * (ne * Hkv + h);
                     const long long ni = (off + tb - 1) / q - off / q + 1;
                     item_pre += ni;
                     row_pre += ni * nq * G;
                 }
+                ++ne;
+            }
             pre += tb;
         }
     }
@@ -113,25 +128,28 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
         return;
     }
 
-    long long pre = tile_pre, it = item_pre, rw = row_pre;
+    long long pre = tile_pre, ne = ne_pre, it = item_pre, rw = row_pre;
     for (int b = b0; b < b1; ++b) {
-        const int c = ctx_of(b);
-        const long long tb = (c + kPlanTile - 1) / kPlanTile;
+        const int ctx = ctx_of(b);
+        const long long tb = (ctx + kPlanTile - 1) / kPlanTile;
         const long long nq = nq_of(b);
         for (int h = 0; h < Hkv; ++h) {
             pair_item_begin[(long long)b * Hkv + h] = (int)it;
             if (tb == 0) continue;
-            const long long off = pre * Hkv + h * tb;
+            const long long off = pre * Hkv + h * tb + c * (ne * Hkv + h);
             const long long p0 = off / q, p1 = (off + tb - 1) / q;
             for (long long p = p0; p <= p1; ++p) {
                 const long long s = max(off, p * q), e = min(off + tb, (p + 1) * q);
-                items[it] = make_int4(b, h, (int)((s - off) * kPlanTile), min(c, (int)((e - off) * kPlanTile)));
+                items[it] = make_int4(b, h, (int)((s - off) * kPlanTile), min(ctx, (int)((e - off) * kPlanTile)));
                 item_prow[it] = (int)rw;
-                if (s == p * q) part_first[p] = (int)it;
+                // the first item of run p: it starts the run, or it starts its pair and the pair before it
+                // (whose last tile sits at off - c - 1) ended in an earlier run
+                if (s == p * q || (s == off && off - c <= p * q)) part_first[p] = (int)it;
                 ++it;
                 rw += nq * G;
             }
         }
+        if (tb > 0) ++ne;
         pre += tb;
     }
     if (tid == 0) {
@@ -149,11 +167,11 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
     ptx::pdl_wait();
 }
 
-int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int parts_hint) {
+int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int parts_hint, int item_cost) {
     const int G = (int)(a->num_q_heads / a->num_kv_heads);
     cudaError_t e = launch_pdl(plan_kernel, dim3(1), dim3(kPlanThreads), 0, as_stream(a->stream), a->context_lens,
                                a->q_start, (int)a->batch, (int)a->num_kv_heads, G, (long long)L.max_parts,
-                               (long long)a->target_chunk, parts_hint, (long long)L.max_items, (long long)L.cap_rows,
+                               (long long)a->target_chunk, parts_hint, (long long)item_cost, (long long)L.max_items, (long long)L.cap_rows,
                                (long long)(a->max_q_len < 1 ? 1 : a->max_q_len), (long long)a->n_q, P.hdr,
                                P.pair_item_begin, P.pair_counter, P.part_first, P.items, P.item_prow);
     if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "rfx_paged_attention_plan: %s", cudaGetErrorString(e));
