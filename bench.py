@@ -90,6 +90,8 @@ def parse_args():
     ap.add_argument("--shard", default=None, choices=["replica", "request", "head"],
                     help="default: request (strong scaling); a multi-GPU run without this flag also measures "
                          "the other modes and reports them under other_shards")
+    ap.add_argument("--small-filter", default=None,
+                    help="with --only small_ops: time only the ops whose label contains this text (small cases for ncu)")
     ap.add_argument("--only", default=None, choices=["cfg3", "cfg5", "linear_norm", "small_ops", "int8_kv", "clocks"],
                     help="run just that secondary block on one GPU and print it (small profiling cases: "
                          "--only cfg3 --requests 2)")
@@ -858,29 +860,35 @@ def measure_small_ops(args, device):
     def copies(nbytes_per_call):  # enough inputs that a graph replay touches at least four times L2
         return max(2, min(16, -(-4 * 126_000_000 // max(nbytes_per_call, 1))))
 
+    def want(label):
+        return not getattr(args, "small_filter", None) or args.small_filter in label
+
     g = torch.Generator(device=device).manual_seed(11)
     N, H, D, bs = 131072, 8, 128, 16
-    k = torch.randn(N, H, D, device=device, generator=g).to(bf)
-    v = torch.randn(N, H, D, device=device, generator=g).to(bf)
-    kc = torch.zeros(N // bs + 8, H, bs, D, dtype=bf, device=device)
-    vc = torch.zeros_like(kc)
-    slots = torch.randperm(kc.shape[0] * bs, device=device, generator=g)[:N]
-    nb = 2 * 2 * N * H * D * 2 + 8 * N
-    put("kv_paged_append 131072 tokens x 8 heads bf16", timed([lambda: kv_paged_append(k, v, kc, vc, slots)] * 2), nb, 2)
-    del k, v, kc, vc
+    if want("kv_paged_append 131072 tokens x 8 heads bf16"):
+        k = torch.randn(N, H, D, device=device, generator=g).to(bf)
+        v = torch.randn(N, H, D, device=device, generator=g).to(bf)
+        kc = torch.zeros(N // bs + 8, H, bs, D, dtype=bf, device=device)
+        vc = torch.zeros_like(kc)
+        slots = torch.randperm(kc.shape[0] * bs, device=device, generator=g)[:N]
+        nb = 2 * 2 * N * H * D * 2 + 8 * N
+        put("kv_paged_append 131072 tokens x 8 heads bf16", timed([lambda: kv_paged_append(k, v, kc, vc, slots)] * 2), nb, 2)
+        del k, v, kc, vc
     B, ctx, H = 8, 8192, 32
-    kc = torch.randn(B * ctx // bs, H, bs, D, device=device, generator=g).to(bf)
-    vc = torch.randn(B * ctx // bs, H, bs, D, device=device, generator=g).to(bf)
-    bt = torch.randperm(kc.shape[0], device=device, generator=g).view(B, -1)
-    lens = torch.full((B,), ctx, dtype=torch.int32, device=device)
-    nb = 2 * 2 * B * H * ctx * D * 2
-    put("kv_paged_lookup 8 x 8192 x 32 heads bf16", timed([lambda: kv_paged_lookup(kc, vc, bt, lens, ctx)] * 2), nb, 2)
-    del kc, vc
-    cos, sin = build_rope_tables(2048, D, base=1e6, device=device, dtype=bf)
-    nb = 2 * 8 * 2048 * 32 * D * 2
-    xs = [torch.randn(8, 2048, 32, D, device=device, generator=g).to(bf) for _ in range(copies(nb))]
-    put("apply_rope_ 8 x 2048 x 32 x 128 bf16", timed([(lambda t=t: apply_rope_(t, cos, sin)) for t in xs]), nb, len(xs))
-    del xs
+    if want("kv_paged_lookup 8 x 8192 x 32 heads bf16"):
+        kc = torch.randn(B * ctx // bs, H, bs, D, device=device, generator=g).to(bf)
+        vc = torch.randn(B * ctx // bs, H, bs, D, device=device, generator=g).to(bf)
+        bt = torch.randperm(kc.shape[0], device=device, generator=g).view(B, -1)
+        lens = torch.full((B,), ctx, dtype=torch.int32, device=device)
+        nb = 2 * 2 * B * H * ctx * D * 2
+        put("kv_paged_lookup 8 x 8192 x 32 heads bf16", timed([lambda: kv_paged_lookup(kc, vc, bt, lens, ctx)] * 2), nb, 2)
+        del kc, vc
+    if want("apply_rope_ 8 x 2048 x 32 x 128 bf16"):
+        cos, sin = build_rope_tables(2048, D, base=1e6, device=device, dtype=bf)
+        nb = 2 * 8 * 2048 * 32 * D * 2
+        xs = [torch.randn(8, 2048, 32, D, device=device, generator=g).to(bf) for _ in range(copies(nb))]
+        put("apply_rope_ 8 x 2048 x 32 x 128 bf16", timed([(lambda t=t: apply_rope_(t, cos, sin)) for t in xs]), nb, len(xs))
+        del xs
     # online_softmax: the reference's four (bench_softmax.py:20-25), then bf16 / fp32 shapes of the path
     # (the reference writes its two causal cases as [B, 32*S, S], which its own square check refuses,
     # triton_softmax.py:146-151; here the same rows as [B*32, S, S])
@@ -894,9 +902,11 @@ def measure_small_ops(args, device):
             numel *= d_
         nb = 2 * numel * torch.empty((), dtype=dt).element_size()
         n_in = copies(nb) if nb < 1_000_000_000 else 1
-        xs = [torch.randn(*shape, device=device, generator=g, dtype=torch.float32).to(dt) for _ in range(n_in)]
         label = f"online_softmax {tag + ' ' if tag else ''}{' x '.join(map(str, shape))} {str(dt)[6:]}" + \
                 (" causal" if causal else "") + (" log" if log else "")
+        if not want(label):
+            continue
+        xs = [torch.randn(*shape, device=device, generator=g, dtype=torch.float32).to(dt) for _ in range(n_in)]
         calls = [(lambda t=t: online_softmax(t, is_causal=causal, log=log)) for t in xs]
         if n_in == 1:
             calls = calls * 2

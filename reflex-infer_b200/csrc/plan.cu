@@ -8,9 +8,10 @@
 
 namespace rfx {
 
-constexpr int kPlanThreads = 1024;
+constexpr int kPlanMaxThreads = 1024;  // one request per thread up to here; small batches take a warp or four
 
-// Exclusive scan of two values per thread across the CTA.
+// Exclusive scan of two values per thread across the CTA of THREADS threads.
+template <int THREADS>
 __device__ inline void block_exscan2(long long& a, long long& b, long long (*red)[2], long long& tot_a,
                                      long long& tot_b) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -26,7 +27,8 @@ __device__ inline void block_exscan2(long long& a, long long& b, long long (*red
     __syncthreads();
     long long ba = 0, bb = 0;
     tot_a = 0; tot_b = 0;
-    for (int i = 0; i < kPlanThreads / 32; ++i) {
+#pragma unroll
+    for (int i = 0; i < THREADS / 32; ++i) {
         if (i < warp) { ba += red[i][0]; bb += red[i][1]; }
         tot_a += red[i][0]; tot_b += red[i][1];
     }
@@ -34,6 +36,7 @@ __device__ inline void block_exscan2(long long& a, long long& b, long long (*red
     b = bb + ib - b;
 }
 
+template <int kPlanThreads>
 __global__ void __launch_bounds__(kPlanThreads)
 plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_start, int B, int Hkv,
             int G, long long max_parts, long long target_chunk, int parts_hint, long long item_cost, long long max_items,
@@ -60,7 +63,7 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
         tile_pre += (ctx_of(b) + kPlanTile - 1) / kPlanTile;
         ne_pre += ctx_of(b) > 0 ? 1 : 0;
     }
-    block_exscan2(tile_pre, ne_pre, red, tiles_all, ne_all);
+    block_exscan2<kPlanThreads>(tile_pre, ne_pre, red, tiles_all, ne_all);
     const long long T_tiles = tiles_all * Hkv;
     // The stream that is cut into equal runs holds, between two consecutive pairs, `item_cost` units that
     // stand for no tile: finishing a pair (merging the warps' partials, writing rows or a partial and
@@ -101,7 +104,7 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
             pre += tb;
         }
     }
-    block_exscan2(item_pre, row_pre, red, n_items, n_rows);
+    block_exscan2<kPlanThreads>(item_pre, row_pre, red, n_items, n_rows);
 
     // The workspace was sized on the host from max_q_len and n_q; the row counts used here come
     // from q_start on the device. If they do not agree (a request with more rows than max_q_len,
@@ -169,11 +172,18 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
 
 int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int parts_hint, int item_cost) {
     const int G = (int)(a->num_q_heads / a->num_kv_heads);
-    cudaError_t e = launch_pdl(plan_kernel, dim3(1), dim3(kPlanThreads), 0, as_stream(a->stream), a->context_lens,
-                               a->q_start, (int)a->batch, (int)a->num_kv_heads, G, (long long)L.max_parts,
-                               (long long)a->target_chunk, parts_hint, (long long)item_cost, (long long)L.max_items, (long long)L.cap_rows,
-                               (long long)(a->max_q_len < 1 ? 1 : a->max_q_len), (long long)a->n_q, P.hdr,
-                               P.pair_item_begin, P.pair_counter, P.part_first, P.items, P.item_prow);
+    // a small batch gets a small CTA: the scans and barriers of 32 warps cost a one-CTA kernel microseconds
+    cudaError_t e;
+#define RFX_PLAN_LAUNCH(THREADS)                                                                                     \
+    e = launch_pdl(plan_kernel<THREADS>, dim3(1), dim3(THREADS), 0, as_stream(a->stream), a->context_lens, a->q_start, \
+                   (int)a->batch, (int)a->num_kv_heads, G, (long long)L.max_parts, (long long)a->target_chunk,        \
+                   parts_hint, (long long)item_cost, (long long)L.max_items, (long long)L.cap_rows,                   \
+                   (long long)(a->max_q_len < 1 ? 1 : a->max_q_len), (long long)a->n_q, P.hdr, P.pair_item_begin,     \
+                   P.pair_counter, P.part_first, P.items, P.item_prow)
+    if (a->batch <= 32) RFX_PLAN_LAUNCH(32);
+    else if (a->batch <= 128) RFX_PLAN_LAUNCH(128);
+    else RFX_PLAN_LAUNCH(kPlanMaxThreads);
+#undef RFX_PLAN_LAUNCH
     if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "rfx_paged_attention_plan: %s", cudaGetErrorString(e));
     return check_launch("rfx_paged_attention_plan");
 }
