@@ -193,7 +193,11 @@ int rfx_rope_append(const RfxRopeAppendArgs* a);
 
 /* online_softmax: kernels/softmax/__init__.py:15-35; torch_reference_softmax,
  * triton_softmax.py:178-202. Rows of a [rows, n] contiguous matrix; causal masks
- * col > row % n (square contract, triton_softmax.py:66-69,146-164). */
+ * col > row % n (square contract, triton_softmax.py:66-69,146-164). Statistics in fp32. For
+ * bf16 / fp16 rows the exponentials are rounded to the row's type once before they are scaled by
+ * 1/sum (the sum is taken from the unrounded values), so a result can differ from the correctly
+ * rounded one by one unit of the 16-bit type -- inside the reference's tolerances (bf16 2e-2,
+ * fp16 1e-3, kernels/_common/dtype.py:47-52). x == y (in place) is allowed. */
 typedef struct {
     const void* x;
     void* y;

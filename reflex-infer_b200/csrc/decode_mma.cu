@@ -304,13 +304,17 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             ptx::prefetch_tensormap(&kmap);
             ptx::prefetch_tensormap(&vmap);
         }
+        // The CTA's first run: its bounds are asked for together with the number of runs (the array has an
+        // entry for every run the launch could have), one round trip instead of two before the first copy.
+        int first_begin = P.part_first[blockIdx.x], first_end = P.part_first[blockIdx.x + 1];
         const int n_parts = P.hdr[HdrNumParts];
         int stage = 0;
         uint32_t phase = 0;
         int turn = 0;  // whose stage comes next
         bool alive = true;
         for (int part = blockIdx.x; part < n_parts && alive; part += gridDim.x) {
-            const int i_begin = P.part_first[part], i_end = P.part_first[part + 1];
+            const int i_begin = part == (int)blockIdx.x ? first_begin : P.part_first[part];
+            const int i_end = part == (int)blockIdx.x ? first_end : P.part_first[part + 1];
             for (int ib = i_begin; ib < i_end && alive; ib += 32) {
                 // one round trip: lane j holds the descriptor of item ib + j
                 const int my_id = ib + lane;

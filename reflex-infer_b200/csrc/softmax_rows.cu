@@ -1,21 +1,21 @@
 // Row softmax / log-softmax (the public online_softmax op). Bandwidth-bound: 2*numel*e
 // bytes (benchmark/bench_softmax.py:34), every element read once and written once.
 //   * rows whose 16-byte vectors divide evenly (and up to 16 K elements): the row lives in
-//     registers as fp32, 1/2/4/8 vectors per thread (templated, so short rows keep their
-//     occupancy); a warp per row with shuffles only (eight rows per CTA) or a CTA of 256 threads
-//     per row with two block reductions; vector stores;
-//   * other rows up to 200 KB: one CTA per row, the row staged in shared memory in its own type
-//     (a 16-bit row of 50 257 elements is 100 KB: two CTAs per SM); loads and stores are 16-byte
-//     vectors over the aligned body of the row with scalar head and tail, so odd lengths and
-//     unaligned rows still move full sectors;
-//   * longer rows: three passes over global memory.
+//     registers -- fp32 rows as they are, 16-bit rows in their own type, widened in each pass --
+//     1/2/4/8 vectors per thread (templated, so short rows keep their occupancy); a warp per row
+//     with shuffles only (eight rows per CTA) or a CTA of 128 or 256 threads per row with two block
+//     reductions; vector stores;
+//   * other rows below 64 KB: one CTA per row, the row staged in shared memory in its own type; loads
+//     and stores are 16-byte vectors over the aligned body of the row with scalar head and tail, so
+//     odd lengths and unaligned rows still move full sectors;
+//   * longer rows (the vocabulary-sized ones): two passes over global memory with a running
+//     (maximum, sum) per thread, the second pass served by L2.
 #include <type_traits>
 
 #include "common.cuh"
 
 namespace rfx {
 
-constexpr int kSoftmaxMaxSmemBytes = 200 * 1024;  // staged rows: up to 51 200 fp32 or 102 400 16-bit elements
 constexpr int kVecThreads = 256;
 constexpr int kVecItems = 8;                  // vectors per thread in the register kernel
 
@@ -308,25 +308,8 @@ softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows
     softmax_rows_reg_body<T, TPR, ITEMS>(x, y, rows, n, causal, is_log);
 }
 
-// Visits elements [0, count) of a row: scalar head up to the first 16-byte boundary, vector
-// body, scalar tail. `fn(index, value)` for loads.
-template <typename T, typename F>
-__device__ inline void for_each_load(const T* row, int count, F fn) {
-    constexpr int V = 16 / sizeof(T);
-    const int mis = (int)(((uintptr_t)row % 16) / sizeof(T));
-    const int head = min(count, mis ? V - mis : 0);
-    for (int i = threadIdx.x; i < head; i += blockDim.x) fn(i, Num<T>::to_f(row[i]));
-    const int nbody = (count - head) / V;
-    const Vec16<T>* body = reinterpret_cast<const Vec16<T>*>(row + head);
-    for (int vi = threadIdx.x; vi < nbody; vi += blockDim.x) {
-        const Vec16<T> p = body[vi];
-#pragma unroll
-        for (int j = 0; j < V; ++j) fn(head + vi * V + j, Num<T>::to_f(p.v[j]));
-    }
-    for (int i = head + nbody * V + threadIdx.x; i < count; i += blockDim.x) fn(i, Num<T>::to_f(row[i]));
-}
-
-// Writes elements [0, count) of a row from `val(index)` with the same head/body/tail split.
+// Writes elements [0, count) of a row from `val(index)`: scalar head up to the first 16-byte boundary,
+// vector body, scalar tail.
 template <typename T, typename F>
 __device__ inline void for_each_store(T* row, int count, F val) {
     constexpr int V = 16 / sizeof(T);
@@ -344,10 +327,9 @@ __device__ inline void for_each_store(T* row, int count, F val) {
     for (int i = head + nbody * V + threadIdx.x; i < count; i += blockDim.x) row[i] = Num<T>::from_f(val(i));
 }
 
-// STAGED: the row is kept in shared memory in its own type (a 16-bit row of 50 257 elements is
-// 100 KB, so two CTAs share an SM), read from global memory once and written once; the
-// exponentials are evaluated twice (sum, output) rather than kept as fp32.
-template <typename T, bool STAGED>
+// Rows below 64 KB that the register kernels do not take (odd lengths, unaligned rows): the row is kept
+// in shared memory in its own type, read from global memory once and written once.
+template <typename T>
 __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n,
                                     int causal, int is_log) {
     extern __shared__ __align__(16) unsigned char srow_raw[];
@@ -359,7 +341,7 @@ __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, 
         T* yr = y + row * (int64_t)n;
         const int valid = causal ? (int)(row % n) + 1 : n;  // columns [0, valid) take part
         float m = -INFINITY;
-        if (STAGED) {
+        {
             // raw copy with 16-byte vectors over the aligned body of the row
             constexpr int V = 16 / sizeof(T);
             const int mis = (int)(((uintptr_t)xr % 16) / sizeof(T));
@@ -470,22 +452,126 @@ __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, 
             } else {
                 for_each_store<T>(yr, n, [&](int i) -> float { return out_of(i, i < valid ? Num<T>::to_f(sr[i]) : 0.f); });
             }
-        } else {
-            for_each_load<T>(xr, valid, [&](int, float v) { m = fmaxf(m, v); });
-            m = block_reduce(m, true, red);
-            float l = 0.f;
-            for_each_load<T>(xr, valid, [&](int, float v) { l += expf(v - m); });
-            l = block_reduce(l, false, red);
-            const float logl = logf(l);
-            for (int i = threadIdx.x; i < n; i += blockDim.x) {
-                float o;
-                if (i >= valid) o = is_log ? -INFINITY : 0.f;
-                else if (is_log) o = (Num<T>::to_f(xr[i]) - m) - logl;
-                else o = expf(Num<T>::to_f(xr[i]) - m) / l;
-                yr[i] = Num<T>::from_f(o);
-            }
         }
         __syncthreads();  // srow is reused by the next row
+    }
+}
+
+// Long rows (64 KB and more: the vocabulary-sized ones): two passes over global memory, nothing staged.
+// Pass one streams the row and keeps a running (maximum, sum of exponentials) per thread, rescaling
+// the sum when a vector brings a larger maximum; the threads' pairs are merged once. Pass two reads
+// the row again -- it is still in L2, a CTA re-reads what it has just read -- and writes the result,
+// so DRAM sees the row once in and once out. A staged row of 100 KB lets only two rows share an SM,
+// and their loads, reductions and stores take turns (0.47-0.62 of the copy rate); without staging a
+// CTA is 256 threads and a few registers, and many rows are on their way at once.
+template <typename T>
+__global__ void __launch_bounds__(256)
+softmax_rows_twopass_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n, int causal, int is_log) {
+    __shared__ float red[32];
+    constexpr float kLog2e = 1.4426950408889634f;
+    constexpr int V = 16 / sizeof(T);
+    struct alignas(16) Vec { T v[V]; };
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* xr = x + row * (int64_t)n;
+        T* yr = y + row * (int64_t)n;
+        const int valid = causal ? (int)(row % n) + 1 : n;  // columns [0, valid) take part
+        const int mis = (int)(((uintptr_t)xr % 16) / sizeof(T));
+        const int head = min(valid, mis ? V - mis : 0);
+        const int nbody = (valid - head) / V;
+        const int tail0 = head + nbody * V;
+        const Vec* gb = reinterpret_cast<const Vec*>(xr + head);
+        // ---- pass one: running maximum (natural units) and sum of 2^((x - m) log2 e)
+        float m = -INFINITY, l = 0.f;
+        auto take = [&](float vmax, auto&& add) {
+            if (vmax > m) {
+                l *= ex2_fast((m - vmax) * kLog2e);  // 0 * 0 at the start
+                m = vmax;
+            }
+            if (m > -INFINITY) add(m * kLog2e);
+        };
+        for (int i = threadIdx.x; i < head; i += blockDim.x) {
+            const float v = Num<T>::to_f(xr[i]);
+            take(v, [&](float mb) { l += ex2_fast(fmaf(v, kLog2e, -mb)); });
+        }
+#pragma unroll 4
+        for (int vi = threadIdx.x; vi < nbody; vi += blockDim.x) {
+            const Vec p = gb[vi];
+            if constexpr (sizeof(T) == 2) {
+                const uint32_t* w = reinterpret_cast<const uint32_t*>(&p);
+                uint32_t m2 = max2_16<T>(max2_16<T>(w[0], w[1]), max2_16<T>(w[2], w[3]));
+                const float2 mm = widen2<T>(m2);
+                take(fmaxf(mm.x, mm.y), [&](float mb) {
+                    const float2 k2 = make_float2(kLog2e, kLog2e), nmb2 = make_float2(-mb, -mb);
+                    float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+                    for (int k = 0; k < V / 2; ++k) {
+                        const float2 t = __ffma2_rn(widen2<T>(w[k]), k2, nmb2);
+                        acc = __fadd2_rn(acc, make_float2(ex2_fast(t.x), ex2_fast(t.y)));
+                    }
+                    l += acc.x + acc.y;
+                });
+            } else {
+                float f[V];
+                float vm = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < V; ++j) { f[j] = Num<T>::to_f(p.v[j]); vm = fmaxf(vm, f[j]); }
+                take(vm, [&](float mb) {
+#pragma unroll
+                    for (int j = 0; j < V; ++j) l += ex2_fast(fmaf(f[j], kLog2e, -mb));
+                });
+            }
+        }
+        for (int i = tail0 + threadIdx.x; i < valid; i += blockDim.x) {
+            const float v = Num<T>::to_f(xr[i]);
+            take(v, [&](float mb) { l += ex2_fast(fmaf(v, kLog2e, -mb)); });
+        }
+        const float M = block_reduce(m, true, red);
+        l = (m > -INFINITY) ? l * ex2_fast((m - M) * kLog2e) : 0.f;
+        l = block_reduce(l, false, red);
+        const float mb = M * kLog2e, logl = logf(l), inv = 1.0f / l;
+        auto out_of = [&](int i, float v) -> float {
+            if (i >= valid) return is_log ? -INFINITY : 0.f;
+            return is_log ? (v - M) - logl : ex2_fast(fmaf(v, kLog2e, -mb)) * inv;
+        };
+        // ---- pass two
+        if ((int)(((uintptr_t)yr % 16) / sizeof(T)) == mis) {
+            const int head_y = min(n, mis ? V - mis : 0);
+            const int nbody_y = (n - head_y) / V;
+            for (int i = threadIdx.x; i < head_y; i += blockDim.x) yr[i] = Num<T>::from_f(out_of(i, i < valid ? Num<T>::to_f(xr[i]) : 0.f));
+            Vec* yb = reinterpret_cast<Vec*>(yr + head_y);
+            const Vec* xb = reinterpret_cast<const Vec*>(xr + head_y);
+            const float2 k2 = make_float2(kLog2e, kLog2e), nmb2 = make_float2(-mb, -mb), inv2 = make_float2(inv, inv);
+#pragma unroll 4
+            for (int vi = threadIdx.x; vi < nbody_y; vi += blockDim.x) {
+                const int c0 = head_y + vi * V;
+                Vec o;
+                if (c0 + V <= valid) {
+                    const Vec p = xb[vi];
+                    if (sizeof(T) == 2 && !is_log) {
+                        const uint32_t* w = reinterpret_cast<const uint32_t*>(&p);
+                        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+                        if constexpr (sizeof(T) == 2) {
+#pragma unroll
+                            for (int k = 0; k < V / 2; ++k) {
+                                const float2 t = __ffma2_rn(widen2<T>(w[k]), k2, nmb2);
+                                ow[k] = pack2_16<T>(__fmul2_rn(make_float2(ex2_fast(t.x), ex2_fast(t.y)), inv2));
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < V; ++j) o.v[j] = Num<T>::from_f(out_of(c0 + j, Num<T>::to_f(p.v[j])));
+                    }
+                } else {  // the vector the causal boundary cuts, and those past it (their input is not read)
+#pragma unroll
+                    for (int j = 0; j < V; ++j) o.v[j] = Num<T>::from_f(out_of(c0 + j, c0 + j < valid ? Num<T>::to_f(xr[c0 + j]) : 0.f));
+                }
+                yb[vi] = o;
+            }
+            for (int i = head_y + nbody_y * V + threadIdx.x; i < n; i += blockDim.x)
+                yr[i] = Num<T>::from_f(out_of(i, i < valid ? Num<T>::to_f(xr[i]) : 0.f));
+        } else {
+            for_each_store<T>(yr, n, [&](int i) -> float { return out_of(i, i < valid ? Num<T>::to_f(xr[i]) : 0.f); });
+        }
     }
 }
 
@@ -571,21 +657,23 @@ extern "C" int rfx_online_softmax(const RfxSoftmaxArgs* a) {
         return check_launch(name);
     }
     const size_t smem_need = (size_t)n * e + 32;  // the row in its own type + room for its misalignment
+    if ((size_t)n * e >= 64 * 1024) {
+        // in place is fine: pass one has read the whole row before pass two writes any of it, and in pass two
+        // a vector is read by the thread that then overwrites it
+        const int64_t g = a->rows < cap ? a->rows : cap;
+        RFX_DISPATCH_DTYPE(a->dtype, T, {
+            softmax_rows_twopass_kernel<T><<<(int)g, 256, 0, s>>>((const T*)a->x, (T*)a->y, a->rows, n, a->is_causal, a->log);
+        });
+        return check_launch(name);
+    }
     const int threads = n <= 512 ? 64 : n <= 4096 ? 128 : n <= 16384 ? 256 : 1024;
-    const bool staged = smem_need <= (size_t)kSoftmaxMaxSmemBytes;
-    const size_t smem = staged ? smem_need : 0;
     RFX_DISPATCH_DTYPE(a->dtype, T, {
-        if (staged) {
-            auto kern = softmax_rows_kernel<T, true>;
-            if (smem > 48 * 1024) {
-                cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                if (ce != cudaSuccess) return fail(RFX_CUDA_ERROR, "%s: smem opt-in: %s", name, cudaGetErrorString(ce));
-            }
-            kern<<<(int)grid, threads, smem, s>>>((const T*)a->x, (T*)a->y, a->rows, n, a->is_causal, a->log);
-        } else {
-            softmax_rows_kernel<T, false><<<(int)grid, threads, 0, s>>>((const T*)a->x, (T*)a->y, a->rows, n,
-                                                                      a->is_causal, a->log);
+        auto kern = softmax_rows_kernel<T>;
+        if (smem_need > 48 * 1024) {
+            cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_need);
+            if (ce != cudaSuccess) return fail(RFX_CUDA_ERROR, "%s: smem opt-in: %s", name, cudaGetErrorString(ce));
         }
+        kern<<<(int)grid, threads, smem_need, s>>>((const T*)a->x, (T*)a->y, a->rows, n, a->is_causal, a->log);
     });
     return check_launch(name);
 }
