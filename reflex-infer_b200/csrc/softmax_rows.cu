@@ -457,17 +457,48 @@ __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, 
     }
 }
 
-// Long rows (64 KB and more: the vocabulary-sized ones): two passes over global memory, nothing staged.
+// Long rows (64 KB and more: the vocabulary-sized ones): two passes over global memory, no row staged.
 // Pass one streams the row and keeps a running (maximum, sum of exponentials) per thread, rescaling
 // the sum when a vector brings a larger maximum; the threads' pairs are merged once. Pass two reads
 // the row again -- it is still in L2, a CTA re-reads what it has just read -- and writes the result,
 // so DRAM sees the row once in and once out. A staged row of 100 KB lets only two rows share an SM,
-// and their loads, reductions and stores take turns (0.47-0.62 of the copy rate); without staging a
-// CTA is 256 threads and a few registers, and many rows are on their way at once.
+// and their loads, reductions and stores take turns. Here a thread walks its vectors through a ring of
+// eight 16-byte slots of its own in shared memory, filled by cp.async: eight vectors per thread are on
+// their way at all times (a slot is refilled as soon as its vector has been used) and no thread ever
+// reads another's slot, so there is no barrier in the loop.
+constexpr int kTwoPassThreads = 256;
+constexpr int kTwoPassDepth = 8;
+
+template <typename VecT, typename F>
+__device__ __forceinline__ void stream_vectors(const VecT* gb, int nvec, unsigned char* ring, F fn) {
+    constexpr int D = kTwoPassDepth;
+    constexpr uint32_t kSlot = kTwoPassThreads * 16;  // bytes between a thread's consecutive slots
+    VecT* mine = reinterpret_cast<VecT*>(ring) + threadIdx.x;
+    const uint32_t base = (uint32_t)__cvta_generic_to_shared(mine);
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+        const int vi = threadIdx.x + d * kTwoPassThreads;
+        if (vi < nvec) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(base + d * kSlot), "l"(gb + vi) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    int slot = 0;
+    for (int vi = threadIdx.x; vi < nvec; vi += kTwoPassThreads) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(D - 1) : "memory");  // this thread's oldest copy has landed
+        const VecT p = mine[slot * kTwoPassThreads];
+        fn(vi, p);  // p is in registers before the slot is refilled
+        const int nx = vi + D * kTwoPassThreads;
+        if (nx < nvec) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(base + slot * kSlot), "l"(gb + nx) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        slot = slot + 1 == D ? 0 : slot + 1;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kTwoPassThreads)
 softmax_rows_twopass_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n, int causal, int is_log) {
     __shared__ float red[32];
+    __shared__ __align__(16) unsigned char ring[kTwoPassThreads * kTwoPassDepth * 16];
     constexpr float kLog2e = 1.4426950408889634f;
     constexpr int V = 16 / sizeof(T);
     struct alignas(16) Vec { T v[V]; };
@@ -477,7 +508,7 @@ softmax_rows_twopass_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t 
         const int valid = causal ? (int)(row % n) + 1 : n;  // columns [0, valid) take part
         const int mis = (int)(((uintptr_t)xr % 16) / sizeof(T));
         const int head = min(valid, mis ? V - mis : 0);
-        const int nbody = (valid - head) / V;
+        const int nbody = (valid - head) / V;  // whole vectors of the aligned body, all inside `valid`
         const int tail0 = head + nbody * V;
         const Vec* gb = reinterpret_cast<const Vec*>(xr + head);
         // ---- pass one: running maximum (natural units) and sum of 2^((x - m) log2 e)
@@ -489,16 +520,15 @@ softmax_rows_twopass_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t 
             }
             if (m > -INFINITY) add(m * kLog2e);
         };
-        for (int i = threadIdx.x; i < head; i += blockDim.x) {
+        auto one = [&](int i) {
             const float v = Num<T>::to_f(xr[i]);
             take(v, [&](float mb) { l += ex2_fast(fmaf(v, kLog2e, -mb)); });
-        }
-#pragma unroll 4
-        for (int vi = threadIdx.x; vi < nbody; vi += blockDim.x) {
-            const Vec p = gb[vi];
+        };
+        for (int i = threadIdx.x; i < head; i += blockDim.x) one(i);
+        stream_vectors(gb, nbody, ring, [&](int, const Vec& p) {
             if constexpr (sizeof(T) == 2) {
                 const uint32_t* w = reinterpret_cast<const uint32_t*>(&p);
-                uint32_t m2 = max2_16<T>(max2_16<T>(w[0], w[1]), max2_16<T>(w[2], w[3]));
+                const uint32_t m2 = max2_16<T>(max2_16<T>(w[0], w[1]), max2_16<T>(w[2], w[3]));
                 const float2 mm = widen2<T>(m2);
                 take(fmaxf(mm.x, mm.y), [&](float mb) {
                     const float2 k2 = make_float2(kLog2e, kLog2e), nmb2 = make_float2(-mb, -mb);
@@ -520,11 +550,8 @@ softmax_rows_twopass_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t 
                     for (int j = 0; j < V; ++j) l += ex2_fast(fmaf(f[j], kLog2e, -mb));
                 });
             }
-        }
-        for (int i = tail0 + threadIdx.x; i < valid; i += blockDim.x) {
-            const float v = Num<T>::to_f(xr[i]);
-            take(v, [&](float mb) { l += ex2_fast(fmaf(v, kLog2e, -mb)); });
-        }
+        });
+        for (int i = tail0 + threadIdx.x; i < valid; i += blockDim.x) one(i);
         const float M = block_reduce(m, true, red);
         l = (m > -INFINITY) ? l * ex2_fast((m - M) * kLog2e) : 0.f;
         l = block_reduce(l, false, red);
@@ -535,36 +562,38 @@ softmax_rows_twopass_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t 
         };
         // ---- pass two
         if ((int)(((uintptr_t)yr % 16) / sizeof(T)) == mis) {
+            // the output row is aligned like the input row: vector k of one body is vector k of the other
             const int head_y = min(n, mis ? V - mis : 0);
             const int nbody_y = (n - head_y) / V;
             for (int i = threadIdx.x; i < head_y; i += blockDim.x) yr[i] = Num<T>::from_f(out_of(i, i < valid ? Num<T>::to_f(xr[i]) : 0.f));
             Vec* yb = reinterpret_cast<Vec*>(yr + head_y);
-            const Vec* xb = reinterpret_cast<const Vec*>(xr + head_y);
             const float2 k2 = make_float2(kLog2e, kLog2e), nmb2 = make_float2(-mb, -mb), inv2 = make_float2(inv, inv);
-#pragma unroll 4
-            for (int vi = threadIdx.x; vi < nbody_y; vi += blockDim.x) {
-                const int c0 = head_y + vi * V;
+            const int nfull = head_y == head ? nbody : 0;  // (they differ only when `valid` ends inside the head)
+            stream_vectors(gb, nfull, ring, [&](int vi, const Vec& p) {
                 Vec o;
-                if (c0 + V <= valid) {
-                    const Vec p = xb[vi];
-                    if (sizeof(T) == 2 && !is_log) {
+                if constexpr (sizeof(T) == 2) {
+                    if (!is_log) {
                         const uint32_t* w = reinterpret_cast<const uint32_t*>(&p);
                         uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
-                        if constexpr (sizeof(T) == 2) {
 #pragma unroll
-                            for (int k = 0; k < V / 2; ++k) {
-                                const float2 t = __ffma2_rn(widen2<T>(w[k]), k2, nmb2);
-                                ow[k] = pack2_16<T>(__fmul2_rn(make_float2(ex2_fast(t.x), ex2_fast(t.y)), inv2));
-                            }
+                        for (int k = 0; k < V / 2; ++k) {
+                            const float2 t = __ffma2_rn(widen2<T>(w[k]), k2, nmb2);
+                            ow[k] = pack2_16<T>(__fmul2_rn(make_float2(ex2_fast(t.x), ex2_fast(t.y)), inv2));
                         }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < V; ++j) o.v[j] = Num<T>::from_f(out_of(c0 + j, Num<T>::to_f(p.v[j])));
+                        yb[vi] = o;
+                        return;
                     }
-                } else {  // the vector the causal boundary cuts, and those past it (their input is not read)
-#pragma unroll
-                    for (int j = 0; j < V; ++j) o.v[j] = Num<T>::from_f(out_of(c0 + j, c0 + j < valid ? Num<T>::to_f(xr[c0 + j]) : 0.f));
                 }
+#pragma unroll
+                for (int j = 0; j < V; ++j) o.v[j] = Num<T>::from_f(out_of(head + vi * V + j, Num<T>::to_f(p.v[j])));
+                yb[vi] = o;
+            });
+            // the vector the causal boundary cuts and those past it (their input is not read), then the tail
+            for (int vi = nfull + threadIdx.x; vi < nbody_y; vi += blockDim.x) {
+                const int c0 = head_y + vi * V;
+                Vec o;
+#pragma unroll
+                for (int j = 0; j < V; ++j) o.v[j] = Num<T>::from_f(out_of(c0 + j, c0 + j < valid ? Num<T>::to_f(xr[c0 + j]) : 0.f));
                 yb[vi] = o;
             }
             for (int i = head_y + nbody_y * V + threadIdx.x; i < n; i += blockDim.x)
@@ -662,7 +691,7 @@ extern "C" int rfx_online_softmax(const RfxSoftmaxArgs* a) {
         // a vector is read by the thread that then overwrites it
         const int64_t g = a->rows < cap ? a->rows : cap;
         RFX_DISPATCH_DTYPE(a->dtype, T, {
-            softmax_rows_twopass_kernel<T><<<(int)g, 256, 0, s>>>((const T*)a->x, (T*)a->y, a->rows, n, a->is_causal, a->log);
+            softmax_rows_twopass_kernel<T><<<(int)g, kTwoPassThreads, 0, s>>>((const T*)a->x, (T*)a->y, a->rows, n, a->is_causal, a->log);
         });
         return check_launch(name);
     }
