@@ -90,6 +90,8 @@ def parse_args():
     ap.add_argument("--shard", default=None, choices=["replica", "request", "head"],
                     help="default: request (strong scaling); a multi-GPU run without this flag also measures "
                          "the other modes and reports them under other_shards")
+    ap.add_argument("--pool-pages", type=int, default=0,
+                    help="with --only cfg5: pages in the pool instead of 1,048,576 (a small case for ncu; >= 65536)")
     ap.add_argument("--small-filter", default=None,
                     help="with --only small_ops: time only the ops whose label contains this text (small cases for ncu)")
     ap.add_argument("--only", default=None, choices=["cfg3", "cfg5", "linear_norm", "small_ops", "int8_kv", "clocks"],
@@ -628,7 +630,7 @@ def measure_mixed(args, device):
     workloads = load_workloads()
     from kernels.attention import PagedAttentionCall, RopeAppendCall
     from kernels.kv_cache import kv_paged_scatter
-    b = workloads.cfg5(device=device)
+    b = workloads.cfg5(device=device, pool_pages=(args.pool_pages or None))
     q_rot = torch.empty_like(b.q_new)
     ra = RopeAppendCall(b.k_new, b.v_new, b.k_cache, b.v_cache, b.slot_mapping, b.positions, b.cos, b.sin,
                         q=b.q_new, q_out=q_rot)
@@ -676,7 +678,7 @@ def measure_mixed(args, device):
     kv = float(b.kv_bytes())
     peak, _ = measured_peak()
     return {"config": "cfg5: bf16 mixed batch, 64 requests x U[1,64] new tokens on contexts U[0,16384], 28q/4kv "
-                      "heads, D=128, page 16, 1,048,576-page pool (40 % free), 10 % of requests compacted",
+                      f"heads, D=128, page 16, {b.num_blocks:,}-page pool (40 % free), 10 % of requests compacted",
             "value": b.n_tokens * args.steps / (total_ms * 1e-3), "unit": UNIT, "ms_per_step": total_ms / args.steps,
             "kernel": {3: "prefill_tc_kernel + decode_mma_kernel (one-row requests)", 2: "prefill_tc_kernel",
                        1: "decode_mma_kernel"}.get(attn.kernel_kind, "scalar"),
