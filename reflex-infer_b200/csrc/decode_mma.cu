@@ -80,6 +80,7 @@ struct DecodeParams {
     const int32_t* pair_item_begin;
     int32_t* pair_counter;
     int n_pairs;
+    int late_trigger;  // 1: dependents may start only once this kernel's own predecessors are done (see the kernel)
 };
 
 template <int HD, int GP, int STAGES, bool Q8 = false>
@@ -304,8 +305,14 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         ptx::fence_barrier_init();
     }
     __syncthreads();
-    ptx::pdl_trigger();  // the combine kernel may be scheduled behind this one already
+    // The kernel behind this one may be scheduled already: the combine kernel waits for this one itself.
+    // When this kernel takes the one-row requests of a mixed batch, the kernel behind it is the chunked
+    // prefill kernel, which reads the same plan and does not wait for this kernel until its own end (its
+    // CTAs fill the SMs this kernel's CTAs leave): it must not start before the plan is complete, so the
+    // trigger comes after this kernel's own wait.
+    if (!P.late_trigger) ptx::pdl_trigger();
     ptx::pdl_wait();     // everything below reads what earlier kernels wrote (plan, pool, Q)
+    if (P.late_trigger) ptx::pdl_trigger();
 
     if (warp >= kConsumers) {  // the last warps
         // ------------------------------------------------------------ producers --
@@ -1052,6 +1059,7 @@ int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const P
     P.pair_item_begin = Pp.pair_item_begin;
     P.pair_counter = Pp.pair_counter;
     P.n_pairs = (int)(a->batch * a->num_kv_heads);
+    P.late_trigger = single_row_requests_only ? 1 : 0;
     if (a->kv_int8) {
         // half the bytes per stage: ten (eight) stages fit where the 16-bit pool has six (five)
         if (a->dtype == RFX_BF16) {

@@ -66,6 +66,7 @@ struct PrefillParams {
     float* pacc;
     int items_cap;
     int skip_single;                           // split-K mode: requests with one query row belong to the decode kernel
+    int wait_late;                             // 1: the kernel before this one (the decode kernel of a mixed batch) is waited for at the end only
     int64_t bt_sb, max_blocks, num_blocks;
     int B, Hq, Hkv, G, T;                      // T = query tokens per tile = 128 / G
     int Sq, Sk;                                // dense sizes (paged: Sq = host bound on rows per request)
@@ -111,11 +112,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    // Launched with programmatic stream serialisation. Normally everything before this kernel (the plan)
+    // has to be complete before anything is read. In a mixed batch the kernel before this one is the decode
+    // kernel for the one-row requests, which itself started only when the plan was complete and lets its
+    // dependents start then: this kernel's CTAs take the SMs as that kernel's CTAs leave them, and wait for
+    // it only before they exit, so that the combine kernel behind sees both kernels' partial rows.
+    if (!P.wait_late) ptx::pdl_wait();
+    ptx::pdl_trigger();
+
     // ---- which pair of tiles: the latest query tokens first (most K tiles under causal masking)
     int qt, b, hkv, kb = 0, ke_item = 0x7fffffff, prow = 0;
     if (P.items) {
         const int item = (int)(blockIdx.x % P.items_cap);
-        if (item >= P.hdr[0]) return;  // hdr[0] = number of items
+        if (item >= P.hdr[0]) { if (P.wait_late) ptx::pdl_wait(); return; }  // hdr[0] = number of items
         qt = (int)(blockIdx.x / P.items_cap);
         const int4 d = P.items[item];
         b = d.x; hkv = d.y; kb = d.z; ke_item = d.w;
@@ -135,7 +144,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     // checked by the plan kernel.)
     if (!P.items && threadIdx.x == 0 && P.status && qt == P.n_qtiles - 1 && n_q > P.n_qtiles * 2 * P.T)
         atomicOr(P.status, kStatusCapacity);
-    if (tok0 >= n_q || (P.skip_single && n_q == 1)) return;  // uniform over the CTA; nothing allocated yet
+    if (tok0 >= n_q || (P.skip_single && n_q == 1)) {  // uniform over the CTA; nothing allocated yet
+        if (P.wait_late) ptx::pdl_wait();
+        return;
+    }
     const int off = ctx - n_q;                      // bottom-right: token t sees keys <= t + off
     const int last_tok = min(n_q, tok0 + 2 * P.T) - 1;
     // keys [kb, kv_end) are streamed: the item's range cut at the causal bound of the last row
@@ -567,6 +579,7 @@ done:
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem, 512);
     }
+    if (P.wait_late) ptx::pdl_wait();
 }
 
 }  // namespace rfx
@@ -586,7 +599,8 @@ static int launch_prefill_t(const CUtensorMap& qm, const CUtensorMap& km, const 
         if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "prefill smem opt-in: %s", cudaGetErrorString(e));
         attr_set.mark(dev);
     }
-    kern<<<grid, kPfThreads, PfSmem::total, stream>>>(qm, km, vm, P);
+    cudaError_t le = launch_pdl(kern, dim3(grid), dim3(kPfThreads), PfSmem::total, stream, qm, km, vm, P);
+    if (le != cudaSuccess) return fail(RFX_CUDA_ERROR, "prefill_tc_kernel: %s", cudaGetErrorString(le));
     return check_launch("prefill_tc_kernel");
 }
 
@@ -747,6 +761,7 @@ int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, c
         if (cap > L->max_items) cap = L->max_items;
         P.items_cap = (int)cap;
         P.skip_single = skip_single_row_requests ? 1 : 0;
+        P.wait_late = P.skip_single;  // then the decode kernel runs right before this one
         grid = (int64_t)P.n_qtiles * cap;
     }
     if (grid >= (1ll << 31)) return fail(RFX_INVALID_ARGUMENT, "prefill grid too large");
