@@ -498,7 +498,7 @@ template <typename T>
 __global__ void __launch_bounds__(kTwoPassThreads)
 softmax_rows_twopass_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n, int causal, int is_log) {
     __shared__ float red[32];
-    __shared__ __align__(16) unsigned char ring[kTwoPassThreads * kTwoPassDepth * 16];
+    extern __shared__ __align__(16) unsigned char ring[];  // kTwoPassThreads * kTwoPassDepth * 16 bytes (+ padding, see the launch)
     constexpr float kLog2e = 1.4426950408889634f;
     constexpr int V = 16 / sizeof(T);
     struct alignas(16) Vec { T v[V]; };
@@ -690,8 +690,25 @@ extern "C" int rfx_online_softmax(const RfxSoftmaxArgs* a) {
         // in place is fine: pass one has read the whole row before pass two writes any of it, and in pass two
         // a vector is read by the thread that then overwrites it
         const int64_t g = a->rows < cap ? a->rows : cap;
+        // CTAs per SM. Pass two finds the row in L2 only while the rows between their two passes fit there
+        // with room to spare: at six CTAs per SM 8 x 1024 x 50 257 fp16 has 90 MB of rows under way and
+        // runs at 0.69 of the copy rate, at four 0.76, at three (44 MB) 0.82, at two 0.71 (too few bytes in
+        // flight). A batch that fits into one wave of at most six CTAs per SM takes that wave. The dynamic
+        // shared memory beyond the ring is padding that sets the number.
+        const size_t row_bytes = (size_t)n * e;
+        const int sms = sm_count();
+        int64_t k = (int64_t)((45ull << 20) / ((size_t)sms * row_bytes));
+        k = k < 2 ? 2 : k > 6 ? 6 : k;
+        const int64_t k_wave = (a->rows + sms - 1) / sms;
+        if (k_wave > k && k_wave <= 6 && (size_t)a->rows * row_bytes <= (64ull << 20)) k = k_wave;
+        const int ring = kTwoPassThreads * kTwoPassDepth * 16;
+        int dyn = (int)(233472 / k) - 1024 - 256;  // shared memory of an SM / k, less the per-CTA reserve and the static part
+        if (dyn < ring) dyn = ring;
         RFX_DISPATCH_DTYPE(a->dtype, T, {
-            softmax_rows_twopass_kernel<T><<<(int)g, kTwoPassThreads, 0, s>>>((const T*)a->x, (T*)a->y, a->rows, n, a->is_causal, a->log);
+            auto kern = softmax_rows_twopass_kernel<T>;
+            cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn);
+            if (ce != cudaSuccess) return fail(RFX_CUDA_ERROR, "%s: smem opt-in: %s", name, cudaGetErrorString(ce));
+            kern<<<(int)g, kTwoPassThreads, dyn, s>>>((const T*)a->x, (T*)a->y, a->rows, n, a->is_causal, a->log);
         });
         return check_launch(name);
     }
