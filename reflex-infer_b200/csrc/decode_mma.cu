@@ -61,7 +61,6 @@ struct DecodeParams {
     const int32_t* rpos;
     int32_t* hdr;
     const int32_t* part_first;
-    const int32_t* run_head;   // the runs' head records (kRunHeadWords each), or nullptr
     const int4* items;
     const int32_t* item_prow;
     float* pm;
@@ -331,15 +330,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         // entry for every run the launch could have), one round trip instead of two before the first copy.
         int first_begin = P.part_first[blockIdx.x], first_end = P.part_first[blockIdx.x + 1];
         const int n_parts = P.hdr[HdrNumParts];
-        // ... and with the run's head record, one word per lane: the first item of the CTA's first run starts
-        // its copies from that record, without the round trips for its descriptor, its pair, its RoPE
-        // position and its pages.
-        const bool use_rec = P.run_head != nullptr;
-        const int rec_w = use_rec ? P.run_head[(size_t)blockIdx.x * kRunHeadWords + lane] : 0;
-        // tiles of the head item whose pages the record holds; the item's page windows (and the descriptor of
-        // the item behind it) are asked for once every producer warp has had a tile of its own, or those run out
-        const int rec_tiles = kRunHeadPages * P.block_size / kTile;
-        const int rec_defer = min(rec_tiles, kProducers);
         int stage = 0;
         uint32_t phase = 0;
         int turn = 0;  // whose stage comes next
@@ -352,7 +342,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 const int my_id = ib + lane;
                 int4 my_desc = make_int4(0, 0, 0, 0);
                 int my_prow = 0, my_pos = -1, my_qrow = -1, my_item0 = 0, my_ns = 1;
-                const bool head_batch = use_rec && part == (int)blockIdx.x && ib == i_begin;
                 if (my_id < i_end) {
                     my_desc = P.items[my_id];
                     my_prow = P.item_prow[my_id];
@@ -375,8 +364,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     return (lb <= last && lb < P.max_blocks) ? bt[lb] : -1;
                 };
                 // block-table window of the first item; later items prefetch during their predecessor
-                int64_t nx_cur = -1, nx_nxt = -1;
-                if (!head_batch) {
+                int64_t nx_cur, nx_nxt;
+                {
                     const int b0 = __shfl_sync(0xffffffffu, my_desc.x, 0);
                     const int kb0 = __shfl_sync(0xffffffffu, my_desc.z, 0), ke0 = __shfl_sync(0xffffffffu, my_desc.w, 0);
                     const int64_t* bt0 = P.block_table + (int64_t)b0 * P.bt_sb;
@@ -384,54 +373,28 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     nx_nxt = load_win(bt0, kb0 / P.block_size + 32, ke0);
                 }
                 for (int j = 0; j < n_here && alive; ++j) {
-                    // the head item takes everything from the record and touches none of the registers the
-                    // loads above are still filling until its first copies are on their way
-                    const bool head_item = head_batch && j == 0;
-                    int b, hkv, kb, ke, prow, pos, qrow, item0, ns;
-                    if (head_item) {
-                        b = __shfl_sync(0xffffffffu, rec_w, RhRequest); hkv = __shfl_sync(0xffffffffu, rec_w, RhHead);
-                        kb = __shfl_sync(0xffffffffu, rec_w, RhKeyBegin); ke = __shfl_sync(0xffffffffu, rec_w, RhKeyEnd);
-                        prow = __shfl_sync(0xffffffffu, rec_w, RhPartialRow);
-                        pos = P.rcos ? __shfl_sync(0xffffffffu, rec_w, RhRopePos) : -1;
-                        qrow = b;
-                        item0 = __shfl_sync(0xffffffffu, rec_w, RhPairItem0); ns = __shfl_sync(0xffffffffu, rec_w, RhPairItems);
-                    } else {
-                        b = __shfl_sync(0xffffffffu, my_desc.x, j); hkv = __shfl_sync(0xffffffffu, my_desc.y, j);
-                        kb = __shfl_sync(0xffffffffu, my_desc.z, j); ke = __shfl_sync(0xffffffffu, my_desc.w, j);
-                        prow = __shfl_sync(0xffffffffu, my_prow, j);
-                        pos = __shfl_sync(0xffffffffu, my_pos, j);
-                        qrow = __shfl_sync(0xffffffffu, my_qrow, j);
-                        item0 = __shfl_sync(0xffffffffu, my_item0, j); ns = __shfl_sync(0xffffffffu, my_ns, j);
-                    }
+                    const int b = __shfl_sync(0xffffffffu, my_desc.x, j), hkv = __shfl_sync(0xffffffffu, my_desc.y, j);
+                    const int kb = __shfl_sync(0xffffffffu, my_desc.z, j), ke = __shfl_sync(0xffffffffu, my_desc.w, j);
+                    const int prow = __shfl_sync(0xffffffffu, my_prow, j);
+                    const int pos = __shfl_sync(0xffffffffu, my_pos, j);
+                    const int qrow = __shfl_sync(0xffffffffu, my_qrow, j);
+                    const int item0 = __shfl_sync(0xffffffffu, my_item0, j), ns = __shfl_sync(0xffffffffu, my_ns, j);
                     const bool rotate = P.rcos != nullptr && pos >= 0 && (int64_t)pos < P.table_rows;
                     const int64_t* bt = P.block_table + (int64_t)b * P.bt_sb;
                     int win0 = kb / P.block_size;
-                    int64_t pg_cur = -1, pg_nxt = -1;
-                    bool need_win = head_item;  // the windows of this item and of the next are still to be asked for
-                    auto next_windows = [&]() {
-                        if (j + 1 < n_here) {
-                            const int b1 = __shfl_sync(0xffffffffu, my_desc.x, j + 1);
-                            const int kb1 = __shfl_sync(0xffffffffu, my_desc.z, j + 1);
-                            const int ke1 = __shfl_sync(0xffffffffu, my_desc.w, j + 1);
-                            const int64_t* bt1 = P.block_table + (int64_t)b1 * P.bt_sb;
-                            nx_cur = load_win(bt1, kb1 / P.block_size, ke1);
-                            nx_nxt = load_win(bt1, kb1 / P.block_size + 32, ke1);
-                        }
-                    };
-                    if (!head_item) {
-                        pg_cur = nx_cur; pg_nxt = nx_nxt;
-                        next_windows();
+                    int64_t pg_cur = nx_cur, pg_nxt = nx_nxt;
+                    if (j + 1 < n_here) {
+                        const int b1 = __shfl_sync(0xffffffffu, my_desc.x, j + 1);
+                        const int kb1 = __shfl_sync(0xffffffffu, my_desc.z, j + 1);
+                        const int ke1 = __shfl_sync(0xffffffffu, my_desc.w, j + 1);
+                        const int64_t* bt1 = P.block_table + (int64_t)b1 * P.bt_sb;
+                        nx_cur = load_win(bt1, kb1 / P.block_size, ke1);
+                        nx_nxt = load_win(bt1, kb1 / P.block_size + 32, ke1);
                     }
                     if (qrow < 0) continue;
                     const int n_tiles = (ke - kb + kTile - 1) / kTile;
                     for (int t = 0; t < n_tiles && alive; ++t) {
                         const int tok0 = kb + t * kTile;
-                        if (need_win && t >= rec_defer) {
-                            pg_cur = load_win(bt, win0, ke);
-                            pg_nxt = load_win(bt, win0 + 32, ke);
-                            next_windows();
-                            need_win = false;
-                        }
                         const bool mine = turn == pw;
                         if (++turn == kProducers) turn = 0;
                         if (!mine) {
@@ -463,14 +426,9 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             const int lb = tok / P.block_size;
                             my_row0 = tok - lb * P.block_size;
                             const int rel = lb - win0;  // 0..63 by construction of the window advance
-                            if (need_win) {  // a tile of the head item that the record covers (rel < kRunHeadPages)
-                                const int pg = __shfl_sync(0xffffffffu, rec_w, RhPages + (rel & (kRunHeadPages - 1)));
-                                if (want) my_page = pg;
-                            } else {
-                                const int64_t a = __shfl_sync(0xffffffffu, pg_cur, rel & 31);
-                                const int64_t c2 = __shfl_sync(0xffffffffu, pg_nxt, rel & 31);
-                                if (want) my_page = rel < 32 ? a : c2;
-                            }
+                            const int64_t a = __shfl_sync(0xffffffffu, pg_cur, rel & 31);
+                            const int64_t c2 = __shfl_sync(0xffffffffu, pg_nxt, rel & 31);
+                            if (want) my_page = rel < 32 ? a : c2;
                         }
                         const bool page_ok = my_page >= 0 && my_page < P.num_blocks;
                         const unsigned okmask = __ballot_sync(0xffffffffu, lane < n_boxes && page_ok);
@@ -535,7 +493,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             pg_nxt = load_win(bt, win0 + 32, ke);
                         }
                     }
-                    if (need_win) next_windows();  // a head item shorter than the record: only the next item's windows
                 }
             }
         }
@@ -1103,7 +1060,6 @@ int launch_decode_mma(const RfxPagedAttentionArgs* a, const PlanLayout&, const P
     P.pair_counter = Pp.pair_counter;
     P.n_pairs = (int)(a->batch * a->num_kv_heads);
     P.late_trigger = single_row_requests_only ? 1 : 0;
-    P.run_head = single_row_requests_only ? nullptr : Pp.run_head;
     if (a->kv_int8) {
         // half the bytes per stage: ten (eight) stages fit where the 16-bit pool has six (five)
         if (a->dtype == RFX_BF16) {

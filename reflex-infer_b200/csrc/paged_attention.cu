@@ -56,14 +56,12 @@ extern "C" int rfx_paged_attention_plan(const RfxPagedAttentionArgs* a) {
     const PlanPtrs P = plan_ptrs(a->workspace, L);
     int ctas = decode_mma_supported(a) ? decode_mma_ctas(a) : sm_count() * 4;
     int item_cost = decode_mma_supported(a) ? kDecodeItemCost : 0;
-    bool head_records = decode_mma_supported(a);
     if (prefill_paged_supported(a)) {
         if (!prefill_paged_split(a)) return RFX_SUCCESS;  // that kernel needs no plan
         ctas = prefill_paged_parts(a);
         item_cost = 0;
-        head_records = false;
     }
-    return launch_plan(a, L, P, ctas, item_cost, head_records);
+    return launch_plan(a, L, P, ctas, item_cost);
 }
 
 namespace rfx {
@@ -112,7 +110,7 @@ static int run_stages(const RfxPagedAttentionArgs* a, const char* name, int stag
     }
     const bool mma = decode_mma_supported(a);
     if (stages & kStagePlan) {
-        st = launch_plan(a, L, P, mma ? decode_mma_ctas(a) : sm_count() * 4, mma ? kDecodeItemCost : 0, mma);
+        st = launch_plan(a, L, P, mma ? decode_mma_ctas(a) : sm_count() * 4, mma ? kDecodeItemCost : 0);
         if (st != RFX_SUCCESS) return st;
     }
     // One call for the whole step and no gather: the decode kernel merges the split pairs itself and

@@ -11,7 +11,6 @@
 //   pair_counter    : int32[B*Hkv]        finished items of each pair (decode kernel's in-kernel merge;
 //                                         zeroed by the plan, put back to zero by the last item of a pair)
 //   part_first      : int32[max_parts+1]  first item of each run
-//   run_head        : int32[max_parts][32] what the decode kernel needs to start a run's first copy (see kRunHead*)
 //   items           : int4[max_items]     (request, kv_head, key_begin, key_end)
 //   item_prow       : int32[max_items+1]  first partial row of each item
 //   m, l            : float[cap_rows] each   running max (scaled, natural-log domain), sum
@@ -40,17 +39,8 @@ constexpr int kStatusBadPage = 2;
 constexpr int kStatusCapacity = 4;   // the device-side row counts exceed what the host sized the workspace for
 constexpr int kPlanTile = 64;  // keys per tile of the stream
 
-// A run's head record: the first item of the run with everything the decode kernel would otherwise fetch
-// in three dependent round trips (item, pair and RoPE position, block table) before its first copy.
-// Words: request, kv head, first key, end key, first partial row, first item of the pair, items of the
-// pair, RoPE position of the request (-1: none); from word 16 the item's first sixteen pages (-1 past
-// its end, or when the table holds a number that is no page).
-constexpr int kRunHeadWords = 32;
-constexpr int kRunHeadPages = 16;
-enum : int { RhRequest = 0, RhHead, RhKeyBegin, RhKeyEnd, RhPartialRow, RhPairItem0, RhPairItems, RhRopePos, RhPages = 16 };
-
 struct PlanLayout {
-    size_t off_pair_begin, off_pair_counter, off_part_first, off_run_head, off_items, off_item_prow, off_m, off_l, off_acc, total;
+    size_t off_pair_begin, off_pair_counter, off_part_first, off_items, off_item_prow, off_m, off_l, off_acc, total;
     int64_t max_parts, max_items, cap_rows;
 };
 
@@ -68,7 +58,6 @@ inline PlanLayout plan_layout(int64_t B, int64_t Hkv, int64_t G, int64_t n_q, in
     L.off_pair_begin = o; o = align_up(o + (size_t)(B * Hkv + 1) * 4, 256);
     L.off_pair_counter = o; o = align_up(o + (size_t)(B * Hkv) * 4, 256);
     L.off_part_first = o; o = align_up(o + (size_t)(L.max_parts + 1) * 4, 256);
-    L.off_run_head = o;   o = align_up(o + (size_t)L.max_parts * kRunHeadWords * 4, 256);
     L.off_items = o;      o = align_up(o + (size_t)L.max_items * 16, 256);
     L.off_item_prow = o;  o = align_up(o + (size_t)(L.max_items + 1) * 4, 256);
     L.off_m = o;          o = align_up(o + (size_t)L.cap_rows * 4, 256);
@@ -83,7 +72,6 @@ struct PlanPtrs {
     int32_t* pair_item_begin;
     int32_t* pair_counter;
     int32_t* part_first;
-    int32_t* run_head;
     int4* items;
     int32_t* item_prow;
     float* m;
@@ -98,7 +86,6 @@ inline PlanPtrs plan_ptrs(void* ws, const PlanLayout& L) {
     r.pair_item_begin = (int32_t*)(p + L.off_pair_begin);
     r.pair_counter = (int32_t*)(p + L.off_pair_counter);
     r.part_first = (int32_t*)(p + L.off_part_first);
-    r.run_head = (int32_t*)(p + L.off_run_head);
     r.items = (int4*)(p + L.off_items);
     r.item_prow = (int32_t*)(p + L.off_item_prow);
     r.m = (float*)(p + L.off_m);
@@ -116,9 +103,7 @@ constexpr int kDecodeItemCost = RFX_DECODE_ITEM_COST;
 
 // Host launchers implemented in their own files. `parts_hint` is the number of runs the
 // partial kernel wants (its CTA count).
-// `head_records`: also write the runs' head records (the decode kernel reads them).
-int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int parts_hint, int item_cost = 0,
-                bool head_records = false);
+int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int parts_hint, int item_cost = 0);
 int launch_paged_generic(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P);
 // `gather` != nullptr: rows go to every rank's full output (see RfxHeadGatherArgs).
 int launch_paged_combine(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P,

@@ -41,9 +41,7 @@ __global__ void __launch_bounds__(kPlanThreads)
 plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_start, int B, int Hkv,
             int G, long long max_parts, long long target_chunk, int parts_hint, long long item_cost, long long max_items,
             long long cap_rows, long long max_q_len, long long n_q, int32_t* hdr,
-            int32_t* pair_item_begin, int32_t* pair_counter, int32_t* part_first, int4* items, int32_t* item_prow,
-            int32_t* run_head, const int64_t* __restrict__ block_table, long long bt_stride, long long max_blocks,
-            int block_size, const int32_t* __restrict__ rope_pos) {
+            int32_t* pair_item_begin, int32_t* pair_counter, int32_t* part_first, int4* items, int32_t* item_prow) {
     __shared__ long long red[kPlanThreads / 32][2];
     ptx::pdl_trigger();  // the partial kernel may set itself up while the plan is computed
     const int tid = threadIdx.x;
@@ -143,31 +141,13 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
             if (tb == 0) continue;
             const long long off = pre * Hkv + h * tb + c * (ne * Hkv + h);
             const long long p0 = off / q, p1 = (off + tb - 1) / q;
-            const long long it_pair = it;
             for (long long p = p0; p <= p1; ++p) {
                 const long long s = max(off, p * q), e = min(off + tb, (p + 1) * q);
-                const int kb = (int)((s - off) * kPlanTile), ke = min(ctx, (int)((e - off) * kPlanTile));
-                items[it] = make_int4(b, h, kb, ke);
+                items[it] = make_int4(b, h, (int)((s - off) * kPlanTile), min(ctx, (int)((e - off) * kPlanTile)));
                 item_prow[it] = (int)rw;
                 // the first item of run p: it starts the run, or it starts its pair and the pair before it
                 // (whose last tile sits at off - c - 1) ended in an earlier run
-                if (s == p * q || (s == off && off - c <= p * q)) {
-                    part_first[p] = (int)it;
-                    if (run_head) {
-                        int32_t* r = run_head + p * kRunHeadWords;
-                        long long pg[kRunHeadPages];
-                        const long long lb0 = kb / block_size, lb_last = ((long long)ke - 1) / block_size;
-#pragma unroll
-                        for (int i = 0; i < kRunHeadPages; ++i)
-                            pg[i] = (lb0 + i <= lb_last && lb0 + i < max_blocks) ? block_table[(long long)b * bt_stride + lb0 + i] : -1;
-                        r[RhRequest] = b; r[RhHead] = h; r[RhKeyBegin] = kb; r[RhKeyEnd] = ke;
-                        r[RhPartialRow] = (int)rw; r[RhPairItem0] = (int)it_pair; r[RhPairItems] = (int)(p1 - p0 + 1);
-                        r[RhRopePos] = rope_pos ? rope_pos[b] : -1;
-#pragma unroll
-                        for (int i = 0; i < kRunHeadPages; ++i)
-                            r[RhPages + i] = (pg[i] >= 0 && pg[i] < 0x7fffffffll) ? (int)pg[i] : -1;
-                    }
-                }
+                if (s == p * q || (s == off && off - c <= p * q)) part_first[p] = (int)it;
                 ++it;
                 rw += nq * G;
             }
@@ -190,8 +170,7 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
     ptx::pdl_wait();
 }
 
-int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int parts_hint, int item_cost,
-                bool head_records) {
+int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int parts_hint, int item_cost) {
     const int G = (int)(a->num_q_heads / a->num_kv_heads);
     // a small batch gets a small CTA: the scans and barriers of 32 warps cost a one-CTA kernel microseconds
     cudaError_t e;
@@ -200,9 +179,7 @@ int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanP
                    (int)a->batch, (int)a->num_kv_heads, G, (long long)L.max_parts, (long long)a->target_chunk,        \
                    parts_hint, (long long)item_cost, (long long)L.max_items, (long long)L.cap_rows,                   \
                    (long long)(a->max_q_len < 1 ? 1 : a->max_q_len), (long long)a->n_q, P.hdr, P.pair_item_begin,     \
-                   P.pair_counter, P.part_first, P.items, P.item_prow, head_records ? P.run_head : (int32_t*)nullptr,     \
-                   a->block_table, (long long)a->bt_stride_b, (long long)a->max_blocks, (int)a->block_size,           \
-                   a->rope_cos ? a->rope_positions : (const int32_t*)nullptr)
+                   P.pair_counter, P.part_first, P.items, P.item_prow)
     if (a->batch <= 32) RFX_PLAN_LAUNCH(32);
     else if (a->batch <= 128) RFX_PLAN_LAUNCH(128);
     else RFX_PLAN_LAUNCH(kPlanMaxThreads);
