@@ -13,6 +13,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace rfx {
 
@@ -296,6 +297,15 @@ softmax_rows_reg_body(const T* __restrict__ x, T* __restrict__ y, int64_t rows, 
     }
 }
 
+// The softmax kernels are launched with programmatic stream serialisation: the kernel behind one of them
+// may be scheduled as soon as all its CTAs have started, so that a CTA slot is taken again the moment
+// it is freed, and reads nothing before everything ahead of it in the stream has completed. A short call
+// between two others no longer pays its launch latency on top of its memory time.
+__device__ __forceinline__ void pdl_prologue() {
+    ptx::pdl_trigger();
+    ptx::pdl_wait();
+}
+
 // MINB = resident CTAs per SM asked of the compiler. Rows of one or two fp32 vectors per thread are
 // bound by the warps in flight (ncu: 40 of 64 warps at 48 registers): eight CTAs per SM, which fits them
 // into 32 registers without spills (4096 x 4096 bf16 24.6 -> 22.5 us); longer fp32 rows keep the plain
@@ -305,6 +315,7 @@ softmax_rows_reg_body(const T* __restrict__ x, T* __restrict__ y, int64_t rows, 
 template <typename T, int TPR, int ITEMS, int MINB>
 __global__ void __launch_bounds__(kVecThreads, MINB)
 softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n, int causal, int is_log) {
+    pdl_prologue();
     softmax_rows_reg_body<T, TPR, ITEMS>(x, y, rows, n, causal, is_log);
 }
 
@@ -332,6 +343,7 @@ __device__ inline void for_each_store(T* row, int count, F val) {
 template <typename T>
 __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n,
                                     int causal, int is_log) {
+    pdl_prologue();
     extern __shared__ __align__(16) unsigned char srow_raw[];
     T* srow = reinterpret_cast<T*>(srow_raw);
     __shared__ float red[32];
@@ -497,6 +509,7 @@ __device__ __forceinline__ void stream_vectors(const VecT* gb, int nvec, unsigne
 template <typename T>
 __global__ void __launch_bounds__(kTwoPassThreads)
 softmax_rows_twopass_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int n, int causal, int is_log) {
+    pdl_prologue();
     __shared__ float red[32];
     extern __shared__ __align__(16) unsigned char ring[];  // kTwoPassThreads * kTwoPassDepth * 16 bytes (+ padding, see the launch)
     constexpr float kLog2e = 1.4426950408889634f;
@@ -621,7 +634,8 @@ static void launch_softmax_reg(const RfxSoftmaxArgs* a, int64_t groups, int64_t 
     }
     const int64_t wave = (TPR == 32 || sizeof(T) != 4 || ITEMS < 4) ? cap : (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);
     const int64_t g2 = groups < wave ? groups : wave;
-    kern<<<(int)g2, TPR == 32 ? kVecThreads : TPR, 0, s>>>((const T*)a->x, (T*)a->y, a->rows, (int)a->n, a->is_causal, a->log);
+    launch_pdl(kern, dim3((unsigned)g2), dim3(TPR == 32 ? kVecThreads : TPR), 0, s, (const T*)a->x, (T*)a->y, a->rows, (int)a->n,
+               (int)a->is_causal, (int)a->log);
 }
 
 template <typename T, int TPR>
@@ -708,7 +722,8 @@ extern "C" int rfx_online_softmax(const RfxSoftmaxArgs* a) {
             auto kern = softmax_rows_twopass_kernel<T>;
             cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn);
             if (ce != cudaSuccess) return fail(RFX_CUDA_ERROR, "%s: smem opt-in: %s", name, cudaGetErrorString(ce));
-            kern<<<(int)g, kTwoPassThreads, dyn, s>>>((const T*)a->x, (T*)a->y, a->rows, n, a->is_causal, a->log);
+            launch_pdl(kern, dim3((unsigned)g), dim3(kTwoPassThreads), (size_t)dyn, s, (const T*)a->x, (T*)a->y, a->rows, n,
+                       (int)a->is_causal, (int)a->log);
         });
         return check_launch(name);
     }
@@ -719,7 +734,8 @@ extern "C" int rfx_online_softmax(const RfxSoftmaxArgs* a) {
             cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_need);
             if (ce != cudaSuccess) return fail(RFX_CUDA_ERROR, "%s: smem opt-in: %s", name, cudaGetErrorString(ce));
         }
-        kern<<<(int)grid, threads, smem_need, s>>>((const T*)a->x, (T*)a->y, a->rows, n, a->is_causal, a->log);
+        launch_pdl(kern, dim3((unsigned)grid), dim3(threads), smem_need, s, (const T*)a->x, (T*)a->y, a->rows, n,
+                   (int)a->is_causal, (int)a->log);
     });
     return check_launch(name);
 }
