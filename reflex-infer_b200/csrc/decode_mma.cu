@@ -313,6 +313,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     if (!P.late_trigger) ptx::pdl_trigger();
     ptx::pdl_wait();     // everything below reads what earlier kernels wrote (plan, pool, Q)
     if (P.late_trigger) ptx::pdl_trigger();
+    // a mixed batch without one-row requests: nothing here is this kernel's (uniform over the grid)
+    if (P.q_start != nullptr && P.hdr[HdrOneRowRequests] == 0) return;
 
     if (warp >= kConsumers) {  // the last warps
         // ------------------------------------------------------------ producers --

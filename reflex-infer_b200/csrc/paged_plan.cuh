@@ -31,6 +31,7 @@ enum : int {
     HdrNumParts = 2,
     HdrStatus = 3,
     HdrTotalRows = 4,
+    HdrOneRowRequests = 5,  // 1: some request has a single query row (and keys)
     HdrWords = 64
 };
 

@@ -112,8 +112,12 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
     // may be written past the capacity: the plan is left empty -- no items, no runs, every pair
     // without splits, so the partial kernels do nothing and the combine writes zeros -- and
     // kStatusCapacity is raised in the status word.
-    int over = 0;
-    for (int b = b0; b < b1; ++b) over |= nq_of(b) > max_q_len ? 1 : 0;
+    int over = 0, one_row = 0;  // one_row: a request with a single query row and keys (the decode kernel's in a mixed batch)
+    for (int b = b0; b < b1; ++b) {
+        over |= nq_of(b) > max_q_len ? 1 : 0;
+        one_row |= (nq_of(b) == 1 && ctx_of(b) > 0) ? 1 : 0;
+    }
+    const int any_one_row = __syncthreads_or(one_row);
     if (tid == 0 && q_start) over |= ((long long)q_start[B] - q_start[0] != n_q) ? 1 : 0;
     over |= (n_items > max_items || n_rows > cap_rows) ? 1 : 0;
     if (__syncthreads_or(over)) {
@@ -126,6 +130,7 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
             hdr[HdrNumParts] = 0;
             hdr[HdrStatus] = kStatusCapacity;
             hdr[HdrTotalRows] = 0;
+            hdr[HdrOneRowRequests] = 0;
         }
         ptx::pdl_wait();
         return;
@@ -164,6 +169,7 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
         hdr[HdrNumParts] = (int)n_parts;
         hdr[HdrStatus] = 0;
         hdr[HdrTotalRows] = (int)n_rows;
+        hdr[HdrOneRowRequests] = any_one_row ? 1 : 0;
     }
     // The plan reads nothing its predecessor wrote, but its successor (the partial kernel) does
     // (the pool pages just appended): do not complete before the predecessor has.

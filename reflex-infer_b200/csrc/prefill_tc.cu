@@ -66,7 +66,7 @@ struct PrefillParams {
     float* pacc;
     int items_cap;
     int skip_single;                           // split-K mode: requests with one query row belong to the decode kernel
-    int wait_late;                             // 1: the kernel before this one (the decode kernel of a mixed batch) is waited for at the end only
+    int wait_late;                             // 1: the kernel before this one (the decode kernel of a mixed batch) is waited for by the grid's last CTA only, at its end
     int64_t bt_sb, max_blocks, num_blocks;
     int B, Hq, Hkv, G, T;                      // T = query tokens per tile = 128 / G
     int Sq, Sk;                                // dense sizes (paged: Sq = host bound on rows per request)
@@ -115,20 +115,24 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     // Launched with programmatic stream serialisation. Normally everything before this kernel (the plan)
     // has to be complete before anything is read. In a mixed batch the kernel before this one is the decode
     // kernel for the one-row requests, which itself started only when the plan was complete and lets its
-    // dependents start then: this kernel's CTAs take the SMs as that kernel's CTAs leave them, and wait for
-    // it only before they exit, so that the combine kernel behind sees both kernels' partial rows.
+    // dependents start then: this kernel's CTAs take the SMs as that kernel's CTAs leave them. The grid
+    // must not complete before that kernel has (the combine kernel behind reads both kernels' partial
+    // rows), but a CTA that waited for it would hold its SM until then, so one CTA waits for all: the last
+    // of the grid, at its end. The plan is read past L1 (this CTA may have started before the grid
+    // boundary that would have emptied it).
     if (!P.wait_late) ptx::pdl_wait();
     ptx::pdl_trigger();
+    const bool waiter = P.wait_late && blockIdx.x == gridDim.x - 1;
 
     // ---- which pair of tiles: the latest query tokens first (most K tiles under causal masking)
     int qt, b, hkv, kb = 0, ke_item = 0x7fffffff, prow = 0;
     if (P.items) {
         const int item = (int)(blockIdx.x % P.items_cap);
-        if (item >= P.hdr[0]) { if (P.wait_late) ptx::pdl_wait(); return; }  // hdr[0] = number of items
+        if (item >= __ldcg(&P.hdr[0])) { if (waiter) ptx::pdl_wait(); return; }  // hdr[0] = number of items
         qt = (int)(blockIdx.x / P.items_cap);
-        const int4 d = P.items[item];
+        const int4 d = __ldcg(&P.items[item]);
         b = d.x; hkv = d.y; kb = d.z; ke_item = d.w;
-        prow = P.item_prow[item];
+        prow = __ldcg(&P.item_prow[item]);
     } else {
         const int pairs = P.B * P.Hkv;
         qt = P.n_qtiles - 1 - (int)(blockIdx.x / pairs);
@@ -145,7 +149,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     if (!P.items && threadIdx.x == 0 && P.status && qt == P.n_qtiles - 1 && n_q > P.n_qtiles * 2 * P.T)
         atomicOr(P.status, kStatusCapacity);
     if (tok0 >= n_q || (P.skip_single && n_q == 1)) {  // uniform over the CTA; nothing allocated yet
-        if (P.wait_late) ptx::pdl_wait();
+        if (waiter) ptx::pdl_wait();
         return;
     }
     const int off = ctx - n_q;                      // bottom-right: token t sees keys <= t + off
@@ -579,7 +583,7 @@ done:
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem, 512);
     }
-    if (P.wait_late) ptx::pdl_wait();
+    if (waiter) ptx::pdl_wait();
 }
 
 }  // namespace rfx
@@ -703,16 +707,15 @@ bool prefill_paged_split(const RfxPagedAttentionArgs* a) {
 int prefill_paged_parts(const RfxPagedAttentionArgs* a) { (void)a; return 4 * sm_count(); }
 
 // A request with a single query row fills 1/18th or less of a 128-row tile and still pays the
-// tile's step time (about 64 KB of K/V per 4600 cycles and SM, a quarter of HBM speed). When most
-// requests of a split batch are such decode rows they go to the decode kernel, which streams K/V
-// at HBM speed, and both kernels leave partials for the one combine. With few decode rows the
-// hand-over does not pay: the decode kernel's CTAs take the plan's runs in a fixed order and
-// the decode rows are spread unevenly over them. The host sees only the totals, so the rule is
-// "at most four query rows per request on average"; the debug words mixed=0 / mixed=1 override it.
+// tile's step time (about 64 KB of K/V per 4600 cycles and SM, a quarter of HBM speed). In a split
+// batch such decode rows go to the decode kernel, which streams K/V at HBM speed; it runs first, this
+// kernel's CTAs take the SMs its CTAs leave, and both leave partials for the one combine. Without
+// one-row requests (the plan says so in the header) the decode kernel returns at once. The debug words
+// mixed=0 / mixed=1 override the choice.
 bool prefill_paged_mixed(const RfxPagedAttentionArgs* a) {
     if (!prefill_paged_split(a) || !decode_mma_shape_ok(a)) return false;
     if (debug_flags() & (kDbgMixedOn | kDbgMixedOff)) return (debug_flags() & kDbgMixedOn) != 0;
-    return a->n_q <= 4 * a->batch;
+    return true;
 }
 
 int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, const PlanLayout* L,

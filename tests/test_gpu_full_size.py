@@ -79,7 +79,7 @@ def test_cfg5_chunk_of_64_tokens_behind_a_16k_context(native):
     ws = PagedWorkspace(DEV)
     call = PagedAttentionCall(q_gpu, g.k_cache, g.v_cache, g.block_table, g.context_lens, q_start=g.q_start,
                               max_q_len=cpu.max_q_len, workspace=ws)
-    assert call.kernel_kind == 2
+    assert call.kernel_kind == 3  # split over the keys; the decode kernel in front finds no one-row request and returns
     out = call.run()
     assert ws.status() == 0
     torch.testing.assert_close(out.cpu().float(), ref.float(), atol=TOL, rtol=TOL)

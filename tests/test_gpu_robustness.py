@@ -62,7 +62,7 @@ def test_page_index_outside_the_pool_is_left_out_by_every_kernel(mode, native):
         call = PagedAttentionCall(q_rot.to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV), cpu.context_lens.to(DEV),
                                   workspace=ws, force_generic=generic, **kw)
         if not generic:
-            assert call.kernel_kind == (1 if mode == "decode" else 2)
+            assert call.kernel_kind == {"decode": 1, "chunks_whole": 2}.get(mode, 3)
         out = call.run()
         assert ws.status() & BAD_PAGE, "the bad page must be reported"
         assert torch.isfinite(out).all()
