@@ -59,7 +59,7 @@ extern "C" int rfx_paged_attention_plan(const RfxPagedAttentionArgs* a) {
     if (prefill_paged_supported(a)) {
         if (!prefill_paged_split(a)) return RFX_SUCCESS;  // that kernel needs no plan
         ctas = prefill_paged_parts(a);
-        item_cost = 0;
+        return launch_plan(a, L, P, ctas, 0, prefill_paged_unit_rows(a), prefill_paged_mixed(a));
     }
     return launch_plan(a, L, P, ctas, item_cost);
 }
@@ -93,7 +93,7 @@ static int run_stages(const RfxPagedAttentionArgs* a, const char* name, int stag
             return launch_prefill_paged(a, P.hdr + HdrStatus, &L, nullptr);
         }
         if (stages & kStagePlan) {
-            st = launch_plan(a, L, P, prefill_paged_parts(a));
+            st = launch_plan(a, L, P, prefill_paged_parts(a), 0, prefill_paged_unit_rows(a), prefill_paged_mixed(a));
             if (st != RFX_SUCCESS) return st;
         }
         if (stages & kStagePartials) {

@@ -12,6 +12,7 @@
 //                                         zeroed by the plan, put back to zero by the last item of a pair)
 //   part_first      : int32[max_parts+1]  first item of each run
 //   items           : int4[max_items]     (request, kv_head, key_begin, key_end)
+//   unit_order      : int2[max_units]     chunked prefill: (item, pair of query tiles) of every CTA, the longest first
 //   item_prow       : int32[max_items+1]  first partial row of each item
 //   m, l            : float[cap_rows] each   running max (scaled, natural-log domain), sum
 //   acc             : float[cap_rows][D]     un-normalised sum of p*V
@@ -32,6 +33,7 @@ enum : int {
     HdrStatus = 3,
     HdrTotalRows = 4,
     HdrOneRowRequests = 5,  // 1: some request has a single query row (and keys)
+    HdrNumUnits = 6,        // entries of unit_order
     HdrWords = 64
 };
 
@@ -41,8 +43,8 @@ constexpr int kStatusCapacity = 4;   // the device-side row counts exceed what t
 constexpr int kPlanTile = 64;  // keys per tile of the stream
 
 struct PlanLayout {
-    size_t off_pair_begin, off_pair_counter, off_part_first, off_items, off_item_prow, off_m, off_l, off_acc, total;
-    int64_t max_parts, max_items, cap_rows;
+    size_t off_pair_begin, off_pair_counter, off_part_first, off_items, off_unit_order, off_item_prow, off_m, off_l, off_acc, total;
+    int64_t max_parts, max_items, cap_rows, max_units;
 };
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -60,6 +62,9 @@ inline PlanLayout plan_layout(int64_t B, int64_t Hkv, int64_t G, int64_t n_q, in
     L.off_pair_counter = o; o = align_up(o + (size_t)(B * Hkv) * 4, 256);
     L.off_part_first = o; o = align_up(o + (size_t)(L.max_parts + 1) * 4, 256);
     L.off_items = o;      o = align_up(o + (size_t)L.max_items * 16, 256);
+    // an item of a request with n rows has ceil(n / 2T) units, 2T * G > 128; the items' rows sum to <= cap_rows / G
+    L.max_units = L.cap_rows / 128 + L.max_items;
+    L.off_unit_order = o; o = align_up(o + (size_t)L.max_units * 8, 256);
     L.off_item_prow = o;  o = align_up(o + (size_t)(L.max_items + 1) * 4, 256);
     L.off_m = o;          o = align_up(o + (size_t)L.cap_rows * 4, 256);
     L.off_l = o;          o = align_up(o + (size_t)L.cap_rows * 4, 256);
@@ -74,6 +79,7 @@ struct PlanPtrs {
     int32_t* pair_counter;
     int32_t* part_first;
     int4* items;
+    int2* unit_order;
     int32_t* item_prow;
     float* m;
     float* l;
@@ -88,6 +94,7 @@ inline PlanPtrs plan_ptrs(void* ws, const PlanLayout& L) {
     r.pair_counter = (int32_t*)(p + L.off_pair_counter);
     r.part_first = (int32_t*)(p + L.off_part_first);
     r.items = (int4*)(p + L.off_items);
+    r.unit_order = (int2*)(p + L.off_unit_order);
     r.item_prow = (int32_t*)(p + L.off_item_prow);
     r.m = (float*)(p + L.off_m);
     r.l = (float*)(p + L.off_l);
@@ -104,7 +111,10 @@ constexpr int kDecodeItemCost = RFX_DECODE_ITEM_COST;
 
 // Host launchers implemented in their own files. `parts_hint` is the number of runs the
 // partial kernel wants (its CTA count).
-int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int parts_hint, int item_cost = 0);
+// `unit_rows` > 0 (chunked prefill): also list the kernel's units of work -- (item, pair of query tiles of
+// unit_rows rows) -- by falling length; `skip_one_row`: without the requests of one query row.
+int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int parts_hint, int item_cost = 0,
+                int unit_rows = 0, bool skip_one_row = false);
 int launch_paged_generic(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P);
 // `gather` != nullptr: rows go to every rank's full output (see RfxHeadGatherArgs).
 int launch_paged_combine(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P,
@@ -121,6 +131,7 @@ int decode_mma_ctas(const RfxPagedAttentionArgs* a);
 bool prefill_paged_supported(const RfxPagedAttentionArgs* a);
 bool prefill_paged_split(const RfxPagedAttentionArgs* a);  // split-K over the plan's items?
 int prefill_paged_parts(const RfxPagedAttentionArgs* a);
+int prefill_paged_unit_rows(const RfxPagedAttentionArgs* a);  // query rows of a request that one CTA takes
 // `split` = nullptr: whole rows per CTA, output written directly; else partials for the combine.
 int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, const PlanLayout* L,
                          const PlanPtrs* split, bool skip_single_row_requests = false);

@@ -36,13 +36,24 @@ __device__ inline void block_exscan2(long long& a, long long& b, long long (*red
     b = bb + ib - b;
 }
 
+// Length classes of the chunked-prefill kernel's units of work (K/V steps of 128 keys, a unit with two
+// live query tiles counted an eighth longer).
+constexpr int kUnitBuckets = 64;
+__device__ inline int unit_bucket(int kb, int ke, bool two_tiles) {
+    const int steps = (ke - kb + 127) / 128;
+    const int c = two_tiles ? steps + (steps + 7) / 8 : steps;
+    return kUnitBuckets - 1 - min(kUnitBuckets - 1, c);  // 0 = the longest
+}
+
 template <int kPlanThreads>
 __global__ void __launch_bounds__(kPlanThreads)
 plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_start, int B, int Hkv,
             int G, long long max_parts, long long target_chunk, int parts_hint, long long item_cost, long long max_items,
             long long cap_rows, long long max_q_len, long long n_q, int32_t* hdr,
-            int32_t* pair_item_begin, int32_t* pair_counter, int32_t* part_first, int4* items, int32_t* item_prow) {
+            int32_t* pair_item_begin, int32_t* pair_counter, int32_t* part_first, int4* items, int32_t* item_prow,
+            int2* unit_order, long long max_units, int unit_rows, int skip_one_row) {
     __shared__ long long red[kPlanThreads / 32][2];
+    __shared__ int unit_hist[kUnitBuckets];  // units per length class, the longest class first; then the class's cursor
     ptx::pdl_trigger();  // the partial kernel may set itself up while the plan is computed
     const int tid = threadIdx.x;
     for (long long i = tid; i < (long long)B * Hkv; i += kPlanThreads) pair_counter[i] = 0;
@@ -131,11 +142,17 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
             hdr[HdrStatus] = kStatusCapacity;
             hdr[HdrTotalRows] = 0;
             hdr[HdrOneRowRequests] = 0;
+            hdr[HdrNumUnits] = 0;
         }
         ptx::pdl_wait();
         return;
     }
 
+    const bool list_units = unit_order != nullptr && unit_rows > 0;
+    if (list_units) {
+        for (int i = tid; i < kUnitBuckets; i += kPlanThreads) unit_hist[i] = 0;
+        __syncthreads();
+    }
     long long pre = tile_pre, ne = ne_pre, it = item_pre, rw = row_pre;
     for (int b = b0; b < b1; ++b) {
         const int ctx = ctx_of(b);
@@ -153,12 +170,53 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
                 // the first item of run p: it starts the run, or it starts its pair and the pair before it
                 // (whose last tile sits at off - c - 1) ended in an earlier run
                 if (s == p * q || (s == off && off - c <= p * q)) part_first[p] = (int)it;
+                if (list_units && !(skip_one_row && nq == 1)) {
+                    const int kb = (int)((s - off) * kPlanTile), ke = min(ctx, (int)((e - off) * kPlanTile));
+                    for (long long u = 0; u * unit_rows < nq; ++u)
+                        atomicAdd(&unit_hist[unit_bucket(kb, ke, u * unit_rows + unit_rows / 2 < nq)], 1);
+                }
                 ++it;
                 rw += nq * G;
             }
         }
         if (tb > 0) ++ne;
         pre += tb;
+    }
+    bool units_over = false;
+    if (list_units) {
+        // classes to cursors (one thread: 64 additions), then every unit takes the next place of its class
+        __shared__ int n_units_s;
+        __syncthreads();
+        if (tid == 0) {
+            int run = 0;
+            for (int i = 0; i < kUnitBuckets; ++i) { const int n = unit_hist[i]; unit_hist[i] = run; run += n; }
+            n_units_s = run;
+        }
+        __syncthreads();
+        const bool fits = n_units_s <= max_units;  // by the capacity rule; if not, the kernel finds no unit and the status says so
+        long long pre2 = tile_pre, ne2 = ne_pre, it2 = item_pre;
+        for (int b = b0; b < b1 && fits; ++b) {
+            const int ctx = ctx_of(b);
+            const long long tb = (ctx + kPlanTile - 1) / kPlanTile;
+            const long long nq = nq_of(b);
+            for (int h = 0; h < Hkv && tb > 0; ++h) {
+                const long long off = pre2 * Hkv + h * tb + c * (ne2 * Hkv + h);
+                const long long p0 = off / q, p1 = (off + tb - 1) / q;
+                for (long long p = p0; p <= p1; ++p, ++it2) {
+                    if (skip_one_row && nq == 1) continue;
+                    const long long s = max(off, p * q), e = min(off + tb, (p + 1) * q);
+                    const int kb = (int)((s - off) * kPlanTile), ke = min(ctx, (int)((e - off) * kPlanTile));
+                    for (long long u = 0; u * unit_rows < nq; ++u) {
+                        const int at = atomicAdd(&unit_hist[unit_bucket(kb, ke, u * unit_rows + unit_rows / 2 < nq)], 1);
+                        unit_order[at] = make_int2((int)it2, (int)u);
+                    }
+                }
+            }
+            if (tb > 0) ++ne2;
+            pre2 += tb;
+        }
+        units_over = !fits;
+        if (tid == 0) hdr[HdrNumUnits] = fits ? n_units_s : 0;
     }
     if (tid == 0) {
         pair_item_begin[(long long)B * Hkv] = (int)n_items;
@@ -167,7 +225,7 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
         hdr[HdrNumItems] = (int)n_items;
         hdr[HdrTilesPerPart] = (int)q;
         hdr[HdrNumParts] = (int)n_parts;
-        hdr[HdrStatus] = 0;
+        hdr[HdrStatus] = units_over ? kStatusCapacity : 0;
         hdr[HdrTotalRows] = (int)n_rows;
         hdr[HdrOneRowRequests] = any_one_row ? 1 : 0;
     }
@@ -176,7 +234,8 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
     ptx::pdl_wait();
 }
 
-int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int parts_hint, int item_cost) {
+int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P, int parts_hint, int item_cost,
+                int unit_rows, bool skip_one_row) {
     const int G = (int)(a->num_q_heads / a->num_kv_heads);
     // a small batch gets a small CTA: the scans and barriers of 32 warps cost a one-CTA kernel microseconds
     cudaError_t e;
@@ -185,7 +244,8 @@ int launch_plan(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanP
                    (int)a->batch, (int)a->num_kv_heads, G, (long long)L.max_parts, (long long)a->target_chunk,        \
                    parts_hint, (long long)item_cost, (long long)L.max_items, (long long)L.cap_rows,                   \
                    (long long)(a->max_q_len < 1 ? 1 : a->max_q_len), (long long)a->n_q, P.hdr, P.pair_item_begin,     \
-                   P.pair_counter, P.part_first, P.items, P.item_prow)
+                   P.pair_counter, P.part_first, P.items, P.item_prow, unit_rows > 0 ? P.unit_order : (int2*)nullptr,     \
+                   (long long)L.max_units, unit_rows, skip_one_row ? 1 : 0)
     if (a->batch <= 32) RFX_PLAN_LAUNCH(32);
     else if (a->batch <= 128) RFX_PLAN_LAUNCH(128);
     else RFX_PLAN_LAUNCH(kPlanMaxThreads);

@@ -61,6 +61,7 @@ struct PrefillParams {
     const int4* items;
     const int32_t* item_prow;
     const int32_t* hdr;
+    const int2* unit_order;
     float* pm;
     float* pl;
     float* pacc;
@@ -127,9 +128,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     // ---- which pair of tiles: the latest query tokens first (most K tiles under causal masking)
     int qt, b, hkv, kb = 0, ke_item = 0x7fffffff, prow = 0;
     if (P.items) {
-        const int item = (int)(blockIdx.x % P.items_cap);
-        if (item >= __ldcg(&P.hdr[0])) { if (waiter) ptx::pdl_wait(); return; }  // hdr[0] = number of items
-        qt = (int)(blockIdx.x / P.items_cap);
+        // the plan lists the units of work -- (item, pair of query tiles) -- the longest first
+        if ((int)blockIdx.x >= __ldcg(&P.hdr[HdrNumUnits])) { if (waiter) ptx::pdl_wait(); return; }
+        const int2 unit = __ldcg(&P.unit_order[blockIdx.x]);
+        const int item = unit.x;
+        qt = unit.y;
         const int4 d = __ldcg(&P.items[item]);
         b = d.x; hkv = d.y; kb = d.z; ke_item = d.w;
         prow = __ldcg(&P.item_prow[item]);
@@ -705,6 +708,7 @@ bool prefill_paged_split(const RfxPagedAttentionArgs* a) {
 // Runs per launch: CTAs of up to ~27 steps keep the last wave short (measured on the mixed
 // batch: 1x 0.547, 2x 0.479, 3x 0.453, 4x 0.449, 6x 0.464 ms; a CTA costs ~6-11 us to start and finish).
 int prefill_paged_parts(const RfxPagedAttentionArgs* a) { (void)a; return 4 * sm_count(); }
+int prefill_paged_unit_rows(const RfxPagedAttentionArgs* a) { return 2 * (int)(128 / (a->num_q_heads / a->num_kv_heads)); }
 
 // A request with a single query row fills 1/18th or less of a 128-row tile and still pays the
 // tile's step time (about 64 KB of K/V per 4600 cycles and SM, a quarter of HBM speed). In a split
@@ -757,7 +761,7 @@ int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, c
     P.scale_log2 = a->sm_scale * 1.4426950408889634f;
     int64_t grid = (int64_t)P.n_qtiles * P.B * P.Hkv;
     if (split) {
-        P.items = split->items; P.item_prow = split->item_prow; P.hdr = split->hdr;
+        P.items = split->items; P.item_prow = split->item_prow; P.hdr = split->hdr; P.unit_order = split->unit_order;
         P.pm = split->m; P.pl = split->l; P.pacc = split->acc;
         // the plan makes at most one item per pair plus one per run boundary
         int64_t cap = a->batch * a->num_kv_heads + (a->target_chunk > 0 ? L->max_parts : prefill_paged_parts(a));
@@ -766,6 +770,7 @@ int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, c
         P.skip_single = skip_single_row_requests ? 1 : 0;
         P.wait_late = P.skip_single;  // then the decode kernel runs right before this one
         grid = (int64_t)P.n_qtiles * cap;
+        if (grid > L->max_units) grid = L->max_units;  // the plan lists no more than that
     }
     if (grid >= (1ll << 31)) return fail(RFX_INVALID_ARGUMENT, "prefill grid too large");
     if (a->dtype == RFX_BF16) return launch_prefill_t<__nv_bfloat16>(qm, km, vm, P, (int)grid, as_stream(a->stream));
