@@ -36,13 +36,17 @@ __device__ inline void block_exscan2(long long& a, long long& b, long long (*red
     b = bb + ib - b;
 }
 
-// Length classes of the chunked-prefill kernel's units of work (K/V steps of 128 keys, a unit with two
-// live query tiles counted an eighth longer).
-constexpr int kUnitBuckets = 64;
-__device__ inline int unit_bucket(int kb, int ke, bool two_tiles) {
-    const int steps = (ke - kb + 127) / 128;
-    const int c = two_tiles ? steps + (steps + 7) / 8 : steps;
-    return kUnitBuckets - 1 - min(kUnitBuckets - 1, c);  // 0 = the longest
+// Length classes of the chunked-prefill kernel's units of work: eighths of the longest a unit can be
+// (K/V steps of 128 keys in a run of `q` 64-key tiles, a unit with two live query tiles counted an
+// eighth longer). Class 0 holds the longest.
+constexpr int kUnitClasses = 8;
+// 32-bit compares only: one warp runs this, every instruction at its full latency, and a 64-bit division
+// per unit made the plan three times as long.
+__device__ inline int unit_class(int cost, const int (&thr)[kUnitClasses - 1]) {
+    int k = 0;
+#pragma unroll
+    for (int i = 0; i < kUnitClasses - 1; ++i) k += cost >= thr[i] ? 1 : 0;
+    return kUnitClasses - 1 - k;
 }
 
 template <int kPlanThreads>
@@ -53,7 +57,6 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
             int32_t* pair_item_begin, int32_t* pair_counter, int32_t* part_first, int4* items, int32_t* item_prow,
             int2* unit_order, long long max_units, int unit_rows, int skip_one_row) {
     __shared__ long long red[kPlanThreads / 32][2];
-    __shared__ int unit_hist[kUnitBuckets];  // units per length class, the longest class first; then the class's cursor
     ptx::pdl_trigger();  // the partial kernel may set itself up while the plan is computed
     const int tid = threadIdx.x;
     for (long long i = tid; i < (long long)B * Hkv; i += kPlanThreads) pair_counter[i] = 0;
@@ -96,6 +99,22 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
     const long long q = T > 0 ? (T + parts - 1) / parts : 1;
     const long long n_parts = T > 0 ? (T + q - 1) / q : 0;
 
+    const bool list_units = unit_order != nullptr && unit_rows > 0;
+    int ucnt[kUnitClasses];  // this thread's units per class (kept in registers: constant indices only)
+#pragma unroll
+    for (int k = 0; k < kUnitClasses; ++k) ucnt[k] = 0;
+    int uthr[kUnitClasses - 1];  // a unit's cost is its steps times 9 (two live query tiles) or 8 (one)
+    {
+        const int cmax = (int)min((long long)(1 << 24), ((q + 1) / 2 + 1)) * 9;
+#pragma unroll
+        for (int k = 0; k < kUnitClasses - 1; ++k) uthr[k] = (cmax * (k + 1) + kUnitClasses - 1) / kUnitClasses;
+    }
+    // units of an item of a request with nq rows: all but possibly the last have two live tiles
+    auto units_of = [&](int nq, int& n_two, int& n_one) {
+        const int n_u = (nq + unit_rows - 1) / unit_rows;
+        n_one = (nq - (n_u - 1) * unit_rows <= unit_rows / 2) ? 1 : 0;
+        n_two = n_u - n_one;
+    };
     // items and partial rows before each request
     long long item_pre = 0, row_pre = 0, n_items, n_rows;
     {
@@ -106,9 +125,23 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
             if (tb > 0) {
                 for (int h = 0; h < Hkv; ++h) {
                     const long long off = pre * Hkv + h * tb + c * (ne * Hkv + h);
-                    const long long ni = (off + tb - 1) / q - off / q + 1;
+                    const long long p0 = off / q, p1 = (off + tb - 1) / q;
+                    const long long ni = p1 - p0 + 1;
                     item_pre += ni;
                     row_pre += ni * nq * G;
+                    if (list_units && !(skip_one_row && nq == 1)) {
+                        int n_two, n_one;
+                        units_of((int)nq, n_two, n_one);
+                        const int ctx = ctx_of(b);
+                        for (long long p = p0; p <= p1; ++p) {
+                            const long long s = max(off, p * q), e = min(off + tb, (p + 1) * q);
+                            const int kb = (int)((s - off) * kPlanTile), ke = min(ctx, (int)((e - off) * kPlanTile));
+                            const int steps = (ke - kb + 127) / 128;
+                            const int c2 = unit_class(steps * 9, uthr), c1 = unit_class(steps * 8, uthr);
+#pragma unroll
+                            for (int k = 0; k < kUnitClasses; ++k) ucnt[k] += (c2 == k ? n_two : 0) + (c1 == k ? n_one : 0);
+                        }
+                    }
                 }
                 ++ne;
             }
@@ -116,6 +149,20 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
         }
     }
     block_exscan2<kPlanThreads>(item_pre, row_pre, red, n_items, n_rows);
+    // places in the unit list: the classes one after the other, inside a class the threads in order (no
+    // atomics: most units of a batch fall into one class)
+    long long upos[kUnitClasses], n_units = 0;
+    if (list_units) {
+        long long utot[kUnitClasses];
+#pragma unroll
+        for (int k = 0; k < kUnitClasses; k += 2) {
+            upos[k] = ucnt[k]; upos[k + 1] = ucnt[k + 1];
+            block_exscan2<kPlanThreads>(upos[k], upos[k + 1], red, utot[k], utot[k + 1]);
+        }
+#pragma unroll
+        for (int k = 0; k < kUnitClasses; ++k) { upos[k] += n_units; n_units += utot[k]; }
+    }
+    const bool units_over = n_units > max_units;  // not by the capacity rule; then the kernel finds no unit and the status says so
 
     // The workspace was sized on the host from max_q_len and n_q; the row counts used here come
     // from q_start on the device. If they do not agree (a request with more rows than max_q_len,
@@ -148,11 +195,6 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
         return;
     }
 
-    const bool list_units = unit_order != nullptr && unit_rows > 0;
-    if (list_units) {
-        for (int i = tid; i < kUnitBuckets; i += kPlanThreads) unit_hist[i] = 0;
-        __syncthreads();
-    }
     long long pre = tile_pre, ne = ne_pre, it = item_pre, rw = row_pre;
     for (int b = b0; b < b1; ++b) {
         const int ctx = ctx_of(b);
@@ -170,10 +212,20 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
                 // the first item of run p: it starts the run, or it starts its pair and the pair before it
                 // (whose last tile sits at off - c - 1) ended in an earlier run
                 if (s == p * q || (s == off && off - c <= p * q)) part_first[p] = (int)it;
-                if (list_units && !(skip_one_row && nq == 1)) {
+                if (list_units && !units_over && !(skip_one_row && nq == 1)) {
                     const int kb = (int)((s - off) * kPlanTile), ke = min(ctx, (int)((e - off) * kPlanTile));
-                    for (long long u = 0; u * unit_rows < nq; ++u)
-                        atomicAdd(&unit_hist[unit_bucket(kb, ke, u * unit_rows + unit_rows / 2 < nq)], 1);
+                    const int steps = (ke - kb + 127) / 128;
+                    int n_two, n_one;
+                    units_of((int)nq, n_two, n_one);
+                    const int c2 = unit_class(steps * 9, uthr), c1 = unit_class(steps * 8, uthr);
+                    for (int u = 0; u < n_two + n_one; ++u) {
+                        const int cls = u < n_two ? c2 : c1;
+                        long long at = 0;
+#pragma unroll
+                        for (int k = 0; k < kUnitClasses; ++k)
+                            if (cls == k) at = upos[k]++;
+                        unit_order[at] = make_int2((int)it, u);
+                    }
                 }
                 ++it;
                 rw += nq * G;
@@ -181,42 +233,6 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
         }
         if (tb > 0) ++ne;
         pre += tb;
-    }
-    bool units_over = false;
-    if (list_units) {
-        // classes to cursors (one thread: 64 additions), then every unit takes the next place of its class
-        __shared__ int n_units_s;
-        __syncthreads();
-        if (tid == 0) {
-            int run = 0;
-            for (int i = 0; i < kUnitBuckets; ++i) { const int n = unit_hist[i]; unit_hist[i] = run; run += n; }
-            n_units_s = run;
-        }
-        __syncthreads();
-        const bool fits = n_units_s <= max_units;  // by the capacity rule; if not, the kernel finds no unit and the status says so
-        long long pre2 = tile_pre, ne2 = ne_pre, it2 = item_pre;
-        for (int b = b0; b < b1 && fits; ++b) {
-            const int ctx = ctx_of(b);
-            const long long tb = (ctx + kPlanTile - 1) / kPlanTile;
-            const long long nq = nq_of(b);
-            for (int h = 0; h < Hkv && tb > 0; ++h) {
-                const long long off = pre2 * Hkv + h * tb + c * (ne2 * Hkv + h);
-                const long long p0 = off / q, p1 = (off + tb - 1) / q;
-                for (long long p = p0; p <= p1; ++p, ++it2) {
-                    if (skip_one_row && nq == 1) continue;
-                    const long long s = max(off, p * q), e = min(off + tb, (p + 1) * q);
-                    const int kb = (int)((s - off) * kPlanTile), ke = min(ctx, (int)((e - off) * kPlanTile));
-                    for (long long u = 0; u * unit_rows < nq; ++u) {
-                        const int at = atomicAdd(&unit_hist[unit_bucket(kb, ke, u * unit_rows + unit_rows / 2 < nq)], 1);
-                        unit_order[at] = make_int2((int)it2, (int)u);
-                    }
-                }
-            }
-            if (tb > 0) ++ne2;
-            pre2 += tb;
-        }
-        units_over = !fits;
-        if (tid == 0) hdr[HdrNumUnits] = fits ? n_units_s : 0;
     }
     if (tid == 0) {
         pair_item_begin[(long long)B * Hkv] = (int)n_items;
@@ -226,6 +242,7 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
         hdr[HdrTilesPerPart] = (int)q;
         hdr[HdrNumParts] = (int)n_parts;
         hdr[HdrStatus] = units_over ? kStatusCapacity : 0;
+        hdr[HdrNumUnits] = (list_units && !units_over) ? (int)n_units : 0;
         hdr[HdrTotalRows] = (int)n_rows;
         hdr[HdrOneRowRequests] = any_one_row ? 1 : 0;
     }
