@@ -72,6 +72,7 @@ const char* rfx_last_error(void);
  *   no_tc            scalar kernels where a tcgen05 kernel would run (attention, linear + norm)
  *   prefill_nosplit  chunked prefill is not split over the keys
  *   mixed=1 / mixed=0  one-row requests of a split batch always / never go to the decode kernel
+ *                    (default: they do whenever that kernel takes the shapes)
  *   tma2d            the decode kernel's 2-D tensor maps
  * rfx_debug_set_flags(words) replaces them for the whole process (NULL: back to the environment's). */
 int rfx_debug_set_flags(const char* words);
@@ -305,8 +306,9 @@ int rfx_paged_attention_partials_final(const RfxPagedAttentionArgs* a);
 /* Which kernel the arguments select: 2 = tcgen05 prefill kernel (16-bit, head_dim 128, ragged
  * query chunks given by q_start, queries already rotated, page size >= 8 dividing or a
  * multiple of 128; whole rows per CTA, or split over the keys with plan and combine when
- * max_q_len <= 512 and pages hold <= 64 keys), 3 = the same split batch with its one-row
- * requests on the decode kernel, 1 = TMA + warp-MMA decode kernel (16-bit, head_dim 64/128,
+ * max_q_len <= 512 and pages hold <= 64 keys), 3 = the same split batch with the decode
+ * kernel launched in front of it for the requests of one query row (whenever the shapes fit that
+ * kernel; it returns at once if the batch has none), 1 = TMA + warp-MMA decode kernel (16-bit, head_dim 64/128,
  * one query row per request, group <= 16, page size a divisor or multiple of 64 and >= 8),
  * 0 = scalar kernel, negative = invalid arguments. With kv_int8: 1 = the decode kernel's int8
  * instantiation (head_dim 128, one query row per request; K and V widened to fp16 in registers,
