@@ -67,6 +67,7 @@ struct PrefillParams {
     float* pacc;
     int items_cap;
     int skip_single;                           // split-K mode: requests with one query row belong to the decode kernel
+    int out_by_tma;                            // 1: `omap` covers the output (laid out like Q): whole tiles are stored through shared memory by TMA
     int wait_late;                             // 1: the kernel before this one (the decode kernel of a mixed batch) is waited for by the grid's last CTA only, at its end
     int64_t bt_sb, max_blocks, num_blocks;
     int B, Hq, Hkv, G, T;                      // T = query tokens per tile = 128 / G
@@ -88,19 +89,20 @@ struct PfSmem {
     static constexpr size_t off_k = 2 * (size_t)kPfTileBytes;
     static constexpr size_t off_v = off_k + (size_t)kPfKvStages * kPfTileBytes;
     static constexpr size_t off_bars = off_v + (size_t)kPfKvStages * kPfTileBytes;
-    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2]
-    static constexpr int n_bars = 1 + 4 * kPfKvStages + 6;
+    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2], o_staged[2]
+    static constexpr int n_bars = 1 + 4 * kPfKvStages + 8;
     static constexpr size_t off_misc = off_bars + 8 * n_bars;
     static constexpr size_t total = off_misc + 64 + 1024;  // misc: TMEM base, abort flag, 4 bad-box masks
 };
 
 enum PfBar { PF_QFULL = 0, PF_KFULL = 1, PF_KEMPTY = 3, PF_VFULL = 5, PF_VEMPTY = 7, PF_SFULL = 9, PF_PFULL = 11,
-             PF_PVDONE = 13 };
+             PF_PVDONE = 13, PF_OSTAGED = 15 };
 
 template <typename T, bool MASK>
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
-                  const __grid_constant__ CUtensorMap vmap, const PrefillParams P) {
+                  const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap omap,
+                  const PrefillParams P) {
     constexpr bool BF = std::is_same<T, __nv_bfloat16>::value;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -165,7 +167,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     if (threadIdx.x == 0) {
         for (int i = 0; i < PfSmem::n_bars; ++i)
             // P ready: the tile's 128 softmax threads and the producer's vote (see `landed`)
-            ptx::mbar_init(&bars[i], (i == PF_PFULL || i == PF_PFULL + 1) ? 129u : 1u);
+            // O staged: the tile's 128 softmax threads (see the epilogue)
+            ptx::mbar_init(&bars[i], (i == PF_PFULL || i == PF_PFULL + 1) ? 129u : (i == PF_OSTAGED || i == PF_OSTAGED + 1) ? 128u : 1u);
         misc[1] = 0;
         ptx::fence_barrier_init();
     }
@@ -542,6 +545,64 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                     for (int i = 0; i < 8; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
                 }
             }
+        } else if (ok_all && P.out_by_tma && tok0 + x * P.T + P.T <= n_q) {
+            // Every row of the tile has a query: the tile goes out the way Q came in. A thread's row is
+            // 256 contiguous bytes, so the 32 rows of a warp's store instruction lie in 32 different
+            // lines and sixteen such instructions per thread took 2 us per tile; here the rows are
+            // written into the tile's Q buffer (free since the last scores), in the layout of the Q box
+            // with its 128-byte swizzle, and one thread hands the two 64-wide halves to the TMA unit.
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            unsigned char* stile = sQ + (size_t)x * kPfTileBytes;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t w[32];
+                if (n_kv > 0) {
+                    ptx::tmem_ld32(o_addr + c * 32, w);
+                    ptx::tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) w[i] = 0;
+                }
+                if (r < rows_used) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float a = __uint_as_float(w[i]) * inv, bq = __uint_as_float(w[i + 1]) * inv;
+                        if (BF) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(a, bq);
+                            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                        } else {
+                            __half2 h = __floats2half2_rn(a, bq);
+                            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                    }
+                    // chunk c holds elements 32c .. 32c+31: half c/2, 16-byte pieces 4(c%2) .. 4(c%2)+3 of the row
+                    unsigned char* hrow = stile + (size_t)(c >> 1) * kPfHalfBytes + (size_t)r * 128;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int piece = (c & 1) * 4 + i;
+                        *reinterpret_cast<uint4*>(hrow + (((piece ^ (r & 7)) << 4))) =
+                            make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                    }
+                }
+            }
+            ptx::fence_proxy_async_smem();
+            ptx::mbar_arrive(&bars[PF_OSTAGED + x]);
+            if ((warp & 3) == 0 && lane == 0) {
+                if (!wait_phase(PF_OSTAGED + x, 0)) {  // bounded like every wait: a warp that gave up never arrives
+                    give_up();
+                    goto done;
+                }
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    if (P.head_major_rows)
+                        ptx::tma_store_3d(&omap, stile + h * kPfHalfBytes, h * 64, tok0 + x * P.T, b * P.Hq + hkv * P.G);
+                    else
+                        ptx::tma_store_3d(&omap, stile + h * kPfHalfBytes, h * 64, hkv * P.G, q0 + tok0 + x * P.T);
+                }
+                ptx::tma_store_commit();
+                ptx::tma_store_wait_read();
+            }
         } else if (ok_all) {
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             T* orow = P.head_major_rows
@@ -596,7 +657,7 @@ namespace rfx {
 
 template <typename T, bool MASK = false>
 static int launch_prefill_t(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm,
-                            const PrefillParams& P, int grid, cudaStream_t stream) {
+                            const CUtensorMap& om, const PrefillParams& P, int grid, cudaStream_t stream) {
     auto kern = prefill_tc_kernel<T, MASK>;
     static PerDeviceOnce attr_set;  // per instantiation
     int dev = 0;
@@ -606,7 +667,7 @@ static int launch_prefill_t(const CUtensorMap& qm, const CUtensorMap& km, const 
         if (e != cudaSuccess) return fail(RFX_CUDA_ERROR, "prefill smem opt-in: %s", cudaGetErrorString(e));
         attr_set.mark(dev);
     }
-    cudaError_t le = launch_pdl(kern, dim3(grid), dim3(kPfThreads), PfSmem::total, stream, qm, km, vm, P);
+    cudaError_t le = launch_pdl(kern, dim3(grid), dim3(kPfThreads), PfSmem::total, stream, qm, km, vm, om, P);
     if (le != cudaSuccess) return fail(RFX_CUDA_ERROR, "prefill_tc_kernel: %s", cudaGetErrorString(le));
     return check_launch("prefill_tc_kernel");
 }
@@ -642,12 +703,15 @@ int launch_dense_tensor(const RfxAttentionArgs* a) {
     if (!dense_tensor_ok(a)) return RFX_NOT_IMPLEMENTED;
     const int G = (int)(a->num_q_heads / a->num_kv_heads);
     const int T = 128 / G;
-    CUtensorMap qm, km, vm;
+    CUtensorMap qm, km, vm, om;
+    bool out_by_tma = false;
     {
         const uint64_t dims[3] = {(uint64_t)kPfHD, (uint64_t)a->seq_q, (uint64_t)(a->batch * a->num_q_heads)};
         const uint64_t str[2] = {(uint64_t)kPfHD * 2, (uint64_t)a->seq_q * kPfHD * 2};
         const uint32_t box[3] = {64, (uint32_t)T, (uint32_t)G};
         if (encode_tiled_16bit(&qm, a->q, 3, dims, str, box)) return RFX_NOT_IMPLEMENTED;
+        out_by_tma = encode_tiled_16bit(&om, a->out, 3, dims, str, box) == 0;  // the output is laid out like Q
+        if (!out_by_tma) om = qm;
     }
     {
         // [half][key][64 elems] per (batch, kv head): one box lands a whole 128-key tile, keys past
@@ -668,6 +732,7 @@ int launch_dense_tensor(const RfxAttentionArgs* a) {
     P.kv_sbo = 1024; P.kv_half = kPfKeys * 128;
     P.n_qtiles = (int)((a->seq_q + 2 * T - 1) / (2 * T));
     P.head_major_rows = 1; P.causal = a->is_causal;
+    P.out_by_tma = out_by_tma ? 1 : 0;
     P.scale_log2 = a->sm_scale * 1.4426950408889634f;
     const int64_t grid = (int64_t)P.n_qtiles * P.B * P.Hkv;
     if (grid >= (1ll << 31)) return RFX_NOT_IMPLEMENTED;
@@ -675,11 +740,11 @@ int launch_dense_tensor(const RfxAttentionArgs* a) {
         P.mask = a->attn_mask;
         P.inv_scale = 1.0f / a->sm_scale;
         if (a->dtype == RFX_BF16)
-            return launch_prefill_t<__nv_bfloat16, true>(qm, km, vm, P, (int)grid, as_stream(a->stream));
-        return launch_prefill_t<__half, true>(qm, km, vm, P, (int)grid, as_stream(a->stream));
+            return launch_prefill_t<__nv_bfloat16, true>(qm, km, vm, om, P, (int)grid, as_stream(a->stream));
+        return launch_prefill_t<__half, true>(qm, km, vm, om, P, (int)grid, as_stream(a->stream));
     }
-    if (a->dtype == RFX_BF16) return launch_prefill_t<__nv_bfloat16>(qm, km, vm, P, (int)grid, as_stream(a->stream));
-    return launch_prefill_t<__half>(qm, km, vm, P, (int)grid, as_stream(a->stream));
+    if (a->dtype == RFX_BF16) return launch_prefill_t<__nv_bfloat16>(qm, km, vm, om, P, (int)grid, as_stream(a->stream));
+    return launch_prefill_t<__half>(qm, km, vm, om, P, (int)grid, as_stream(a->stream));
 }
 
 // Paged (chunked) prefill: q [N,Hq,D] already rotated, K/V in the pool.
@@ -727,13 +792,17 @@ int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, c
     const int G = (int)(a->num_q_heads / a->num_kv_heads);
     const int T = 128 / G;
     const int R = (int)(a->block_size < kPfKeys ? a->block_size : kPfKeys);  // keys per box
-    CUtensorMap qm, km, vm;
+    CUtensorMap qm, km, vm, om;
+    bool out_by_tma = false;
     {
         const uint64_t dims[3] = {(uint64_t)kPfHD, (uint64_t)a->num_q_heads, (uint64_t)a->n_q};
         const uint64_t str[2] = {(uint64_t)kPfHD * 2, (uint64_t)a->num_q_heads * kPfHD * 2};
         const uint32_t box[3] = {64, (uint32_t)G, (uint32_t)T};
         int r = encode_tiled_16bit(&qm, a->q, 3, dims, str, box);
         if (r) return fail(RFX_CUDA_ERROR, "cuTensorMapEncodeTiled(q) failed (%d)", r);
+        // whole rows per CTA: the output [N, Hq, D] is laid out like Q
+        out_by_tma = split == nullptr && encode_tiled_16bit(&om, a->out, 3, dims, str, box) == 0;
+        if (!out_by_tma) om = qm;
     }
     {
         // The pool's rows (page, kv head, position) in groups of 8: [group][half][row in group][64 elems],
@@ -758,6 +827,7 @@ int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, c
     P.kv_sbo = 2048; P.kv_half = 1024;
     P.n_qtiles = (int)((a->max_q_len + 2 * T - 1) / (2 * T));
     P.head_major_rows = 0; P.causal = a->is_causal;
+    P.out_by_tma = out_by_tma ? 1 : 0;
     P.scale_log2 = a->sm_scale * 1.4426950408889634f;
     int64_t grid = (int64_t)P.n_qtiles * P.B * P.Hkv;
     if (split) {
@@ -773,8 +843,8 @@ int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, c
         if (grid > L->max_units) grid = L->max_units;  // the plan lists no more than that
     }
     if (grid >= (1ll << 31)) return fail(RFX_INVALID_ARGUMENT, "prefill grid too large");
-    if (a->dtype == RFX_BF16) return launch_prefill_t<__nv_bfloat16>(qm, km, vm, P, (int)grid, as_stream(a->stream));
-    return launch_prefill_t<__half>(qm, km, vm, P, (int)grid, as_stream(a->stream));
+    if (a->dtype == RFX_BF16) return launch_prefill_t<__nv_bfloat16>(qm, km, vm, om, P, (int)grid, as_stream(a->stream));
+    return launch_prefill_t<__half>(qm, km, vm, om, P, (int)grid, as_stream(a->stream));
 }
 
 }  // namespace rfx
