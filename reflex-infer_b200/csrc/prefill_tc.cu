@@ -528,22 +528,36 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 P.pm[pr] = m_run * 0.6931471805599453f;
                 P.pl[pr] = l_run;
             }
-            float* arow = P.pacc + pr * kPfHD;
+            // The accumulator rows: a thread's row is 512 contiguous bytes and the rows of a tile are
+            // consecutive in the partial array, so the warp's 32 rows are one block of 16 KB. Written
+            // straight from the threads, every store instruction touched 32 different lines (32 such
+            // instructions per thread); instead the warp passes its block through shared memory -- 16 KB
+            // of the Q buffers (tile a) or the K stages (tile b), all free since the last scores, 16-byte
+            // pieces XOR-swizzled by the row so that neither side has bank conflicts -- and stores it
+            // 512 contiguous bytes per instruction. Nothing crosses a warp: __syncwarp is all it needs.
+            unsigned char* wbuf = (x == 0 ? sQ : sK) + (size_t)(warp & 3) * 16384;
+            const int rl = r & 31;
+            if (n_kv > 0) {  // uniform over the CTA; the load is warp-collective
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t w[32];
-                if (n_kv > 0) {  // uniform over the CTA; the load is warp-collective
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t w[32];
                     ptx::tmem_ld32(o_addr + c * 32, w);
                     ptx::tmem_wait_ld();
-                } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) w[i] = 0;
+                    for (int i = 0; i < 8; ++i)
+                        *reinterpret_cast<uint4*>(wbuf + rl * 512 + (((c * 8 + i) ^ rl) << 4)) =
+                            make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
                 }
-                if (row_live) {
-                    uint4* dst = reinterpret_cast<uint4*>(arow + c * 32);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
-                }
+            }
+            __syncwarp();
+            const int r_base = (warp & 3) * 32;
+            const int live_rows = max(0, min(32, min(rows_used, (n_q - tok0 - x * P.T) * P.G) - r_base));
+            float* gblock = P.pacc + ((int64_t)prow + (int64_t)(tok0 + x * P.T) * P.G + r_base) * kPfHD;
+#pragma unroll 4
+            for (int k = 0; k < live_rows; ++k) {
+                const uint4 v = n_kv > 0 ? *reinterpret_cast<const uint4*>(wbuf + k * 512 + ((lane ^ k) << 4))
+                                         : make_uint4(0, 0, 0, 0);
+                reinterpret_cast<uint4*>(gblock + (size_t)k * kPfHD)[lane] = v;
             }
         } else if (ok_all && P.out_by_tma && tok0 + x * P.T + P.T <= n_q) {
             // Every row of the tile has a query: the tile goes out the way Q came in. A thread's row is
