@@ -786,7 +786,11 @@ bool prefill_paged_split(const RfxPagedAttentionArgs* a) {
 
 // Runs per launch: CTAs of up to ~27 steps keep the last wave short (measured on the mixed
 // batch: 1x 0.547, 2x 0.479, 3x 0.453, 4x 0.449, 6x 0.464 ms; a CTA costs ~6-11 us to start and finish).
-int prefill_paged_parts(const RfxPagedAttentionArgs* a) { (void)a; return 4 * sm_count(); }
+// Runs the key stream of a split batch is cut into. With the units taken longest first and the one-row
+// requests on the decode kernel, two per SM balance as well as more (cfg5: 1 x 0.330 ms, 2 x 0.330, 3 x
+// 0.335, 4 x 0.347, 6 x 0.370, 8 x 0.401): every cut costs a CTA's set-up, a tile of partial rows written
+// and read again, and a Q load.
+int prefill_paged_parts(const RfxPagedAttentionArgs* a) { (void)a; return 2 * sm_count(); }
 int prefill_paged_unit_rows(const RfxPagedAttentionArgs* a) { return 2 * (int)(128 / (a->num_q_heads / a->num_kv_heads)); }
 
 // A request with a single query row fills 1/18th or less of a 128-row tile and still pays the
