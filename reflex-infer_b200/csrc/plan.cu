@@ -98,6 +98,13 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
     if (parts < 1) parts = 1;
     const long long q = T > 0 ? (T + parts - 1) / parts : 1;
     const long long n_parts = T > 0 ? (T + q - 1) / q : 0;
+    // Positions in the stream are divided by the run length twice per (request, kv head) and pass. One or
+    // two warps run this kernel, every instruction at its full latency, and a 64-bit division is some 150
+    // of them: with the stream shorter than 2^31 tiles (it always is) the 32-bit one is taken.
+    const bool small_stream = T < (1ll << 31);
+    auto run_of = [&](long long pos) -> long long {
+        return small_stream ? (long long)((unsigned)pos / (unsigned)q) : pos / q;
+    };
 
     const bool list_units = unit_order != nullptr && unit_rows > 0;
     int ucnt[kUnitClasses];  // this thread's units per class (kept in registers: constant indices only)
@@ -125,7 +132,7 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
             if (tb > 0) {
                 for (int h = 0; h < Hkv; ++h) {
                     const long long off = pre * Hkv + h * tb + c * (ne * Hkv + h);
-                    const long long p0 = off / q, p1 = (off + tb - 1) / q;
+                    const long long p0 = run_of(off), p1 = run_of(off + tb - 1);
                     const long long ni = p1 - p0 + 1;
                     item_pre += ni;
                     row_pre += ni * nq * G;
@@ -204,7 +211,7 @@ plan_kernel(const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ q_
             pair_item_begin[(long long)b * Hkv + h] = (int)it;
             if (tb == 0) continue;
             const long long off = pre * Hkv + h * tb + c * (ne * Hkv + h);
-            const long long p0 = off / q, p1 = (off + tb - 1) / q;
+            const long long p0 = run_of(off), p1 = run_of(off + tb - 1);
             for (long long p = p0; p <= p1; ++p) {
                 const long long s = max(off, p * q), e = min(off + tb, (p + 1) * q);
                 items[it] = make_int4(b, h, (int)((s - off) * kPlanTile), min(ctx, (int)((e - off) * kPlanTile)));
