@@ -175,10 +175,18 @@ paged_combine_kernel(T* __restrict__ out, const __grid_constant__ HeadGatherDev 
         const int64_t r = orow / Hq;
         int b, qi;
         if (q_start) {
-            int lo = 0, hi = B;  // last b with q_start[b] <= r
-            while (hi - lo > 1) {
-                const int mid = (lo + hi) >> 1;
-                if (q_start[mid] <= r) lo = mid; else hi = mid;
+            // The last b with q_start[b] <= r, 32 probes at a time: every probe of a binary search is a
+            // dependent round trip (ten of them for a thousand requests), and with a few rows per warp the
+            // kernel's time was those round trips.
+            int lo = 0, span = B;  // the answer is in [lo, lo + span)
+            while (span > 1) {
+                const int step = (span + 31) >> 5;
+                const int idx = lo + (int)(threadIdx.x & 31) * step;
+                const bool le = idx < lo + span && (int64_t)q_start[idx] <= r;  // true for lane 0
+                const unsigned m = __ballot_sync(0xffffffffu, le);
+                const int k = 31 - __clz((int)(m | 1u));
+                lo += k * step;
+                span = min(step, span - k * step);
             }
             b = lo;
             qi = (int)(r - q_start[b]);
