@@ -32,6 +32,16 @@
 //
 // Causal masking is bottom-right aligned: token t of n sees keys 0..ctx-n+t; K tiles wholly
 // above the diagonal are never loaded. Tensor-pipe bound: 4*rows*keys*D FLOPs per tile pair.
+//
+// The way out. A thread owns a whole row, so rows stored straight from the threads put the 32 rows
+// of every store instruction into 32 different lines. Whole rows (no split over the keys): a tile
+// whose rows all have a query is written into its Q buffer in the Q box's layout and leaves as two
+// TMA stores through a tensor map over the output; other tiles are stored row by row. Split over
+// the keys: a warp's 32 partial rows are one 16 KB block of the workspace, passed through shared
+// memory and stored 512 contiguous bytes per instruction.
+//
+// Split batches take their work from the plan's list of units -- (item, pair of query tiles), the
+// longest first -- one CTA per unit; a CTA beyond the list leaves on one header read.
 #include <stdlib.h>
 
 #include <type_traits>
