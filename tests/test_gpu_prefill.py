@@ -154,14 +154,16 @@ def test_chunked_prefill_mixed_batch_tensor_core(bs, native, monkeypatch):
                                 target_chunk=chunk, **kw)
         assert ws.status() == 0 and torch.isfinite(out_c).all()
         torch.testing.assert_close(out_c.cpu().float(), ref.float(), atol=2e-2, rtol=2e-2)
-    # the one-row requests handed to the decode kernel (on by itself only for decode-heavy batches)
-    with _debug(native, "mixed=1"):
-        call = PagedAttentionCall(q_rot.to(DEV), kc.to(DEV), vc.to(DEV), g.block_table, g.context_lens, **kw)
-        if bs <= 64:
-            assert call.kernel_kind == 3
-        out_m = call.run()
-    assert ws.status() == 0
-    torch.testing.assert_close(out_m.cpu().float(), ref.float(), atol=2e-2, rtol=2e-2)
+    # the one-row requests handed to the decode kernel (the default for a split batch), and kept on the
+    # tensor-core kernel
+    for words, kind in (("mixed=1", 3), ("mixed=0", 2)):
+        with _debug(native, words):
+            call = PagedAttentionCall(q_rot.to(DEV), kc.to(DEV), vc.to(DEV), g.block_table, g.context_lens, **kw)
+            if bs <= 64:
+                assert call.kernel_kind == kind
+            out_m = call.run()
+        assert ws.status() == 0
+        torch.testing.assert_close(out_m.cpu().float(), ref.float(), atol=2e-2, rtol=2e-2)
 
 
 def test_decode_heavy_mixed_batch_hands_rows_to_decode_kernel(native):
