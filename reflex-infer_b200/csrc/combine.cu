@@ -168,16 +168,19 @@ paged_combine_kernel(T* __restrict__ out, const __grid_constant__ HeadGatherDev 
     }
     const int warp = threadIdx.x >> 5;
     const int G = Hq / Hkv;
-    const int64_t rows = n_q * Hq;
-    for (int64_t orow = (int64_t)blockIdx.x * kCombineWarps + warp; orow < rows;
-         orow += (int64_t)gridDim.x * kCombineWarps) {
-        const int h = (int)(orow % Hq);
-        const int64_t r = orow / Hq;
+    // A warp takes the G rows of one (query row, kv head) after one another: they belong to the same
+    // request and pair and share its items, so the look-ups that come before a row's partials (request,
+    // pair, items: dependent round trips, most of this kernel's time when each row did its own) are made
+    // once per group.
+    const int64_t groups = n_q * Hkv;
+    for (int64_t grp = (int64_t)blockIdx.x * kCombineWarps + warp; grp < groups;
+         grp += (int64_t)gridDim.x * kCombineWarps) {
+        const int hkv = (int)(grp % Hkv);
+        const int64_t r = grp / Hkv;
         int b, qi;
         if (q_start) {
             // The last b with q_start[b] <= r, 32 probes at a time: every probe of a binary search is a
-            // dependent round trip (ten of them for a thousand requests), and with a few rows per warp the
-            // kernel's time was those round trips.
+            // dependent round trip (ten of them for a thousand requests).
             int lo = 0, span = B;  // the answer is in [lo, lo + span)
             while (span > 1) {
                 const int step = (span + 31) >> 5;
@@ -194,22 +197,25 @@ paged_combine_kernel(T* __restrict__ out, const __grid_constant__ HeadGatherDev 
             b = (int)r;
             qi = 0;
         }
-        const int hkv = h / G, g = h % G;
         const long long pair = (long long)b * Hkv + hkv;
         const int item0 = pair_item_begin[pair];
         const int ns = pair_item_begin[pair + 1] - item0;
-        const int within = qi * G + g;
-        auto run = [&](const auto& sink) {
-            if (rows_follow_items)  // one query row per request: item i owns partial rows [i*G, i*G + G)
-                combine_row<T>(ns, [&](int s) { return (long long)(item0 + s) * G + g; }, pm, pl, pacc, D, sink);
+        for (int g = 0; g < G; ++g) {
+            const int h = hkv * G + g;
+            const int64_t orow = r * Hq + h;
+            const int within = qi * G + g;
+            auto run = [&](const auto& sink) {
+                if (rows_follow_items)  // one query row per request: item i owns partial rows [i*G, i*G + G)
+                    combine_row<T>(ns, [&](int s) { return (long long)(item0 + s) * G + g; }, pm, pl, pacc, D, sink);
+                else
+                    combine_row<T>(ns, [&](int s) { return (long long)item_prow[item0 + s] + within; }, pm, pl, pacc, D,
+                                   sink);
+            };
+            if (GATHER)
+                run(PeerRows<T>{&hg, (r * ((int64_t)hg.world * Hq) + (int64_t)hg.rank * Hq + h) * D, buf_off});
             else
-                combine_row<T>(ns, [&](int s) { return (long long)item_prow[item0 + s] + within; }, pm, pl, pacc, D,
-                               sink);
-        };
-        if (GATHER)
-            run(PeerRows<T>{&hg, (r * ((int64_t)hg.world * Hq) + (int64_t)hg.rank * Hq + h) * D, buf_off});
-        else
-            run(LocalRow<T>{out + orow * D});
+                run(LocalRow<T>{out + orow * D});
+        }
     }
     if (GATHER) {
         // Every thread's stores are visible system-wide before its CTA is counted.
@@ -259,8 +265,8 @@ splitk_combine_kernel(T* __restrict__ out, const int32_t* __restrict__ split_beg
 
 int launch_paged_combine(const RfxPagedAttentionArgs* a, const PlanLayout& L, const PlanPtrs& P,
                          const RfxHeadGatherArgs* g) {
-    const int64_t rows = a->n_q * a->num_q_heads;
-    int64_t blocks = ceil_div<int64_t>(rows, kCombineWarps);
+    const int64_t groups = a->n_q * a->num_kv_heads;  // a warp per (query row, kv head)
+    int64_t blocks = ceil_div<int64_t>(groups, kCombineWarps);
     const int64_t cap = (int64_t)sm_count() * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
