@@ -547,6 +547,30 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             // 512 contiguous bytes per instruction. Nothing crosses a warp: __syncwarp is all it needs.
             unsigned char* wbuf = (x == 0 ? sQ : sK) + (size_t)(warp & 3) * 16384;
             const int rl = r & 31;
+            const int r_base = (warp & 3) * 32;
+            const int live_rows = max(0, min(32, min(rows_used, (n_q - tok0 - x * P.T) * P.G) - r_base));
+            if (n_kv > 0 && live_rows == 32 && P.out_by_tma) {
+                // All 32 rows have a query: the block is written in the form of one TMA box of a view
+                // [4 column blocks][rows][128 B] of the partial array (128-byte swizzle) and one thread
+                // hands it over; the threads save their store and wait instructions.
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t w[32];
+                    ptx::tmem_ld32(o_addr + c * 32, w);
+                    ptx::tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        *reinterpret_cast<uint4*>(wbuf + c * 4096 + rl * 128 + ((i ^ (rl & 7)) << 4)) =
+                            make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+                }
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::tma_store_3d(&omap, wbuf, 0, (int)((int64_t)prow + (int64_t)(tok0 + x * P.T) * P.G + r_base), 0);
+                    ptx::tma_store_commit();
+                    ptx::tma_store_wait_read();
+                }
+            } else {
             if (n_kv > 0) {  // uniform over the CTA; the load is warp-collective
 #pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
@@ -560,14 +584,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 }
             }
             __syncwarp();
-            const int r_base = (warp & 3) * 32;
-            const int live_rows = max(0, min(32, min(rows_used, (n_q - tok0 - x * P.T) * P.G) - r_base));
             float* gblock = P.pacc + ((int64_t)prow + (int64_t)(tok0 + x * P.T) * P.G + r_base) * kPfHD;
 #pragma unroll 4
             for (int k = 0; k < live_rows; ++k) {
                 const uint4 v = n_kv > 0 ? *reinterpret_cast<const uint4*>(wbuf + k * 512 + ((lane ^ k) << 4))
                                          : make_uint4(0, 0, 0, 0);
                 reinterpret_cast<uint4*>(gblock + (size_t)k * kPfHD)[lane] = v;
+            }
             }
         } else if (ok_all && P.out_by_tma && tok0 + x * P.T + P.T <= n_q) {
             // Every row of the tile has a query: the tile goes out the way Q came in. A thread's row is
@@ -830,6 +853,14 @@ int launch_prefill_paged(const RfxPagedAttentionArgs* a, int32_t* status_word, c
         if (r) return fail(RFX_CUDA_ERROR, "cuTensorMapEncodeTiled(q) failed (%d)", r);
         // whole rows per CTA: the output [N, Hq, D] is laid out like Q
         out_by_tma = split == nullptr && encode_tiled_16bit(&om, a->out, 3, dims, str, box) == 0;
+        if (!out_by_tma) om = qm;
+    }
+    if (split) {
+        // the partial accumulator rows [cap_rows][128 fp32] seen as [4 column blocks][rows][64 16-bit units]
+        const uint64_t dims[3] = {64, (uint64_t)L->cap_rows, 4};
+        const uint64_t str[2] = {(uint64_t)kPfHD * 4, 128};
+        const uint32_t box[3] = {64, 32, 4};
+        out_by_tma = encode_tiled_16bit(&om, split->acc, 3, dims, str, box) == 0;
         if (!out_by_tma) om = qm;
     }
     {
