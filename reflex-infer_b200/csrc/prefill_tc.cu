@@ -499,15 +499,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             }
             const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
             // probabilities, packed to 16 bits, written over the S columns (all already in registers)
-            float ls[4] = {0.f, 0.f, 0.f, 0.f};  // independent partial sums
+            float2 ls[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};  // independent partial sums
+            const float2 sc2 = make_float2(P.scale_log2, P.scale_log2), nm2 = make_float2(-m_use, -m_use);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float p0 = ptx::ex2(fmaf(__uint_as_float(v[c * 32 + i]), P.scale_log2, -m_use));
-                    const float p1 = ptx::ex2(fmaf(__uint_as_float(v[c * 32 + i + 1]), P.scale_log2, -m_use));
-                    ls[(i >> 1) & 3] += p0 + p1;
+                    // two scores per FMA and per add (the packed fp32 forms)
+                    const float2 t = __ffma2_rn(make_float2(__uint_as_float(v[c * 32 + i]), __uint_as_float(v[c * 32 + i + 1])), sc2, nm2);
+                    const float p0 = ptx::ex2(t.x), p1 = ptx::ex2(t.y);
+                    ls[(i >> 1) & 1] = __fadd2_rn(ls[(i >> 1) & 1], make_float2(p0, p1));
                     if (BF) {
                         __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                         pk[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
@@ -518,7 +520,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 }
                 ptx::tmem_st16(s_addr + c * 16, pk);
             }
-            l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+            l_run += (ls[0].x + ls[0].y) + (ls[1].x + ls[1].y);
             ptx::tmem_wait_st();
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(&bars[PF_PFULL + x]);
